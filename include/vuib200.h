@@ -1,0 +1,214 @@
+/*
+ * vuib200.h - C ABI of libvuib200: Vui Nano's per-codec-frame decode step as
+ * hand-written CUDA for sm_100a.
+ *
+ * The reference (fluxions-ai/vui) is pure Python over PyTorch: it has no FFI for
+ * this path, so each entry point cites the Python function whose device work it
+ * replaces (paths relative to that project).  The Python shim in
+ * vui_b200/engine.py keeps the reference's Engine / Row / GenConfig surface and
+ * calls these through ctypes.
+ *
+ * Conventions
+ *  - every function returns a VuibStatus (0 = OK, negative = error); nothing
+ *    throws, aborts or exits; vuib_last_error() gives the text of the last error.
+ *  - all "dev" pointers are DEVICE pointers borrowed from the caller (torch
+ *    tensors); the library never allocates or frees device memory, and never
+ *    synchronises the device unless a function says so.
+ *  - every kernel is launched on the cudaStream_t the caller passes (as void*),
+ *    so the calls can be captured into a CUDA graph and replayed once per frame.
+ *  - a handle is not thread-safe; use one host thread per engine.
+ *  - matrices are bf16, row-major (out_features, in_features), as torch stores
+ *    nn.Linear.weight.  Codes are int64.  KV layout is the reference's
+ *    FlashKVCache: (slots, max_seq, n_kv_heads, head_dim) bf16 per layer plus one
+ *    shared int32 seq_lens[slots]  (src/vui/model.py:71-99, 473-495).
+ */
+#ifndef VUIB200_H
+#define VUIB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VUIB_ABI_VERSION 1
+#define VUIB_MAX_LAYERS 64
+
+typedef enum VuibStatus {
+    VUIB_OK = 0,
+    VUIB_ERR_NULL = -1,        /* a required pointer is NULL */
+    VUIB_ERR_SHAPE = -2,       /* unsupported model shape */
+    VUIB_ERR_RANGE = -3,       /* batch / row count / slot / length out of range */
+    VUIB_ERR_UNBOUND = -4,     /* weights, KV, rope table or workspace not bound yet */
+    VUIB_ERR_CUDA = -5,        /* a CUDA runtime call failed (text in last_error) */
+    VUIB_ERR_WORKSPACE = -6,   /* workspace too small or misaligned */
+    VUIB_ERR_DEVICE_FLAG = -7  /* a kernel recorded a bad slot / position / code */
+} VuibStatus;
+
+/* Model + engine shape.  Mirrors vui.config.VuiConfig (src/vui/config.py:16-54)
+ * plus the sizes Engine.__init__ fixes (src/vui/engine.py:294-346). */
+typedef struct VuibConfig {
+    int32_t d_model, n_layers, n_heads, n_kv_heads, head_dim, ffn;
+    int32_t n_quantizers, codebook_size;
+    int32_t rq_d_model, rq_n_layers, rq_n_heads, rq_ffn;
+    float norm_eps;     /* backbone RMSNorm eps (1e-5) */
+    float rq_norm_eps;  /* depth-transformer RMSNorm eps (1e-6) */
+    int32_t n_slots;    /* KV slots = max_rows + 1 (spare slot = padding target) */
+    int32_t max_seq;    /* positions per slot */
+    int32_t max_rows;   /* most rows (streams) in one decode step */
+    int32_t max_prefill_rows; /* most rows (positions) in one prefill call */
+} VuibConfig;
+
+/* Borrowed device pointers to the weights; names follow the reference state dict
+ * (src/vui/mlx/tts/weights.py:121-192 lists the keys). */
+typedef struct VuibWeights {
+    const void* audio_emb;   /* audio_emb.embedding.weight (Q*CS, d) */
+    const void* codec_head;  /* codec_head.weight (CS, d) */
+    const void* eos_w;       /* eos_head.weight (1, d) */
+    const void* eos_b;       /* eos_head.bias (1) */
+    const void* final_norm;  /* decoder.norm.weight (d) */
+    const void* attn_norm[VUIB_MAX_LAYERS];
+    const void* wqkv[VUIB_MAX_LAYERS];      /* ((H+2Hkv)*hd, d), rows q|k|v */
+    const void* out_proj[VUIB_MAX_LAYERS];  /* (d, d) */
+    const void* mlp_norm[VUIB_MAX_LAYERS];
+    const void* w1[VUIB_MAX_LAYERS];        /* (ffn, d) */
+    const void* w3[VUIB_MAX_LAYERS];        /* (ffn, d) */
+    const void* w2[VUIB_MAX_LAYERS];        /* (d, ffn) */
+    const void* rq_backbone_proj;  /* (rd, d) */
+    const void* rq_code_emb;       /* ((Q-1)*CS, rd) */
+    const void* rq_pos_emb;        /* (Q, rd) */
+    const void* rq_head;           /* head_W (Q-1, CS, rd) */
+    const void* rq_norm;           /* (rd) */
+    const void* rq_attn_norm[VUIB_MAX_LAYERS];
+    const void* rq_wqkv[VUIB_MAX_LAYERS];   /* (3*rd, rd) */
+    const void* rq_out_proj[VUIB_MAX_LAYERS];
+    const void* rq_mlp_norm[VUIB_MAX_LAYERS];
+    const void* rq_w1[VUIB_MAX_LAYERS];
+    const void* rq_w3[VUIB_MAX_LAYERS];
+    const void* rq_w2[VUIB_MAX_LAYERS];
+} VuibWeights;
+
+/* Sampling controls for one depth step.  Copied to the device by
+ * vuib_set_sampling(), so a captured graph picks up new values on replay. */
+typedef struct VuibSampling {
+    float temperature;     /* cb0 and depth codebooks (engine.py:857, model.py:957) */
+    int32_t top_k_cb0;     /* 1 = greedy (first index on ties), 0 = whole distribution */
+    int32_t top_k_rq;      /* 1 = greedy; the reference captures 100 (engine.py:395-397) */
+    float rep_penalty;     /* <= 1 disables (engine.py:571-590) */
+    int32_t rep_window;    /* 0 = counts never expire (engine.py:606-616) */
+    int32_t n_codebooks;   /* 0 = all Q; else emit Q' codes, rest zero (engine.py:473-479) */
+    uint64_t seed;         /* Philox key; draws are keyed (seed, slot, frame, codebook) */
+} VuibSampling;
+
+typedef struct VuibEngine VuibEngine;
+
+int32_t vuib_abi_version(void);
+
+/* Validates the shape and creates a handle (host memory only).
+ * Replaces the bookkeeping half of Engine._setup_graphs (engine.py:375-432). */
+int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out);
+int32_t vuib_destroy(VuibEngine* e);
+int32_t vuib_last_error(VuibEngine* e, char* buf, size_t n);
+
+/* Scratch for activations, attention partials, depth-transformer KV, sampling
+ * state.  The caller allocates `bytes` (256-byte aligned), ZEROES it once, and
+ * binds it; it must outlive the handle's use. */
+int32_t vuib_workspace_bytes(VuibEngine* e, size_t* bytes);
+int32_t vuib_bind_workspace(VuibEngine* e, void* dev, size_t bytes);
+
+int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w);
+/* k[l], v[l]: (n_slots, max_seq, n_kv_heads, head_dim) bf16; seq_lens: int32[n_slots].
+ * Same tensors the reference keeps in model.decoder.flash_kv_caches (model.py:473-495),
+ * so its KV save/load code (serving/stream/tts_worker.py:885-1028) keeps working. */
+int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* v_dev, int32_t* seq_lens_dev);
+/* (max_seq, head_dim, 2) bf16 [cos, sin] table as precompute_freqs_cis builds it
+ * (src/vui/rope.py:60-77) and Vui.bfloat16() casts it. */
+int32_t vuib_bind_rope(VuibEngine* e, const void* freqs_cis_dev);
+
+/* Copies *s to the device-side control block (async on `stream`). */
+int32_t vuib_set_sampling(VuibEngine* e, const VuibSampling* s, void* stream);
+
+/* Optional debug taps for the parity tests (NULL disables each):
+ *  layer_hidden: (n_layers, max_rows, d) bf16 - residual stream after each block
+ *  rq_logits:    (max_rows, Q-1, CS) bf16     - depth-head logits per codebook   */
+int32_t vuib_set_taps(VuibEngine* e, void* layer_hidden_dev, void* rq_logits_dev);
+
+/* Prefill: run n_rows embeddings through the backbone, appending K/V.
+ * Replaces Engine._prefill_emb (engine.py:674-694) for any number of slots at once.
+ *  row_slot/row_pos: int32[n_rows] - slot and position of each row; rows of one
+ *      slot must carry consecutive positions starting at that slot's length.
+ *  emb: (n_rows, d) bf16;  hidden_out: (n_rows, d) bf16 final-norm output.
+ * Does not touch seq_lens (the caller adds the segment lengths, as the reference
+ * does on the host). */
+int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* row_slot_dev,
+                     const int32_t* row_pos_dev, const void* emb_dev, void* hidden_out_dev,
+                     void* stream);
+
+/* One backbone decode step for B rows.  Replaces Engine._backbone_decode_body(_b)
+ * (engine.py:434-449, 485-502): embeds codes_in (gather-sum, model.py:559-563),
+ * 24 blocks at position seq_lens[slot], final norm, codec_head, eos_head, then
+ * seq_lens[slot[r]] += seq_inc[r] (1 when seq_inc is NULL).
+ *  slots: int32[B]; codes_in: int64 (B, Q); hidden_out (B, d), cb0_out (B, CS),
+ *  eos_out (B, 1): bf16. */
+int32_t vuib_backbone_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                           const int32_t* seq_inc_dev, const int64_t* codes_in_dev,
+                           void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
+                           void* stream);
+
+/* codec_head + eos_head on an already final-normed hidden (B, d): the frame-0
+ * path, model.codec_head(hidden) at engine.py:929, 1152, 1414. */
+int32_t vuib_heads(VuibEngine* e, int32_t B, const void* hidden_dev, void* cb0_out_dev,
+                   void* eos_out_dev, void* stream);
+
+/* Depth step: sample cb0 from cb0_logits (Engine._sample_cb0 + _rep_apply/_rep_push,
+ * engine.py:571-590, 855-863) then the RQ depth transformer over codebooks 1..Q-1
+ * (RQTransformer._generate_graph_body_kv, model.py:908-986) with no host round
+ * trip between codebooks.  Writes codes_out (B, Q) int64 and eos_prob_out (B) f32
+ * = sigmoid(eos logit) when both eos pointers are given.
+ *  first_frame != 0 samples cb0 from the whole distribution (engine.py:936-937). */
+int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                        const void* hidden_dev, const void* cb0_logits_dev,
+                        const void* eos_logit_dev, int32_t first_frame,
+                        int64_t* codes_out_dev, float* eos_prob_out_dev, void* stream);
+
+/* backbone step + depth step: one whole frame; codes_io holds frame k-1 on entry
+ * and frame k on return, so replaying the captured call generates a stream. */
+int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                          const int32_t* seq_inc_dev, int64_t* codes_io_dev,
+                          void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
+                          float* eos_prob_out_dev, void* stream);
+
+/* Gather-sum of codec codes alone: out[r] = sum_q audio_emb[q*CS + codes[r,q]]
+ * (AudioEmbedding.forward, model.py:559-563; Engine._audio_emb, engine.py:705-709).
+ * codes: int64 (n_rows, Q); out: bf16 (n_rows, d).  Feeds a prefill of audio frames. */
+int32_t vuib_embed_codes(VuibEngine* e, int32_t n_rows, const int64_t* codes_dev, void* out_dev,
+                         void* stream);
+
+/* The sampler alone on caller-supplied logits (B, CS) bf16: codebook 0 follows
+ * Engine._sample_cb0 (+ repetition penalty), codebooks >= 1 the depth-transformer
+ * rule (model.py:955-962).  Writes one int64 per row and advances the slot's
+ * draw counter.  Used by the distribution tests. */
+int32_t vuib_sample_rows(VuibEngine* e, int32_t B, const int32_t* slots_dev, const void* logits_dev,
+                         int32_t codebook, int64_t* codes_out_dev, void* stream);
+
+/* Clears the repetition-penalty state (counts + rolling history) of one slot, or
+ * of every slot when slot == -1: Engine._rep_reset / _rep_reset_slot
+ * (engine.py:555-569, 594-595).  Async on `stream`. */
+int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream);
+
+/* Position-only rewind / reset (engine.py:651-654).  Synchronous small copies. */
+int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len);
+int32_t vuib_get_seq_len(VuibEngine* e, int32_t slot, int32_t* len);
+
+/* Reads and clears the device error flag (bad slot / position / code seen by a
+ * kernel).  Synchronises `stream`. */
+int32_t vuib_check_device_flag(VuibEngine* e, void* stream);
+
+/* Kernel launches issued by this handle since creation (for benchmarks). */
+int64_t vuib_launch_count(VuibEngine* e);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VUIB200_H */

@@ -1,0 +1,107 @@
+"""The oracle (oracle/vui_oracle.py) against fixtures produced by the reference's
+own classes (tests/golden/make_golden.py).  CPU only."""
+import os
+
+import pytest
+import torch
+
+from oracle.vui_oracle import (TINY, FrameTrace, Oracle, OracleConfig, apply_rope, audio_embed,
+                               init_weights, rmsnorm, rope_table)
+
+
+def _load(golden_dir, name):
+    return torch.load(os.path.join(golden_dir, name))
+
+
+def test_tiny_fp32_end_to_end(golden_dir):
+    fx = _load(golden_dir, "tiny_fp32.pt")
+    o = Oracle(TINY, init_weights(TINY, 0, torch.float32), max_seq=64, dtype=torch.float32)
+    tr = FrameTrace()
+    codes = o.generate_greedy(0, fx["ids"], fx["codes"].shape[0], record=tr)
+    assert torch.equal(codes, fx["codes"])
+    assert torch.allclose(torch.stack(tr.hidden), fx["hidden"], atol=1e-4)
+    assert torch.allclose(torch.stack(tr.rq_logits), fx["rq_logits"], atol=1e-4)
+
+
+def test_ops_bf16_bit_exact(golden_dir, nano_sd):
+    """Elementwise ops and the gather-sum must match the reference's bf16 modules bit for bit."""
+    fx = _load(golden_dir, "ops_bf16.pt")
+    cfg = OracleConfig()
+    assert torch.equal(rmsnorm(fx["norm_x"], fx["norm_w"], cfg.norm_eps), fx["norm_y"])
+    assert torch.equal(
+        rmsnorm(fx["norm_x"][:, : cfg.rq_d_model], nano_sd["rq_transformer.norm.weight"], cfg.rq_norm_eps),
+        fx["rq_norm_y"])
+    table = rope_table(cfg.head_dim, 1360, cfg.rope_theta, torch.bfloat16)
+    assert torch.equal(table[fx["rope_pos"]], fx["rope_table_rows"])
+    assert torch.equal(apply_rope(table[fx["rope_pos"]], fx["rope_q"]), fx["rope_out"])
+    assert torch.equal(audio_embed(nano_sd["audio_emb.embedding.weight"], fx["emb_codes"], cfg.codebook_size),
+                       fx["emb_out"])
+    w = nano_sd
+    p = "decoder.blocks.0."
+    h = fx["mlp_x"]
+    F = torch.nn.functional
+    y = F.linear(F.silu(F.linear(h, w[p + "mlp.w1.weight"])) * F.linear(h, w[p + "mlp.w3.weight"]),
+                 w[p + "mlp.w2.weight"])
+    assert torch.equal(y, fx["mlp_y"])
+    assert torch.equal(F.linear(h, w[p + "attn.Wqkv.weight"]), fx["qkv_y"])
+
+
+def test_rq_bf16_against_reference(golden_dir, nano_sd):
+    fx = _load(golden_dir, "ops_bf16.pt")
+    o = Oracle(OracleConfig(), nano_sd, max_seq=8, dtype=torch.bfloat16)
+    # teacher-forced on the reference's codes: logits agree to bf16 tolerance (the reference's
+    # eager RQ path does its softmax attention in bf16, the graph path and this oracle in fp32),
+    # and every argmax that differs is a near-tie in the reference's logits
+    codes, logits = o.rq_generate(fx["rq_hidden"], fx["rq_code0"], top_k=1, return_logits=True,
+                                  forced=fx["rq_codes"])
+    ref = fx["rq_logits"].float()
+    err = (logits.float() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
+    diff = (codes != fx["rq_codes"]).nonzero()
+    for b, q in diff.tolist():
+        top2 = ref[b, q - 1].topk(2).values
+        assert (top2[0] - top2[1]) <= 2 * 2.0 ** -7, (b, q, top2)
+    assert len(diff) <= 6
+
+
+def test_cb0_topk_distribution(golden_dir):
+    fx = _load(golden_dir, "ops_bf16.pt")
+    lg = fx["cb0_logits"]
+    probs = torch.softmax(lg.float() / 0.8, dim=-1)
+    topv, topi = probs.topk(50, dim=-1)
+    mask = torch.zeros_like(probs).scatter_(1, topi, topv)
+    assert torch.allclose(mask / mask.sum(-1, keepdim=True), fx["cb0_probs_t0.8_k50"])
+
+
+def test_cfg1_fp32_codes(golden_dir, nano_sd):
+    """BASELINE config 1 (CPU fp32, 64 ids -> greedy frames) against the reference's codes."""
+    fx = _load(golden_dir, "cfg1_fp32.pt")
+    n = 12  # the first frames; the full 50 take ~10 s more and add nothing new
+    o = Oracle(OracleConfig(), nano_sd, max_seq=128, dtype=torch.float32)
+    tr = FrameTrace()
+    codes = o.generate_greedy(0, fx["ids"], n, record=tr)
+    assert torch.equal(codes, fx["codes"][:n])
+    kept = fx["frames_kept"].tolist()
+    for j, f in enumerate(kept):
+        if f < n:
+            assert torch.allclose(tr.hidden[f], fx["hidden"][j], atol=2e-4)
+            assert torch.allclose(tr.cb0[f], fx["cb0"][j], atol=2e-4)
+            assert torch.allclose(tr.rq_logits[f], fx["rq_logits"][j], atol=2e-4)
+
+
+def test_bf16_tolerance(golden_dir, nano_sd):
+    """bf16 oracle, frame 0 (64-token prefill through 24 blocks): within the bf16 tolerance
+    (max-abs error / max-abs value <= 2e-2, cosine >= 0.999) of the reference's fp32 result,
+    and as close to the reference's own CPU bf16 result as that one is to fp32 (two bf16 runs
+    that round at different places differ by about sqrt(2) times that)."""
+    fx = _load(golden_dir, "cfg_bf16_cpu.pt")
+    fx32 = _load(golden_dir, "cfg1_fp32.pt")
+    o = Oracle(OracleConfig(), nano_sd, max_seq=128, dtype=torch.bfloat16)
+    tr = FrameTrace()
+    o.generate_greedy(0, fx["ids"], 1, record=tr)
+    cos = torch.nn.functional.cosine_similarity
+    ref32, ref16 = fx32["hidden"][0], fx["hidden"][0].float()
+    assert cos(tr.hidden[0], ref32, dim=0) > 0.999
+    assert (tr.hidden[0] - ref32).abs().max() / ref32.abs().max() < 2e-2
+    assert cos(tr.hidden[0], ref16, dim=0) > 0.999
+    assert (tr.hidden[0] - ref16).abs().max() / ref16.abs().max() < 3e-2

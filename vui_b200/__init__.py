@@ -1,0 +1,7 @@
+"""vui_b200: Vui Nano's per-codec-frame decode step as sm_100a CUDA behind the
+reference's Engine / Row / GenConfig API."""
+
+from .engine import Engine, GenConfig, RenderRequest, Row, Segment
+from .model import VuiB200, VuiShape
+
+__all__ = ["Engine", "GenConfig", "RenderRequest", "Row", "Segment", "VuiB200", "VuiShape"]

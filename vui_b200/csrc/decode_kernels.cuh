@@ -1,0 +1,951 @@
+// Device code for the Vui Nano decode step on sm_100a: weight-streaming batched
+// GEMV with fused RMSNorm / RoPE / KV-append / SwiGLU / residual epilogues,
+// ragged split-KV GQA decode attention, the depth-transformer attention, and the
+// per-codebook sampler.
+//
+// Numerics follow the reference's bf16 rounding points (src/vui/model.py 286-297,
+// 204-258, 261-283; src/vui/rope.py 50): every tensor PyTorch materialises in
+// bf16 is rounded to bf16 here at the same place; GEMV sums are fp32.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vuib {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int HD = 64;             // head_dim of backbone and depth transformer
+constexpr int GEMV_THREADS = 256;  // 8 warps; one work item (1-2 weight rows) per warp
+constexpr int GEMV_WARPS = 8;
+constexpr int ATT_SPLIT = 128;     // keys per CTA in the backbone attention
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_ITERS = ATT_SPLIT / 16;  // 4 warps x 4 key groups per pass
+constexpr int PART_STRIDE = HD + 2;        // acc[64], m, l
+constexpr int SAMPLE_THREADS = 256;
+constexpr int SAMPLE_EL = 8;               // codebook_size = 256 * 8
+constexpr int REP_HIST_MAX = 64;
+
+enum DeviceFlag { FLAG_BAD_SLOT = 1, FLAG_BAD_POS = 2, FLAG_BAD_CODE = 4 };
+
+// Device-side control block (lives in the workspace; vuib_set_sampling fills it).
+struct SamplingCtl {
+    float temperature;
+    int32_t top_k_cb0;
+    int32_t top_k_rq;
+    float rep_penalty;
+    int32_t rep_window;
+    int32_t n_codebooks;
+    uint32_t seed_lo, seed_hi;
+};
+
+__device__ __forceinline__ float bf2f(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ bf16 f2bf(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ float rbf(float v) { return bf2f(f2bf(v)); }
+
+// 16-byte streaming load of weights: read-only path, do not pollute L1.
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int RT>
+__device__ __forceinline__ float pick(const float (&a)[RT], int r) {
+    float v = a[0];
+#pragma unroll
+    for (int i = 1; i < RT; ++i)
+        if (r == i) v = a[i];
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// Embedding gather-sum for a decode step (AudioEmbedding.forward, model.py:559-563)
+// plus the per-row (slot, position) table every later kernel of the step reads.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_embed_codes(
+    const int64_t* __restrict__ codes, const int32_t* __restrict__ slots,
+    const int32_t* __restrict__ seq_lens, const bf16* __restrict__ table, bf16* __restrict__ x,
+    int32_t* __restrict__ row_slot, int32_t* __restrict__ row_pos, int d, int Q, int CS,
+    int n_slots, int max_seq, int32_t* __restrict__ flag) {
+    const int r = blockIdx.x;
+    if (slots) {  // decode step: also publish the row's (slot, position)
+        int slot = slots[r];
+        if (slot < 0 || slot >= n_slots) {
+            if (threadIdx.x == 0) atomicOr(flag, FLAG_BAD_SLOT);
+            slot = n_slots - 1;
+        }
+        if (threadIdx.x == 0) {
+            int pos = seq_lens[slot];
+            if (pos < 0 || pos >= max_seq) {
+                atomicOr(flag, FLAG_BAD_POS);
+                pos = pos < 0 ? 0 : max_seq - 1;
+            }
+            row_slot[r] = slot;
+            row_pos[r] = pos;
+        }
+    }
+    for (int k = threadIdx.x * 8; k < d; k += blockDim.x * 8) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int q = 0; q < Q; ++q) {
+            long long c = codes[(size_t)r * Q + q];
+            if (c < 0 || c >= CS) {
+                atomicOr(flag, FLAG_BAD_CODE);
+                c = 0;
+            }
+            uint4 u = __ldg(reinterpret_cast<const uint4*>(table + ((size_t)q * CS + c) * d + k));
+            float f[8];
+            unpack8(u, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        }
+        *reinterpret_cast<uint4*>(x + (size_t)r * d + k) = pack8(acc);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Staging functors: fill the CTA's shared activation tile Xs[nr][K] (bf16).
+// ---------------------------------------------------------------------------
+
+// RMSNorm (model.py:292-297): fp32 x*rsqrt(mean(x^2)+eps) -> bf16 -> * weight -> bf16.
+struct StageNorm {
+    const bf16* x;   // row r of the GEMV lives at x + (r*row_mul + row_add)*K
+    const bf16* w;   // (K)
+    float eps;
+    int row_mul, row_add;
+    template <int K>
+    __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int rr = warp; rr < nr; rr += GEMV_WARPS) {
+            const bf16* xr = x + ((size_t)(r0 + rr) * row_mul + row_add) * K;
+            constexpr int IT = (K + 255) / 256;
+            float v[IT][8];
+            float ss = 0.f;
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int k = it * 256 + lane * 8;
+                if (k < K) {
+                    uint4 u = *reinterpret_cast<const uint4*>(xr + k);
+                    unpack8(u, v[it]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = fmaf(v[it][j], v[it][j], ss);
+                }
+            }
+            ss = warp_sum(ss);
+            const float rinv = rsqrtf(ss / (float)K + eps);
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int k = it * 256 + lane * 8;
+                if (k < K) {
+                    float wf[8], o[8];
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = rbf(v[it][j] * rinv) * wf[j];
+                    *reinterpret_cast<uint4*>(Xs + rr * K + k) = pack8(o);
+                }
+            }
+        }
+    }
+};
+
+struct StageCopy {
+    const bf16* x;  // (M, K)
+    template <int K>
+    __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r0 * K);
+        uint4* dst = reinterpret_cast<uint4*>(Xs);
+        for (int i = threadIdx.x; i < nr * (K / 8); i += GEMV_THREADS) dst[i] = src[i];
+    }
+};
+
+// Online-softmax state merge helpers (fp32, finite sentinel instead of -inf).
+constexpr float NEG_BIG = -1.0e30f;
+
+// Depth-transformer attention (RQBlock.forward_kv, model.py:613-635; SDPA math
+// backend: fp32 softmax over <= Q keys, scale 1/8) computed straight into the
+// tile that feeds out_proj.  One warp per head; lane = (key group g, 8-dim chunk s).
+struct StageRqAttn {
+    const bf16* q;    // (M, H*64)
+    const bf16* kc;   // (R, Qpos, H*64) this layer
+    const bf16* vc;
+    int H;            // heads
+    int Qpos;         // positions per row in the cache (n_quantizers)
+    int rows_per_b;   // row r -> b = r / rows_per_b, pos = pos_base + r % rows_per_b
+    int pos_base;
+    template <int K>
+    __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int s = lane & 7, g = lane >> 3;
+        for (int rr = 0; rr < nr; ++rr) {
+            const int r = r0 + rr;
+            const int b = r / rows_per_b, pos = pos_base + r % rows_per_b;
+            for (int h = warp; h < H; h += GEMV_WARPS) {
+                float qf[8];
+                unpack8(*reinterpret_cast<const uint4*>(q + (size_t)r * K + h * HD + s * 8), qf);
+                float m = NEG_BIG, l = 0.f, acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int t0 = 0; t0 <= pos; t0 += 4) {
+                    const int t = t0 + g;
+                    const bool ok = t <= pos;
+                    const size_t off = ((size_t)b * Qpos + (ok ? t : 0)) * K + h * HD + s * 8;
+                    float kf[8], vf[8];
+                    unpack8(*reinterpret_cast<const uint4*>(kc + off), kf);
+                    unpack8(*reinterpret_cast<const uint4*>(vc + off), vf);
+                    float d = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) d = fmaf(qf[j], kf[j], d);
+                    d += __shfl_xor_sync(0xffffffffu, d, 1);
+                    d += __shfl_xor_sync(0xffffffffu, d, 2);
+                    d += __shfl_xor_sync(0xffffffffu, d, 4);
+                    if (ok) {
+                        const float sc = d * 0.125f;
+                        const float mn = fmaxf(m, sc);
+                        const float corr = __expf(m - mn), p = __expf(sc - mn);
+                        l = l * corr + p;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(p, vf[j], acc[j] * corr);
+                        m = mn;
+                    }
+                }
+#pragma unroll
+                for (int o = 8; o <= 16; o <<= 1) {
+                    const float mo = __shfl_xor_sync(0xffffffffu, m, o);
+                    const float lo = __shfl_xor_sync(0xffffffffu, l, o);
+                    const float mn = fmaxf(m, mo);
+                    const float ca = __expf(m - mn), cb = __expf(mo - mn);
+                    l = l * ca + lo * cb;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float ao = __shfl_xor_sync(0xffffffffu, acc[j], o);
+                        acc[j] = acc[j] * ca + ao * cb;
+                    }
+                    m = mn;
+                }
+                if (g == 0) {
+                    const float inv = 1.f / l;
+                    float o8[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o8[j] = acc[j] * inv;
+                    *reinterpret_cast<uint4*>(Xs + rr * K + h * HD + s * 8) = pack8(o8);
+                }
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Epilogue functors: which weight rows a work item reads, and what to do with
+// the RT sums per weight row.  After the butterfly reduction every lane holds all
+// sums; lane r finishes activation row r.
+// ---------------------------------------------------------------------------
+
+// Wqkv (+ RoPE on q,k) with K/V written straight into the cache (MHA.forward_flash,
+// model.py:220-257; rope.py:16-57).  Work item = one interleaved pair (2i, 2i+1).
+struct EpiQkv {
+    const bf16* W;      // (N, K)
+    int K;
+    bf16* q_out;        // (M, q_cols)
+    int q_cols, kv_cols;
+    bf16* k_cache;      // this layer
+    bf16* v_cache;
+    const int32_t* row_slot;  // NULL -> depth-transformer addressing below
+    const int32_t* row_pos;
+    int max_seq;              // positions per slot in the cache
+    const bf16* rope;         // (max_seq, 64, 2) or NULL
+    int rows_per_b, pos_base; // used when row_slot == NULL
+    static constexpr int NC = 2;
+    __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
+        wr[0] = W + (size_t)(2 * item) * K;
+        wr[1] = wr[0] + K;
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[2][RT]) const {
+        if (lane >= nr) return;
+        const int r = r0 + lane;
+        const int n = 2 * item;
+        float t0 = rbf(pick<RT>(acc[0], lane)), t1 = rbf(pick<RT>(acc[1], lane));
+        int slot, pos;
+        if (row_slot) {
+            slot = row_slot[r];
+            pos = row_pos[r];
+        } else {
+            slot = r / rows_per_b;
+            pos = pos_base + r % rows_per_b;
+        }
+        if (rope && n < q_cols + kv_cols) {
+            const int dd = n & (HD - 1);
+            const bf16* f = rope + ((size_t)pos * HD + dd) * 2;
+            const float c0 = bf2f(f[0]), s0 = bf2f(f[1]), c1 = bf2f(f[2]), s1 = bf2f(f[3]);
+            // t*cos + rotate_half(t)*sin, each product and the sum rounded to bf16
+            const float o0 = rbf(rbf(t0 * c0) + rbf((-t1) * s0));
+            const float o1 = rbf(rbf(t1 * c1) + rbf(t0 * s1));
+            t0 = o0;
+            t1 = o1;
+        }
+        __nv_bfloat162 pr = __floats2bfloat162_rn(t0, t1);
+        if (n < q_cols) {
+            *reinterpret_cast<__nv_bfloat162*>(q_out + (size_t)r * q_cols + n) = pr;
+        } else if (n < q_cols + kv_cols) {
+            *reinterpret_cast<__nv_bfloat162*>(
+                k_cache + ((size_t)slot * max_seq + pos) * kv_cols + (n - q_cols)) = pr;
+        } else {
+            *reinterpret_cast<__nv_bfloat162*>(
+                v_cache + ((size_t)slot * max_seq + pos) * kv_cols + (n - q_cols - kv_cols)) = pr;
+        }
+    }
+};
+
+// x += bf16(W a): out_proj and w2 with the residual add (model.py:367, 374).
+struct EpiResidual {
+    const bf16* W;  // (N, K)
+    int K;
+    bf16* x;        // (M, N) residual stream, updated in place
+    int N;
+    bf16* tap;      // optional copy of the new x (M, N)
+    static constexpr int NC = 1;
+    __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
+        wr[0] = W + (size_t)item * K;
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[1][RT]) const {
+        if (lane >= nr) return;
+        const size_t idx = (size_t)(r0 + lane) * N + item;
+        const bf16 o = f2bf(bf2f(x[idx]) + rbf(pick<RT>(acc[0], lane)));
+        x[idx] = o;
+        if (tap) tap[idx] = o;
+    }
+};
+
+// silu(w1 h) * (w3 h)  (LlamaMLP.forward, model.py:282-283); item = hidden unit n.
+struct EpiSwiGLU {
+    const bf16* W1;
+    const bf16* W3;
+    int K;
+    bf16* act;  // (M, F)
+    int F;
+    static constexpr int NC = 2;
+    __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
+        wr[0] = W1 + (size_t)item * K;
+        wr[1] = W3 + (size_t)item * K;
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[2][RT]) const {
+        if (lane >= nr) return;
+        const float a = rbf(pick<RT>(acc[0], lane)), g = rbf(pick<RT>(acc[1], lane));
+        const float s = rbf(a / (1.0f + expf(-a)));
+        act[(size_t)(r0 + lane) * F + item] = f2bf(s * g);
+    }
+};
+
+// Plain bf16 output rows: codec_head / eos_head (item == n_main -> extra row with
+// bias, model.py:1099) and the depth-transformer heads.
+struct EpiLogits {
+    const bf16* W;      // (n_main, K)
+    int K;
+    int n_main;
+    bf16* out;          // (M, n_main)
+    const bf16* W_extra;  // (1, K) or NULL
+    const bf16* b_extra;  // (1)
+    bf16* out_extra;      // (M)
+    bf16* tap;            // optional second copy of out with its own row stride
+    int tap_stride;
+    static constexpr int NC = 1;
+    __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
+        wr[0] = item < n_main ? W + (size_t)item * K : W_extra;
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[1][RT]) const {
+        if (lane >= nr) return;
+        const int r = r0 + lane;
+        const float v = pick<RT>(acc[0], lane);
+        if (item < n_main) {
+            const bf16 o = f2bf(v);
+            out[(size_t)r * n_main + item] = o;
+            if (tap) tap[(size_t)r * tap_stride + item] = o;
+        } else {
+            out_extra[r] = f2bf(v + bf2f(b_extra[0]));
+        }
+    }
+};
+
+// Depth-transformer position 0: backbone_proj(hidden) + pos_emb[0] (model.py:921).
+struct EpiProjPos {
+    const bf16* W;    // (rd, K)
+    int K;
+    const bf16* pos_emb;  // row 0
+    bf16* out;        // (rows_out, rd); row of stream b is b*row_mul
+    int rd, row_mul;
+    static constexpr int NC = 1;
+    __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
+        wr[0] = W + (size_t)item * K;
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[1][RT]) const {
+        if (lane >= nr) return;
+        const int b = r0 + lane;
+        out[(size_t)b * row_mul * rd + item] =
+            f2bf(rbf(pick<RT>(acc[0], lane)) + bf2f(pos_emb[item]));
+    }
+};
+
+// ---------------------------------------------------------------------------
+// The batched GEMV.  Each warp keeps its 1-2 weight rows in registers (loaded
+// once, 16 bytes per lane per request, all requests in flight before any use)
+// and sweeps the M activation rows in tiles of RT staged in shared memory.
+// ---------------------------------------------------------------------------
+template <int K, int RT, class Stage, class Epi>
+__global__ void __launch_bounds__(GEMV_THREADS) k_gemv(Stage st, Epi ep, int M, int n_items) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Xs = reinterpret_cast<bf16*>(smem_raw);
+    constexpr int NC = Epi::NC;
+    constexpr int IT = (K + 255) / 256;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * GEMV_WARPS + warp;
+    const bool live = item < n_items;
+
+    uint4 w[NC][IT];
+    if (live) {
+        const bf16* wr[NC];
+        ep.rows(item, wr);
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int k = it * 256 + lane * 8;
+                w[c][it] = (k < K) ? ldg_stream(wr[c] + k) : make_uint4(0, 0, 0, 0);
+            }
+    }
+    for (int r0 = 0; r0 < M; r0 += RT) {
+        const int nr = min(RT, M - r0);
+        if (r0) __syncthreads();
+        st.template stage<K>(Xs, r0, nr);
+        __syncthreads();
+        if (live) {
+            float acc[NC][RT];
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                for (int r = 0; r < RT; ++r) acc[c][r] = 0.f;
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int k = it * 256 + lane * 8;
+                if (k < K) {
+                    float wf[NC][8];
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) unpack8(w[c][it], wf[c]);
+#pragma unroll
+                    for (int r = 0; r < RT; ++r) {
+                        if (r < nr) {
+                            float xf[8];
+                            unpack8(*reinterpret_cast<const uint4*>(Xs + r * K + k), xf);
+#pragma unroll
+                            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    acc[c][r] = fmaf(wf[c][j], xf[j], acc[c][r]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                for (int r = 0; r < RT; ++r) acc[c][r] = warp_sum(acc[c][r]);
+            ep.template store<RT>(item, r0, nr, lane, acc);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Backbone decode attention (flash_attn_with_kvcache call, model.py:247-257):
+// ragged per-row length row_pos[r]+1, GQA 2:1, scale 1/8, fp32 softmax.  One CTA
+// = (split of ATT_SPLIT keys, kv head, row); partial (acc, m, l) per split go to
+// scratch and the last CTA of a (row, kv head) merges them in split order, so the
+// result does not depend on arrival order.
+// ---------------------------------------------------------------------------
+struct AttnArgs {
+    const bf16* q;        // (R, Hq*64)
+    const bf16* kc;       // (slots, max_seq, Hkv, 64) this layer
+    const bf16* vc;
+    const int32_t* row_slot;
+    const int32_t* row_pos;
+    float* part;          // (R, Hq, S, PART_STRIDE)
+    int32_t* counters;    // (R, Hkv), zero between launches
+    bf16* out;            // (R, Hq*64)
+    int Hq, Hkv, max_seq, S;
+};
+
+__device__ __forceinline__ void softmax_merge(float& m, float& l, float (&acc)[8], float mo,
+                                              float lo, const float (&ao)[8]) {
+    const float mn = fmaxf(m, mo);
+    const float ca = __expf(m - mn), cb = __expf(mo - mn);
+    l = l * ca + lo * cb;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = acc[j] * ca + ao[j] * cb;
+    m = mn;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
+    const int sp = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+    const int len = a.row_pos[r] + 1;
+    const int nsplit = (len + ATT_SPLIT - 1) / ATT_SPLIT;
+    if (sp >= nsplit) return;
+    const int slot = a.row_slot[r];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = lane & 7, g = lane >> 3;
+    const int G = a.Hq / a.Hkv;  // q heads per kv head (2)
+    const int t_begin = sp * ATT_SPLIT, t_end = min(len, t_begin + ATT_SPLIT);
+    const size_t pos_stride = (size_t)a.Hkv * HD;
+    const bf16* kb = a.kc + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s * 8;
+    const bf16* vb = a.vc + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s * 8;
+
+    // all K and V requests of this lane in flight before any arithmetic
+    uint4 kr[ATT_ITERS], vr[ATT_ITERS];
+#pragma unroll
+    for (int it = 0; it < ATT_ITERS; ++it) {
+        const int t = t_begin + it * 16 + warp * 4 + g;
+        if (t < t_end) {
+            kr[it] = ldg_stream(kb + (size_t)t * pos_stride);
+            vr[it] = ldg_stream(vb + (size_t)t * pos_stride);
+        } else {
+            kr[it] = make_uint4(0, 0, 0, 0);
+            vr[it] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    __shared__ float sm[4][2][8][10];  // [warp][head][s][acc8, m, l]
+    __shared__ int s_last;
+    float qf[2][8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int hq = kvh * G + (h < G ? h : 0);
+        unpack8(*reinterpret_cast<const uint4*>(a.q + (size_t)r * a.Hq * HD + hq * HD + s * 8), qf[h]);
+    }
+    float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f}, acc[2][8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+
+#pragma unroll
+    for (int it = 0; it < ATT_ITERS; ++it) {
+        const int t = t_begin + it * 16 + warp * 4 + g;
+        float kf[8], vf[8];
+        unpack8(kr[it], kf);
+        unpack8(vr[it], vf);
+        float d[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float dd = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dd = fmaf(qf[h][j], kf[j], dd);
+            dd += __shfl_xor_sync(0xffffffffu, dd, 1);
+            dd += __shfl_xor_sync(0xffffffffu, dd, 2);
+            dd += __shfl_xor_sync(0xffffffffu, dd, 4);
+            d[h] = dd * 0.125f;
+        }
+        if (t < t_end) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float mn = fmaxf(m[h], d[h]);
+                const float corr = __expf(m[h] - mn), p = __expf(d[h] - mn);
+                l[h] = l[h] * corr + p;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(p, vf[j], acc[h][j] * corr);
+                m[h] = mn;
+            }
+        }
+    }
+    // merge the 4 key groups of the warp
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
+            const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+            float ao[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ao[j] = __shfl_xor_sync(0xffffffffu, acc[h][j], o);
+            softmax_merge(m[h], l[h], acc[h], mo, lo, ao);
+        }
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sm[warp][h][s][j] = acc[h][j];
+            sm[warp][h][s][8] = m[h];
+            sm[warp][h][s][9] = l[h];
+        }
+    }
+    __syncthreads();
+    // thread (h, dim): merge the 4 warps
+    const int h = threadIdx.x >> 6, dim = threadIdx.x & 63;
+    const int ds = dim >> 3, dj = dim & 7;
+    float M_ = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M_ = fmaxf(M_, sm[w][h][ds][8]);
+    float L_ = 0.f, O_ = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float c = __expf(sm[w][h][ds][8] - M_);
+        L_ += sm[w][h][ds][9] * c;
+        O_ += sm[w][h][ds][dj] * c;
+    }
+    const bool head_ok = h < G;
+    const int hq = kvh * G + (head_ok ? h : 0);
+    if (nsplit == 1) {
+        if (head_ok) a.out[(size_t)r * a.Hq * HD + hq * HD + dim] = f2bf(O_ / L_);
+        return;
+    }
+    float* pp = a.part + (((size_t)r * a.Hq + hq) * a.S + sp) * PART_STRIDE;
+    if (head_ok) {
+        pp[dim] = O_;
+        if (dim == 0) {
+            pp[HD] = M_;
+            pp[HD + 1] = L_;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(a.counters + r * a.Hkv + kvh, 1);
+        s_last = (old == nsplit - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (head_ok) {
+        const float* pb = a.part + ((size_t)r * a.Hq + hq) * a.S * PART_STRIDE;
+        float Mx = NEG_BIG;
+        for (int i = 0; i < nsplit; ++i) Mx = fmaxf(Mx, __ldcg(pb + i * PART_STRIDE + HD));
+        float Ls = 0.f, Os = 0.f;
+        for (int i = 0; i < nsplit; ++i) {
+            const float c = __expf(__ldcg(pb + i * PART_STRIDE + HD) - Mx);
+            Ls += __ldcg(pb + i * PART_STRIDE + HD + 1) * c;
+            Os += __ldcg(pb + i * PART_STRIDE + dim) * c;
+        }
+        a.out[(size_t)r * a.Hq * HD + hq * HD + dim] = f2bf(Os / Ls);
+    }
+    if (threadIdx.x == 0) a.counters[r * a.Hkv + kvh] = 0;
+}
+
+// ---------------------------------------------------------------------------
+// Final RMSNorm of the backbone -> hidden_out, and seq_lens[slot] += inc.
+// (Decoder.forward_flash model.py:548-549; engine.py:449, 502.)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_final_norm(const bf16* __restrict__ x,
+                                                    const bf16* __restrict__ w, float eps,
+                                                    bf16* __restrict__ out, int d,
+                                                    const int32_t* __restrict__ row_slot,
+                                                    const int32_t* __restrict__ seq_inc,
+                                                    int32_t* __restrict__ seq_lens, int bump) {
+    const int r = blockIdx.x;
+    __shared__ float red[4];
+    const bf16* xr = x + (size_t)r * d;
+    float ss = 0.f;
+    for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + k), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float tot = red[0] + red[1] + red[2] + red[3];
+    const float rinv = rsqrtf(tot / (float)d + eps);
+    for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
+        float f[8], wf[8], o[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + k), f);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rbf(f[j] * rinv) * wf[j];
+        *reinterpret_cast<uint4*>(out + (size_t)r * d + k) = pack8(o);
+    }
+    if (bump && threadIdx.x == 0) {
+        const int inc = seq_inc ? seq_inc[r] : 1;
+        if (inc) seq_lens[row_slot[r]] += inc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Depth-transformer token for position p >= 1: code_emb[(p-1)*CS + code] + pos_emb[p]
+// (model.py:922-925, 967-969).  Stage 0 writes it to row 2b+1, later stages to row b.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(64) k_rq_embed(const int32_t* __restrict__ code_cur,
+                                                 const bf16* __restrict__ code_emb,
+                                                 const bf16* __restrict__ pos_emb,
+                                                 bf16* __restrict__ xout, int rd, int CS, int p,
+                                                 int row_mul, int row_add) {
+    const int b = blockIdx.x;
+    const int code = code_cur[b];
+    const bf16* e = code_emb + ((size_t)(p - 1) * CS + code) * rd;
+    const bf16* pe = pos_emb + (size_t)p * rd;
+    bf16* o = xout + ((size_t)b * row_mul + row_add) * rd;
+    for (int k = threadIdx.x * 8; k < rd; k += 64 * 8) {
+        float a[8], c[8], s[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(e + k)), a);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(pe + k)), c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j] = a[j] + c[j];
+        *reinterpret_cast<uint4*>(o + k) = pack8(s);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Sampler: one CTA per row over CS = 2048 logits.
+//   cb0 (engine.py:571-590, 855-863): optional repetition penalty, then greedy or
+//       softmax(l/T) restricted to the top-k, inverse-CDF draw.
+//   depth codebooks (model.py:955-962): l/T, keep entries >= k-th value, softmax,
+//       draw.  Greedy = first index of the maximum (torch.argmax).
+// Uniforms come from Philox4x32-10 keyed (seed; slot, frame counter, codebook).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+        const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+        c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+}
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+struct SampleArgs {
+    const bf16* logits;       // (B, CS) rows with stride `stride`
+    int stride;
+    const SamplingCtl* ctl;
+    const int32_t* slots;     // (B)
+    int32_t* frame_ctr;       // (n_slots)
+    int codebook;             // 0 = cb0
+    int first_frame;          // cb0 of a chunk's first frame: no top-k
+    float* rep_counts;        // (n_slots, CS) cb0 only
+    int32_t* rep_hist;        // (n_slots, REP_HIST_MAX)
+    int32_t* rep_head;        // (n_slots)
+    int32_t* rep_filled;      // (n_slots)
+    int32_t* code_cur;        // (B) out
+    int64_t* codes_out;       // (B, Q) out, column out_col
+    int Q, out_col;
+    const bf16* eos_logit;    // (B) optional, cb0 only
+    float* eos_prob;          // (B)
+    int bump_frame;           // last sampler of the frame advances frame_ctr
+    int zero_from;            // >0: also zero codes_out[r, zero_from..Q)
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
+    constexpr int CS = SAMPLE_THREADS * SAMPLE_EL;
+    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int slot = a.slots[r];
+    const SamplingCtl ctl = *a.ctl;
+    const bool is_cb0 = a.codebook == 0;
+    __shared__ float s_f[8];
+    __shared__ int s_i[8];
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_prefix, s_krem;
+    __shared__ int s_pick, s_lastkept;
+
+    float v[SAMPLE_EL];
+    unpack8(*reinterpret_cast<const uint4*>(a.logits + (size_t)r * a.stride + tid * SAMPLE_EL), v);
+    if (is_cb0 && ctl.rep_penalty > 1.0f) {
+        const float* cnt = a.rep_counts + (size_t)slot * CS + tid * SAMPLE_EL;
+#pragma unroll
+        for (int j = 0; j < SAMPLE_EL; ++j) {
+            const float c = cnt[j];
+            if (c != 0.f) {
+                const float f = powf(ctl.rep_penalty, c);
+                v[j] = v[j] > 0.f ? v[j] / f : v[j] * f;
+            }
+        }
+    }
+    int top_k = is_cb0 ? (a.first_frame && ctl.top_k_cb0 != 1 ? 0 : ctl.top_k_cb0) : ctl.top_k_rq;
+    if (top_k >= CS) top_k = 0;
+
+    // block argmax, first index on ties
+    float bv = v[0];
+    int bi = tid * SAMPLE_EL;
+#pragma unroll
+    for (int j = 1; j < SAMPLE_EL; ++j)
+        if (v[j] > bv) { bv = v[j]; bi = tid * SAMPLE_EL + j; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { s_f[warp] = bv; s_i[warp] = bi; }
+    __syncthreads();
+    bv = s_f[0]; bi = s_i[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w)
+        if (s_f[w] > bv || (s_f[w] == bv && s_i[w] < bi)) { bv = s_f[w]; bi = s_i[w]; }
+    __syncthreads();
+
+    int choice = bi;
+    if (top_k != 1) {
+        const float T = ctl.temperature;
+        float sc[SAMPLE_EL];
+#pragma unroll
+        for (int j = 0; j < SAMPLE_EL; ++j) sc[j] = v[j] / T;
+        const float smax = bv / T;
+        bool keep[SAMPLE_EL];
+#pragma unroll
+        for (int j = 0; j < SAMPLE_EL; ++j) keep[j] = true;
+        if (top_k > 0) {
+            // radix select of the top_k-th largest key, 8 bits per pass
+            if (tid == 0) { s_prefix = 0u; s_krem = (uint32_t)top_k; }
+            uint32_t key[SAMPLE_EL];
+#pragma unroll
+            for (int j = 0; j < SAMPLE_EL; ++j) key[j] = order_key(sc[j]);
+            for (int pass = 0; pass < 4; ++pass) {
+                const int shift = 24 - 8 * pass;
+                hist[tid] = 0u;
+                __syncthreads();
+                const uint32_t prefix = s_prefix;
+                const uint32_t pmask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+#pragma unroll
+                for (int j = 0; j < SAMPLE_EL; ++j)
+                    if ((key[j] & pmask) == prefix) atomicAdd(&hist[(key[j] >> shift) & 255u], 1u);
+                __syncthreads();
+                if (warp == 0) {
+                    // lane covers digits 255-8*lane .. 248-8*lane (descending)
+                    uint32_t c8[8], tot = 0u;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { c8[j] = hist[255 - 8 * lane - j]; tot += c8[j]; }
+                    uint32_t inc = tot;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+                        if (lane >= o) inc += t;
+                    }
+                    const uint32_t before = inc - tot, krem = s_krem;
+                    if (before < krem && krem <= inc) {
+                        uint32_t cum = before;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (cum < krem && krem <= cum + c8[j]) {
+                                s_prefix = prefix | ((uint32_t)(255 - 8 * lane - j) << shift);
+                                s_krem = krem - cum;
+                            }
+                            cum += c8[j];
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+            const uint32_t thr = s_prefix;
+#pragma unroll
+            for (int j = 0; j < SAMPLE_EL; ++j) keep[j] = key[j] >= thr;
+        }
+        float p[SAMPLE_EL], loc = 0.f;
+#pragma unroll
+        for (int j = 0; j < SAMPLE_EL; ++j) {
+            p[j] = keep[j] ? expf(sc[j] - smax) : 0.f;
+            loc += p[j];
+        }
+        // block exclusive scan of per-thread totals
+        float inc = loc;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) s_f[warp] = inc;
+        if (tid == 0) { s_pick = 0x7fffffff; s_lastkept = -1; }
+        __syncthreads();
+        float wbase = 0.f, total = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            if (w < warp) wbase += s_f[w];
+            total += s_f[w];
+        }
+        uint32_t c[4] = {(uint32_t)slot, (uint32_t)a.frame_ctr[slot], (uint32_t)a.codebook, 0u};
+        philox4x32_10(c, ctl.seed_lo, ctl.seed_hi);
+        const float u = (float)(c[0] >> 8) * (1.0f / 16777216.0f);
+        const float target = u * total;
+        float cum = wbase + inc - loc;
+        int mine = 0x7fffffff, lastk = -1;
+#pragma unroll
+        for (int j = 0; j < SAMPLE_EL; ++j) {
+            cum += p[j];
+            if (keep[j]) {
+                lastk = tid * SAMPLE_EL + j;
+                if (cum > target && mine == 0x7fffffff) mine = tid * SAMPLE_EL + j;
+            }
+        }
+        if (mine != 0x7fffffff) atomicMin(&s_pick, mine);
+        if (lastk >= 0) atomicMax(&s_lastkept, lastk);
+        __syncthreads();
+        choice = s_pick != 0x7fffffff ? s_pick : s_lastkept;
+    }
+    if (tid == 0) {
+        a.code_cur[r] = choice;
+        a.codes_out[(size_t)r * a.Q + a.out_col] = (int64_t)choice;
+        if (a.zero_from > 0)
+            for (int q = a.zero_from; q < a.Q; ++q) a.codes_out[(size_t)r * a.Q + q] = 0;
+        if (is_cb0) {
+            if (a.eos_logit && a.eos_prob) a.eos_prob[r] = 1.f / (1.f + expf(-bf2f(a.eos_logit[r])));
+            if (ctl.rep_penalty > 1.0f) {
+                float* cnt = a.rep_counts + (size_t)slot * CS;
+                int W = ctl.rep_window > REP_HIST_MAX ? REP_HIST_MAX : ctl.rep_window;
+                if (W > 0) {
+                    int head = a.rep_head[slot], filled = a.rep_filled[slot];
+                    if (head >= W) head = 0;
+                    if (filled >= W) {
+                        const int old = a.rep_hist[slot * REP_HIST_MAX + head];
+                        cnt[old] -= 1.f;
+                        filled = W;
+                    } else {
+                        filled += 1;
+                    }
+                    a.rep_hist[slot * REP_HIST_MAX + head] = choice;
+                    a.rep_head[slot] = (head + 1) % W;
+                    a.rep_filled[slot] = filled;
+                }
+                cnt[choice] += 1.f;
+            }
+        }
+        if (a.bump_frame) a.frame_ctr[slot] += 1;
+    }
+}
+
+}  // namespace vuib

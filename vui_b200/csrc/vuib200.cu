@@ -1,0 +1,627 @@
+// libvuib200: C ABI over the sm_100a decode kernels (see include/vuib200.h).
+// Host side only validates, lays out the caller's workspace and enqueues
+// kernels on the caller's stream; it never allocates device memory.
+#include "../../include/vuib200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "decode_kernels.cuh"
+
+using namespace vuib;
+
+struct WsLayout {
+    size_t flag, ctl, row_slot, row_pos, x, q, attn, act, part, counters;
+    size_t rq_x2, rq_x, rq_q, rq_act, rq_k, rq_v, rq_logits, code_cur;
+    size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
+    size_t total;
+};
+
+struct VuibEngine {
+    VuibConfig cfg;
+    VuibWeights w;
+    bool have_w, have_kv, have_rope, have_ws;
+    void* k[VUIB_MAX_LAYERS];
+    void* v[VUIB_MAX_LAYERS];
+    int32_t* seq_lens;
+    const bf16* rope;
+    unsigned char* ws;
+    WsLayout lay;
+    int R;        // rows of backbone scratch
+    int S;        // attention splits per row
+    VuibSampling samp;
+    bf16* tap_layers;
+    bf16* tap_rq;
+    long long launches;
+    char err[256];
+};
+
+static int32_t fail(VuibEngine* e, int32_t code, const char* fmt, ...) {
+    if (e) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(e->err, sizeof(e->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+static size_t align_up(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static void make_layout(VuibEngine* e) {
+    const VuibConfig& c = e->cfg;
+    WsLayout& L = e->lay;
+    const size_t R = e->R, RB = c.max_rows, d = c.d_model;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes); return o; };
+    L.flag = take(256);
+    L.ctl = take(sizeof(SamplingCtl));
+    L.row_slot = take(R * 4);
+    L.row_pos = take(R * 4);
+    L.x = take(R * d * 2);
+    L.q = take(R * (size_t)c.n_heads * HD * 2);
+    L.attn = take(R * (size_t)c.n_heads * HD * 2);
+    L.act = take(R * (size_t)c.ffn * 2);
+    L.part = take(R * (size_t)c.n_heads * e->S * PART_STRIDE * 4);
+    L.counters = take(R * (size_t)c.n_kv_heads * 4);
+    const size_t rd = c.rq_d_model;
+    L.rq_x2 = take(2 * RB * rd * 2);
+    L.rq_x = take(RB * rd * 2);
+    L.rq_q = take(2 * RB * rd * 2);
+    L.rq_act = take(2 * RB * (size_t)c.rq_ffn * 2);
+    L.rq_k = take((size_t)c.rq_n_layers * RB * c.n_quantizers * rd * 2);
+    L.rq_v = take((size_t)c.rq_n_layers * RB * c.n_quantizers * rd * 2);
+    L.rq_logits = take(RB * (size_t)c.codebook_size * 2);
+    L.code_cur = take(RB * 4);
+    L.frame_ctr = take((size_t)c.n_slots * 4);
+    L.rep_counts = take((size_t)c.n_slots * c.codebook_size * 4);
+    L.rep_hist = take((size_t)c.n_slots * REP_HIST_MAX * 4);
+    L.rep_head = take((size_t)c.n_slots * 4);
+    L.rep_filled = take((size_t)c.n_slots * 4);
+    L.total = off;
+}
+
+template <class T>
+static T* wsp(VuibEngine* e, size_t off) { return reinterpret_cast<T*>(e->ws + off); }
+
+// ---------------------------------------------------------------------------
+// GEMV launch: pick the row-tile size from M, K from the supported set.
+// ---------------------------------------------------------------------------
+template <int K, class Stage, class Epi>
+static cudaError_t launch_gemv_k(VuibEngine* e, const Stage& st, const Epi& ep, int M, int n_items,
+                                 cudaStream_t s) {
+    const int grid = (n_items + GEMV_WARPS - 1) / GEMV_WARPS;
+    e->launches++;
+    if (M <= 1) {
+        k_gemv<K, 1, Stage, Epi><<<grid, GEMV_THREADS, 1 * K * 2, s>>>(st, ep, M, n_items);
+    } else if (M <= 2) {
+        k_gemv<K, 2, Stage, Epi><<<grid, GEMV_THREADS, 2 * K * 2, s>>>(st, ep, M, n_items);
+    } else if (M <= 4) {
+        k_gemv<K, 4, Stage, Epi><<<grid, GEMV_THREADS, 4 * K * 2, s>>>(st, ep, M, n_items);
+    } else {
+        k_gemv<K, 8, Stage, Epi><<<grid, GEMV_THREADS, 8 * K * 2, s>>>(st, ep, M, n_items);
+    }
+    return cudaGetLastError();
+}
+
+#define VUIB_GEMV(Kval, ...)                                                        \
+    [&]() -> cudaError_t {                                                          \
+        switch (Kval) {                                                             \
+            case 512: return launch_gemv_k<512>(__VA_ARGS__);                       \
+            case 1024: return launch_gemv_k<1024>(__VA_ARGS__);                     \
+            case 1408: return launch_gemv_k<1408>(__VA_ARGS__);                     \
+            case 1536: return launch_gemv_k<1536>(__VA_ARGS__);                     \
+            case 3072: return launch_gemv_k<3072>(__VA_ARGS__);                     \
+            default: return cudaErrorInvalidValue;                                  \
+        }                                                                           \
+    }()
+
+#define CK(call)                                                                              \
+    do {                                                                                      \
+        cudaError_t _err = (call);                                                            \
+        if (_err != cudaSuccess)                                                              \
+            return fail(e, VUIB_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(_err));  \
+    } while (0)
+
+static bool k_supported(int K) {
+    return K == 512 || K == 1024 || K == 1408 || K == 1536 || K == 3072;
+}
+
+// ---------------------------------------------------------------------------
+// Handle lifecycle
+// ---------------------------------------------------------------------------
+extern "C" int32_t vuib_abi_version(void) { return VUIB_ABI_VERSION; }
+
+extern "C" int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out) {
+    if (!cfg || !out) return VUIB_ERR_NULL;
+    *out = nullptr;
+    const VuibConfig& c = *cfg;
+    const int G = c.n_kv_heads > 0 ? c.n_heads / c.n_kv_heads : 0;
+    const bool ok = c.head_dim == HD && c.d_model == c.n_heads * HD && c.n_kv_heads > 0 &&
+                    c.n_heads % c.n_kv_heads == 0 && (G == 1 || G == 2) &&
+                    k_supported(c.d_model) && k_supported(c.ffn) && k_supported(c.rq_d_model) &&
+                    k_supported(c.rq_ffn) && c.rq_d_model == c.rq_n_heads * HD &&
+                    c.codebook_size == SAMPLE_THREADS * SAMPLE_EL && c.n_quantizers >= 2 &&
+                    c.n_quantizers <= 32 && c.n_layers >= 1 && c.n_layers <= VUIB_MAX_LAYERS &&
+                    c.rq_n_layers >= 1 && c.rq_n_layers <= VUIB_MAX_LAYERS;
+    if (!ok) return VUIB_ERR_SHAPE;
+    if (c.n_slots < 1 || c.max_seq < 1 || c.max_rows < 1 || c.max_prefill_rows < 1)
+        return VUIB_ERR_RANGE;
+    VuibEngine* e = new (std::nothrow) VuibEngine();
+    if (!e) return VUIB_ERR_NULL;
+    memset(e, 0, sizeof(*e));
+    e->cfg = c;
+    e->R = c.max_rows > c.max_prefill_rows ? c.max_rows : c.max_prefill_rows;
+    e->S = (c.max_seq + ATT_SPLIT - 1) / ATT_SPLIT;
+    e->samp.temperature = 1.0f;
+    e->samp.top_k_cb0 = 1;
+    e->samp.top_k_rq = 1;
+    e->samp.rep_penalty = 1.0f;
+    make_layout(e);
+    *out = e;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_destroy(VuibEngine* e) {
+    delete e;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_last_error(VuibEngine* e, char* buf, size_t n) {
+    if (!e || !buf || n == 0) return VUIB_ERR_NULL;
+    strncpy(buf, e->err, n - 1);
+    buf[n - 1] = 0;
+    return VUIB_OK;
+}
+
+extern "C" int64_t vuib_launch_count(VuibEngine* e) { return e ? e->launches : 0; }
+
+extern "C" int32_t vuib_workspace_bytes(VuibEngine* e, size_t* bytes) {
+    if (!e || !bytes) return VUIB_ERR_NULL;
+    *bytes = e->lay.total;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_bind_workspace(VuibEngine* e, void* dev, size_t bytes) {
+    if (!e || !dev) return VUIB_ERR_NULL;
+    if (bytes < e->lay.total || ((uintptr_t)dev & 255))
+        return fail(e, VUIB_ERR_WORKSPACE, "workspace needs %zu bytes, 256-byte aligned; got %zu at %p",
+                    e->lay.total, bytes, dev);
+    e->ws = static_cast<unsigned char*>(dev);
+    e->have_ws = true;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
+    if (!e || !w) return VUIB_ERR_NULL;
+    const VuibConfig& c = e->cfg;
+    bool ok = w->audio_emb && w->codec_head && w->eos_w && w->eos_b && w->final_norm &&
+              w->rq_backbone_proj && w->rq_code_emb && w->rq_pos_emb && w->rq_head && w->rq_norm;
+    for (int i = 0; i < c.n_layers; ++i)
+        ok = ok && w->attn_norm[i] && w->wqkv[i] && w->out_proj[i] && w->mlp_norm[i] && w->w1[i] &&
+             w->w3[i] && w->w2[i];
+    for (int i = 0; i < c.rq_n_layers; ++i)
+        ok = ok && w->rq_attn_norm[i] && w->rq_wqkv[i] && w->rq_out_proj[i] && w->rq_mlp_norm[i] &&
+             w->rq_w1[i] && w->rq_w3[i] && w->rq_w2[i];
+    if (!ok) return fail(e, VUIB_ERR_NULL, "a weight pointer is NULL");
+    e->w = *w;
+    e->have_w = true;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* v_dev,
+                                int32_t* seq_lens_dev) {
+    if (!e || !k_dev || !v_dev || !seq_lens_dev) return VUIB_ERR_NULL;
+    for (int i = 0; i < e->cfg.n_layers; ++i) {
+        if (!k_dev[i] || !v_dev[i]) return fail(e, VUIB_ERR_NULL, "KV pointer of layer %d is NULL", i);
+        e->k[i] = k_dev[i];
+        e->v[i] = v_dev[i];
+    }
+    e->seq_lens = seq_lens_dev;
+    e->have_kv = true;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_bind_rope(VuibEngine* e, const void* freqs_cis_dev) {
+    if (!e || !freqs_cis_dev) return VUIB_ERR_NULL;
+    e->rope = static_cast<const bf16*>(freqs_cis_dev);
+    e->have_rope = true;
+    return VUIB_OK;
+}
+
+static int32_t ready(VuibEngine* e) {
+    if (!e) return VUIB_ERR_NULL;
+    if (!(e->have_w && e->have_kv && e->have_rope && e->have_ws))
+        return fail(e, VUIB_ERR_UNBOUND, "bind weights, kv, rope table and workspace first");
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_set_sampling(VuibEngine* e, const VuibSampling* s, void* stream) {
+    if (!e || !s) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    if (!(s->temperature > 0.f)) return fail(e, VUIB_ERR_RANGE, "temperature must be > 0");
+    if (s->n_codebooks < 0 || s->n_codebooks == 1 || s->n_codebooks > e->cfg.n_quantizers)
+        return fail(e, VUIB_ERR_RANGE, "n_codebooks must be 0 or in [2, %d]", e->cfg.n_quantizers);
+    if (s->rep_window < 0 || s->rep_window > REP_HIST_MAX)
+        return fail(e, VUIB_ERR_RANGE, "rep_window must be in [0, %d]", REP_HIST_MAX);
+    e->samp = *s;
+    SamplingCtl ctl;
+    ctl.temperature = s->temperature;
+    ctl.top_k_cb0 = s->top_k_cb0;
+    ctl.top_k_rq = s->top_k_rq;
+    ctl.rep_penalty = s->rep_penalty;
+    ctl.rep_window = s->rep_window;
+    ctl.n_codebooks = s->n_codebooks;
+    ctl.seed_lo = (uint32_t)(s->seed & 0xffffffffu);
+    ctl.seed_hi = (uint32_t)(s->seed >> 32);
+    CK(cudaMemcpyAsync(e->ws + e->lay.ctl, &ctl, sizeof(ctl), cudaMemcpyHostToDevice,
+                       static_cast<cudaStream_t>(stream)));
+    // the source is a stack object: make sure the copy has read it before returning
+    CK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_set_taps(VuibEngine* e, void* layer_hidden_dev, void* rq_logits_dev) {
+    if (!e) return VUIB_ERR_NULL;
+    e->tap_layers = static_cast<bf16*>(layer_hidden_dev);
+    e->tap_rq = static_cast<bf16*>(rq_logits_dev);
+    return VUIB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Backbone: 24 blocks over M rows whose (slot, position) are in the workspace.
+// ---------------------------------------------------------------------------
+static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    bf16* x = wsp<bf16>(e, L.x);
+    bf16* q = wsp<bf16>(e, L.q);
+    bf16* attn = wsp<bf16>(e, L.attn);
+    bf16* act = wsp<bf16>(e, L.act);
+    const int32_t* row_slot = wsp<int32_t>(e, L.row_slot);
+    const int32_t* row_pos = wsp<int32_t>(e, L.row_pos);
+    const int d = c.d_model, qc = c.n_heads * HD, kvc = c.n_kv_heads * HD;
+    for (int li = 0; li < c.n_layers; ++li) {
+        StageNorm sn{x, static_cast<const bf16*>(e->w.attn_norm[li]), c.norm_eps, 1, 0};
+        EpiQkv eq{static_cast<const bf16*>(e->w.wqkv[li]), d, q, qc, kvc,
+                  static_cast<bf16*>(e->k[li]), static_cast<bf16*>(e->v[li]),
+                  row_slot, row_pos, c.max_seq, e->rope, 1, 0};
+        CK(VUIB_GEMV(d, e, sn, eq, M, (qc + 2 * kvc) / 2, s));
+
+        AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
+                    row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
+                    c.n_heads, c.n_kv_heads, c.max_seq, e->S};
+        k_attn_decode<<<dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s>>>(aa);
+        e->launches++;
+        CK(cudaGetLastError());
+
+        StageCopy sc{attn};
+        EpiResidual eo{static_cast<const bf16*>(e->w.out_proj[li]), qc, x, d, nullptr};
+        CK(VUIB_GEMV(qc, e, sc, eo, M, d, s));
+
+        StageNorm sm{x, static_cast<const bf16*>(e->w.mlp_norm[li]), c.norm_eps, 1, 0};
+        EpiSwiGLU eg{static_cast<const bf16*>(e->w.w1[li]), static_cast<const bf16*>(e->w.w3[li]), d,
+                     act, c.ffn};
+        CK(VUIB_GEMV(d, e, sm, eg, M, c.ffn, s));
+
+        StageCopy sa{act};
+        bf16* tap = (e->tap_layers && M <= c.max_rows)
+                        ? e->tap_layers + (size_t)li * c.max_rows * d : nullptr;
+        EpiResidual ew{static_cast<const bf16*>(e->w.w2[li]), c.ffn, x, d, tap};
+        CK(VUIB_GEMV(c.ffn, e, sa, ew, M, d, s));
+    }
+    return VUIB_OK;
+}
+
+static int32_t run_heads(VuibEngine* e, int B, const bf16* hidden, bf16* cb0, bf16* eos,
+                         cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    StageCopy sc{hidden};
+    EpiLogits el{static_cast<const bf16*>(e->w.codec_head), c.d_model, c.codebook_size, cb0,
+                 static_cast<const bf16*>(e->w.eos_w), static_cast<const bf16*>(e->w.eos_b), eos,
+                 nullptr, 0};
+    CK(VUIB_GEMV(c.d_model, e, sc, el, B, c.codebook_size + 1, s));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* row_slot_dev,
+                                const int32_t* row_pos_dev, const void* emb_dev,
+                                void* hidden_out_dev, void* stream) {
+    int32_t rc = ready(e);
+    if (rc) return rc;
+    if (!row_slot_dev || !row_pos_dev || !emb_dev || !hidden_out_dev) return VUIB_ERR_NULL;
+    if (n_rows < 1 || n_rows > e->cfg.max_prefill_rows)
+        return fail(e, VUIB_ERR_RANGE, "n_rows %d outside [1, %d]", n_rows, e->cfg.max_prefill_rows);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const WsLayout& L = e->lay;
+    const int d = e->cfg.d_model;
+    CK(cudaMemcpyAsync(e->ws + L.row_slot, row_slot_dev, (size_t)n_rows * 4, cudaMemcpyDeviceToDevice, s));
+    CK(cudaMemcpyAsync(e->ws + L.row_pos, row_pos_dev, (size_t)n_rows * 4, cudaMemcpyDeviceToDevice, s));
+    CK(cudaMemcpyAsync(e->ws + L.x, emb_dev, (size_t)n_rows * d * 2, cudaMemcpyDeviceToDevice, s));
+    rc = run_layers(e, n_rows, s);
+    if (rc) return rc;
+    k_final_norm<<<n_rows, 128, 0, s>>>(wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
+                                        e->cfg.norm_eps, static_cast<bf16*>(hidden_out_dev), d,
+                                        nullptr, nullptr, nullptr, 0);
+    e->launches++;
+    CK(cudaGetLastError());
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_backbone_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                                      const int32_t* seq_inc_dev, const int64_t* codes_in_dev,
+                                      void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
+                                      void* stream) {
+    int32_t rc = ready(e);
+    if (rc) return rc;
+    if (!slots_dev || !codes_in_dev || !hidden_out_dev || !cb0_out_dev || !eos_out_dev)
+        return VUIB_ERR_NULL;
+    if (B < 1 || B > e->cfg.max_rows)
+        return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    k_embed_codes<<<B, 128, 0, s>>>(codes_in_dev, slots_dev, e->seq_lens,
+                                    static_cast<const bf16*>(e->w.audio_emb), wsp<bf16>(e, L.x),
+                                    wsp<int32_t>(e, L.row_slot), wsp<int32_t>(e, L.row_pos), c.d_model,
+                                    c.n_quantizers, c.codebook_size, c.n_slots, c.max_seq,
+                                    wsp<int32_t>(e, L.flag));
+    e->launches++;
+    CK(cudaGetLastError());
+    rc = run_layers(e, B, s);
+    if (rc) return rc;
+    k_final_norm<<<B, 128, 0, s>>>(wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
+                                   c.norm_eps, static_cast<bf16*>(hidden_out_dev), c.d_model,
+                                   wsp<int32_t>(e, L.row_slot), seq_inc_dev, e->seq_lens, 1);
+    e->launches++;
+    CK(cudaGetLastError());
+    return run_heads(e, B, static_cast<const bf16*>(hidden_out_dev), static_cast<bf16*>(cb0_out_dev),
+                     static_cast<bf16*>(eos_out_dev), s);
+}
+
+extern "C" int32_t vuib_heads(VuibEngine* e, int32_t B, const void* hidden_dev, void* cb0_out_dev,
+                              void* eos_out_dev, void* stream) {
+    int32_t rc = ready(e);
+    if (rc) return rc;
+    if (!hidden_dev || !cb0_out_dev || !eos_out_dev) return VUIB_ERR_NULL;
+    if (B < 1 || B > e->cfg.max_rows)
+        return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    return run_heads(e, B, static_cast<const bf16*>(hidden_dev), static_cast<bf16*>(cb0_out_dev),
+                     static_cast<bf16*>(eos_out_dev), static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Depth step
+// ---------------------------------------------------------------------------
+static int32_t rq_layers(VuibEngine* e, int M, bf16* x, int rows_per_b, int pos_base,
+                         cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    const int rd = c.rq_d_model, Q = c.n_quantizers;
+    bf16* q = wsp<bf16>(e, L.rq_q);
+    bf16* act = wsp<bf16>(e, L.rq_act);
+    const size_t layer_kv = (size_t)c.max_rows * Q * rd;
+    for (int li = 0; li < c.rq_n_layers; ++li) {
+        bf16* kc = wsp<bf16>(e, L.rq_k) + li * layer_kv;
+        bf16* vc = wsp<bf16>(e, L.rq_v) + li * layer_kv;
+        StageNorm sn{x, static_cast<const bf16*>(e->w.rq_attn_norm[li]), c.rq_norm_eps, 1, 0};
+        EpiQkv eq{static_cast<const bf16*>(e->w.rq_wqkv[li]), rd, q, rd, rd, kc, vc,
+                  nullptr, nullptr, Q, nullptr, rows_per_b, pos_base};
+        CK(VUIB_GEMV(rd, e, sn, eq, M, 3 * rd / 2, s));
+
+        StageRqAttn sa{q, kc, vc, c.rq_n_heads, Q, rows_per_b, pos_base};
+        EpiResidual eo{static_cast<const bf16*>(e->w.rq_out_proj[li]), rd, x, rd, nullptr};
+        CK(VUIB_GEMV(rd, e, sa, eo, M, rd, s));
+
+        StageNorm sm{x, static_cast<const bf16*>(e->w.rq_mlp_norm[li]), c.rq_norm_eps, 1, 0};
+        EpiSwiGLU eg{static_cast<const bf16*>(e->w.rq_w1[li]), static_cast<const bf16*>(e->w.rq_w3[li]),
+                     rd, act, c.rq_ffn};
+        CK(VUIB_GEMV(rd, e, sm, eg, M, c.rq_ffn, s));
+
+        StageCopy sc{act};
+        EpiResidual ew{static_cast<const bf16*>(e->w.rq_w2[li]), c.rq_ffn, x, rd, nullptr};
+        CK(VUIB_GEMV(c.rq_ffn, e, sc, ew, M, rd, s));
+    }
+    return VUIB_OK;
+}
+
+static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16* hidden,
+                         const bf16* cb0_logits, const bf16* eos_logit, int first_frame,
+                         int64_t* codes_out, float* eos_prob, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    const int Q = c.n_quantizers, CS = c.codebook_size, rd = c.rq_d_model;
+    const int Qn = e->samp.n_codebooks > 0 ? e->samp.n_codebooks : Q;
+    int32_t* code_cur = wsp<int32_t>(e, L.code_cur);
+    SampleArgs sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.ctl = wsp<SamplingCtl>(e, L.ctl);
+    sa.slots = slots;
+    sa.frame_ctr = wsp<int32_t>(e, L.frame_ctr);
+    sa.rep_counts = wsp<float>(e, L.rep_counts);
+    sa.rep_hist = wsp<int32_t>(e, L.rep_hist);
+    sa.rep_head = wsp<int32_t>(e, L.rep_head);
+    sa.rep_filled = wsp<int32_t>(e, L.rep_filled);
+    sa.code_cur = code_cur;
+    sa.codes_out = codes_out;
+    sa.Q = Q;
+
+    // cb0
+    sa.logits = cb0_logits;
+    sa.stride = CS;
+    sa.codebook = 0;
+    sa.out_col = 0;
+    sa.first_frame = first_frame;
+    sa.eos_logit = eos_logit;
+    sa.eos_prob = eos_prob;
+    sa.bump_frame = 0;
+    sa.zero_from = Qn < Q ? Qn : 0;
+    k_sample<<<B, SAMPLE_THREADS, 0, s>>>(sa);
+    e->launches++;
+    CK(cudaGetLastError());
+    sa.eos_logit = nullptr;
+    sa.eos_prob = nullptr;
+    sa.first_frame = 0;
+    sa.zero_from = 0;
+
+    // depth positions 0 (projected hidden) and 1 (code 0): rows 2b, 2b+1
+    bf16* x2 = wsp<bf16>(e, L.rq_x2);
+    bf16* x1 = wsp<bf16>(e, L.rq_x);
+    const bf16* pos_emb = static_cast<const bf16*>(e->w.rq_pos_emb);
+    const bf16* code_emb = static_cast<const bf16*>(e->w.rq_code_emb);
+    {
+        StageCopy sc{hidden};
+        EpiProjPos ep{static_cast<const bf16*>(e->w.rq_backbone_proj), c.d_model, pos_emb, x2, rd, 2};
+        CK(VUIB_GEMV(c.d_model, e, sc, ep, B, rd, s));
+    }
+    k_rq_embed<<<B, 64, 0, s>>>(code_cur, code_emb, pos_emb, x2, rd, CS, 1, 2, 1);
+    e->launches++;
+    CK(cudaGetLastError());
+    int32_t rc = rq_layers(e, 2 * B, x2, 2, 0, s);
+    if (rc) return rc;
+
+    bf16* logits = wsp<bf16>(e, L.rq_logits);
+    const bf16* head = static_cast<const bf16*>(e->w.rq_head);
+    for (int i = 0; i < Qn - 1; ++i) {
+        if (i > 0) {
+            k_rq_embed<<<B, 64, 0, s>>>(code_cur, code_emb, pos_emb, x1, rd, CS, i + 1, 1, 0);
+            e->launches++;
+            CK(cudaGetLastError());
+            rc = rq_layers(e, B, x1, 1, i + 1, s);
+            if (rc) return rc;
+        }
+        StageNorm sn{i == 0 ? x2 : x1, static_cast<const bf16*>(e->w.rq_norm), c.rq_norm_eps,
+                     i == 0 ? 2 : 1, i == 0 ? 1 : 0};
+        EpiLogits el{head + (size_t)i * CS * rd, rd, CS, logits, nullptr, nullptr, nullptr,
+                     e->tap_rq ? e->tap_rq + (size_t)i * CS : nullptr, (Q - 1) * CS};
+        CK(VUIB_GEMV(rd, e, sn, el, B, CS, s));
+        sa.logits = logits;
+        sa.codebook = i + 1;
+        sa.out_col = i + 1;
+        sa.bump_frame = (i == Qn - 2);
+        k_sample<<<B, SAMPLE_THREADS, 0, s>>>(sa);
+        e->launches++;
+        CK(cudaGetLastError());
+    }
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                                   const void* hidden_dev, const void* cb0_logits_dev,
+                                   const void* eos_logit_dev, int32_t first_frame,
+                                   int64_t* codes_out_dev, float* eos_prob_out_dev, void* stream) {
+    int32_t rc = ready(e);
+    if (rc) return rc;
+    if (!slots_dev || !hidden_dev || !cb0_logits_dev || !codes_out_dev) return VUIB_ERR_NULL;
+    if (B < 1 || B > e->cfg.max_rows)
+        return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_dev),
+                     static_cast<const bf16*>(cb0_logits_dev), static_cast<const bf16*>(eos_logit_dev),
+                     first_frame, codes_out_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                                     const int32_t* seq_inc_dev, int64_t* codes_io_dev,
+                                     void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
+                                     float* eos_prob_out_dev, void* stream) {
+    int32_t rc = vuib_backbone_step(e, B, slots_dev, seq_inc_dev, codes_io_dev, hidden_out_dev,
+                                    cb0_out_dev, eos_out_dev, stream);
+    if (rc) return rc;
+    return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
+                     static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
+                     codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t vuib_embed_codes(VuibEngine* e, int32_t n_rows, const int64_t* codes_dev,
+                                    void* out_dev, void* stream) {
+    if (!e || !codes_dev || !out_dev) return VUIB_ERR_NULL;
+    if (!e->have_w || !e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind weights and workspace first");
+    if (n_rows < 1) return fail(e, VUIB_ERR_RANGE, "n_rows %d < 1", n_rows);
+    const VuibConfig& c = e->cfg;
+    k_embed_codes<<<n_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        codes_dev, nullptr, nullptr, static_cast<const bf16*>(e->w.audio_emb), static_cast<bf16*>(out_dev),
+        nullptr, nullptr, c.d_model, c.n_quantizers, c.codebook_size, c.n_slots, c.max_seq,
+        wsp<int32_t>(e, e->lay.flag));
+    e->launches++;
+    CK(cudaGetLastError());
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_sample_rows(VuibEngine* e, int32_t B, const int32_t* slots_dev,
+                                    const void* logits_dev, int32_t codebook, int64_t* codes_out_dev,
+                                    void* stream) {
+    if (!e || !slots_dev || !logits_dev || !codes_out_dev) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    if (B < 1 || B > e->cfg.max_rows) return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    if (codebook < 0 || codebook >= e->cfg.n_quantizers) return fail(e, VUIB_ERR_RANGE, "codebook %d", codebook);
+    const WsLayout& L = e->lay;
+    SampleArgs sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.logits = static_cast<const bf16*>(logits_dev);
+    sa.stride = e->cfg.codebook_size;
+    sa.ctl = wsp<SamplingCtl>(e, L.ctl);
+    sa.slots = slots_dev;
+    sa.frame_ctr = wsp<int32_t>(e, L.frame_ctr);
+    sa.codebook = codebook;
+    sa.rep_counts = wsp<float>(e, L.rep_counts);
+    sa.rep_hist = wsp<int32_t>(e, L.rep_hist);
+    sa.rep_head = wsp<int32_t>(e, L.rep_head);
+    sa.rep_filled = wsp<int32_t>(e, L.rep_filled);
+    sa.code_cur = wsp<int32_t>(e, L.code_cur);
+    sa.codes_out = codes_out_dev;
+    sa.Q = 1;
+    sa.out_col = 0;
+    sa.bump_frame = 1;
+    k_sample<<<B, SAMPLE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(sa);
+    e->launches++;
+    CK(cudaGetLastError());
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream) {
+    if (!e) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    const VuibConfig& c = e->cfg;
+    if (slot < -1 || slot >= c.n_slots) return fail(e, VUIB_ERR_RANGE, "slot %d out of range", slot);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const WsLayout& L = e->lay;
+    const size_t first = slot < 0 ? 0 : slot, n = slot < 0 ? c.n_slots : 1;
+    CK(cudaMemsetAsync(e->ws + L.rep_counts + first * c.codebook_size * 4, 0, n * c.codebook_size * 4, s));
+    CK(cudaMemsetAsync(e->ws + L.rep_hist + first * REP_HIST_MAX * 4, 0, n * REP_HIST_MAX * 4, s));
+    CK(cudaMemsetAsync(e->ws + L.rep_head + first * 4, 0, n * 4, s));
+    CK(cudaMemsetAsync(e->ws + L.rep_filled + first * 4, 0, n * 4, s));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len) {
+    if (!e) return VUIB_ERR_NULL;
+    if (!e->have_kv) return fail(e, VUIB_ERR_UNBOUND, "bind kv first");
+    if (slot < 0 || slot >= e->cfg.n_slots || len < 0 || len > e->cfg.max_seq)
+        return fail(e, VUIB_ERR_RANGE, "slot %d / len %d out of range", slot, len);
+    CK(cudaMemcpy(e->seq_lens + slot, &len, 4, cudaMemcpyHostToDevice));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_get_seq_len(VuibEngine* e, int32_t slot, int32_t* len) {
+    if (!e || !len) return VUIB_ERR_NULL;
+    if (!e->have_kv) return fail(e, VUIB_ERR_UNBOUND, "bind kv first");
+    if (slot < 0 || slot >= e->cfg.n_slots) return fail(e, VUIB_ERR_RANGE, "slot %d out of range", slot);
+    CK(cudaMemcpy(len, e->seq_lens + slot, 4, cudaMemcpyDeviceToHost));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_check_device_flag(VuibEngine* e, void* stream) {
+    if (!e) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int32_t flag = 0;
+    CK(cudaMemcpyAsync(&flag, e->ws + e->lay.flag, 4, cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    if (flag) {
+        CK(cudaMemsetAsync(e->ws + e->lay.flag, 0, 4, s));
+        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code)", flag);
+    }
+    return VUIB_OK;
+}
