@@ -179,6 +179,16 @@ int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* slots_dev,
                           void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
                           float* eos_prob_out_dev, void* stream);
 
+/* Decode attention alone over layer `layer` of the bound KV cache: the device work of the
+ * flash_attn_with_kvcache call (MHA.forward_flash, model.py:247-257) minus the append, which
+ * the QKV kernel has already done.  Row r attends keys [0, row_pos[r]] of slot row_slot[r];
+ * GQA (n_heads / n_kv_heads query heads per KV head), scale 1/sqrt(head_dim), fp32 softmax.
+ *  q, out: (n_rows, n_heads*head_dim) bf16, q with RoPE applied; n_rows <= max(max_rows,
+ *  max_prefill_rows).  Uses the bound workspace for its split-KV partial results. */
+int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, const void* q_dev,
+                       const int32_t* row_slot_dev, const int32_t* row_pos_dev, void* out_dev,
+                       void* stream);
+
 /* Gather-sum of codec codes alone: out[r] = sum_q audio_emb[q*CS + codes[r,q]]
  * (AudioEmbedding.forward, model.py:559-563; Engine._audio_emb, engine.py:705-709).
  * codes: int64 (n_rows, Q); out: bf16 (n_rows, d).  Feeds a prefill of audio frames. */

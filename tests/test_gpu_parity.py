@@ -149,6 +149,39 @@ def test_per_layer_hidden_vs_oracle(eng1, oracle_gpu, oracle_fp32):
     row.close()
 
 
+def _ref_attention(q, k_cache, v_cache, slot, pos):
+    """fp32 softmax attention of one row: q (16, 64), caches (slots, S, 8, 64)."""
+    k = k_cache[slot, : pos + 1].float().repeat_interleave(2, dim=1)  # (T, 16, 64)
+    v = v_cache[slot, : pos + 1].float().repeat_interleave(2, dim=1)
+    s = torch.einsum("hd,thd->ht", q.float(), k) * 0.125
+    return torch.einsum("ht,thd->hd", torch.softmax(s, dim=-1), v)
+
+
+def test_attention_kernel_ragged(eng8):
+    """The attention kernel alone on random K/V: one key, a partial split, exact split boundaries,
+    several splits, two rows on one slot; against fp32 softmax attention."""
+    eng = eng8
+    g = torch.Generator().manual_seed(7)
+    layer = 5
+    kv = eng.model.decoder.flash_kv_caches[layer]
+    saved = (kv.k_cache.clone(), kv.v_cache.clone())
+    kv.k_cache.copy_(torch.randn(kv.k_cache.shape, generator=g).to(torch.bfloat16))
+    kv.v_cache.copy_(torch.randn(kv.v_cache.shape, generator=g).to(torch.bfloat16))
+    slots = torch.tensor([0, 1, 2, 3, 4, 4, 7, 8])
+    pos = torch.tensor([0, 5, 127, 128, 300, 301, 639, 255])
+    q = torch.randn(8, 1024, generator=g).to(torch.bfloat16)
+    out = eng._attention(layer, q, slots, pos).float().cpu()
+    out2 = eng._attention(layer, q, slots, pos).float().cpu()
+    assert torch.equal(out, out2)  # split merge order is fixed: bitwise repeatable
+    kc, vc = kv.k_cache.cpu(), kv.v_cache.cpu()
+    for r in range(8):
+        ref = _ref_attention(q[r].view(16, 64), kc, vc, int(slots[r]), int(pos[r])).reshape(-1)
+        err = (out[r] - ref).abs().max().item()
+        assert err <= 2.0 ** -8 * max(1.0, ref.abs().max().item()) + 1e-3, (r, err)
+    kv.k_cache.copy_(saved[0])
+    kv.v_cache.copy_(saved[1])
+
+
 def _greedy_engine(eng, ids, n_frames):
     eng.reset()
     row = eng.new_row()

@@ -83,6 +83,7 @@ SYMBOLS = {
     "vuib_heads": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P]),
     "vuib_depth_step": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, C.c_int32, _P, _P, _P]),
     "vuib_decode_frame": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "vuib_attention": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "vuib_embed_codes": (C.c_int32, [_P, C.c_int32, _P, _P, _P]),
     "vuib_sample_rows": (C.c_int32, [_P, C.c_int32, _P, _P, C.c_int32, _P, _P]),
     "vuib_rep_reset": (C.c_int32, [_P, C.c_int32, _P]),

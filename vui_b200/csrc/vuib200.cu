@@ -534,6 +534,24 @@ extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* sl
                      codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, const void* q_dev,
+                                  const int32_t* row_slot_dev, const int32_t* row_pos_dev,
+                                  void* out_dev, void* stream) {
+    if (!e || !q_dev || !row_slot_dev || !row_pos_dev || !out_dev) return VUIB_ERR_NULL;
+    if (!e->have_kv || !e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind kv and workspace first");
+    const VuibConfig& c = e->cfg;
+    if (layer < 0 || layer >= c.n_layers) return fail(e, VUIB_ERR_RANGE, "layer %d out of range", layer);
+    if (n_rows < 1 || n_rows > e->R) return fail(e, VUIB_ERR_RANGE, "n_rows %d outside [1, %d]", n_rows, e->R);
+    AttnArgs aa{static_cast<const bf16*>(q_dev), static_cast<const bf16*>(e->k[layer]),
+                static_cast<const bf16*>(e->v[layer]), row_slot_dev, row_pos_dev,
+                wsp<float>(e, e->lay.part), wsp<int32_t>(e, e->lay.counters), static_cast<bf16*>(out_dev),
+                c.n_heads, c.n_kv_heads, c.max_seq, e->S};
+    k_attn_decode<<<dim3(e->S, c.n_kv_heads, n_rows), ATT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(aa);
+    e->launches++;
+    CK(cudaGetLastError());
+    return VUIB_OK;
+}
+
 extern "C" int32_t vuib_embed_codes(VuibEngine* e, int32_t n_rows, const int64_t* codes_dev,
                                     void* out_dev, void* stream) {
     if (!e || !codes_dev || !out_dev) return VUIB_ERR_NULL;

@@ -553,6 +553,17 @@ class Engine:
         P = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
         self._ck(self._lib.vuib_set_taps(self._handle, P(layer_hidden), P(rq_logits)))
 
+    def _attention(self, layer: int, q: Tensor, row_slot: Tensor, row_pos: Tensor) -> Tensor:
+        """Decode attention of one layer over the engine's KV cache: q (n, H*hd) bf16 with RoPE
+        applied, row r attends keys [0, row_pos[r]] of slot row_slot[r]."""
+        q = q.to(self.device, self.dtype).contiguous()
+        rs = row_slot.to(self.device, torch.int32).contiguous()
+        rp = row_pos.to(self.device, torch.int32).contiguous()
+        out = torch.empty_like(q)
+        P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        self._ck(self._lib.vuib_attention(self._handle, layer, q.shape[0], P(q), P(rs), P(rp), P(out), self._stream))
+        return out
+
     def _sample_rows(self, logits: Tensor, n_draws: int, cb0: bool = False) -> Tensor:
         """Draw n_draws times per row from logits (B, CS); returns (n_draws, B) on the host."""
         B = logits.shape[0]
