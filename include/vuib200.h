@@ -189,6 +189,27 @@ int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, const void*
                        const int32_t* row_slot_dev, const int32_t* row_pos_dev, void* out_dev,
                        void* stream);
 
+/* vuib_attention for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference; it exists for hosts of this library that may not call cudaMalloc: a real-time
+ * audio thread that must never wait on the driver's allocator, or a plug-in inside a server
+ * that owns all device memory through its own pool.  It needs no handle and no workspace: the
+ * split-KV partial results live in a fixed array inside the library (about 529 KB, held by every
+ * GPU that loads the library until the process exits), and it calls neither cudaMalloc nor
+ * cudaFree nor any allocating routine.
+ *  Limits: n_rows <= 8, max_seq <= 2048, n_heads <= 16 with 1 or 2 query heads per kv head,
+ *  head_dim 64.  Larger sizes return VUIB_ERR_RANGE with the reason in `err`.
+ *  k_cache / v_cache: (slots, max_seq, n_kv_heads, 64) bf16 of ONE layer; q, out: (n_rows,
+ *  n_heads*64) bf16; row r attends keys [0, row_pos[r]] of slot row_slot[r].
+ *  The first call on a device looks up the array's device address (cudaGetSymbolAddress), so
+ *  make that call before starting any stream capture.  All calls share the one array: it keeps
+ *  the last call's contents (the call clears what it needs zeroed), and two calls that overlap
+ *  on the GPU (different streams) race; keep them on one stream or order them.
+ *  err / err_len: optional buffer for the error text. */
+int32_t vuib_attention_noalloc(int32_t n_heads, int32_t n_kv_heads, int32_t max_seq, int32_t n_rows,
+                               const void* q_dev, const void* k_cache_dev, const void* v_cache_dev,
+                               const int32_t* row_slot_dev, const int32_t* row_pos_dev, void* out_dev,
+                               void* stream, char* err, size_t err_len);
+
 /* Gather-sum of codec codes alone: out[r] = sum_q audio_emb[q*CS + codes[r,q]]
  * (AudioEmbedding.forward, model.py:559-563; Engine._audio_emb, engine.py:705-709).
  * codes: int64 (n_rows, Q); out: bf16 (n_rows, d).  Feeds a prefill of audio frames. */

@@ -84,6 +84,8 @@ SYMBOLS = {
     "vuib_depth_step": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, C.c_int32, _P, _P, _P]),
     "vuib_decode_frame": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P, _P, _P, _P]),
     "vuib_attention": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
+    "vuib_attention_noalloc": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P,
+                                           C.c_char_p, C.c_size_t]),
     "vuib_embed_codes": (C.c_int32, [_P, C.c_int32, _P, _P, _P]),
     "vuib_sample_rows": (C.c_int32, [_P, C.c_int32, _P, _P, C.c_int32, _P, _P]),
     "vuib_rep_reset": (C.c_int32, [_P, C.c_int32, _P]),

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "decode_kernels.cuh"
@@ -641,5 +642,98 @@ extern "C" int32_t vuib_check_device_flag(VuibEngine* e, void* stream) {
         CK(cudaMemsetAsync(e->ws + e->lay.flag, 0, 4, s));
         return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code)", flag);
     }
+    return VUIB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// A real-time audio thread cannot afford to block on the driver's allocator
+// lock, and a plug-in inside a serving process that has already handed all
+// device memory to its own pool may be forbidden to call cudaMalloc at all.
+// Such callers cannot create the workspace the handle-based API needs, so this
+// entry point keeps the split-KV partial results and the per-(row, kv head)
+// arrival counters in a fixed array that is part of the loaded module.  Every
+// GPU that loads the library holds these ~529 KB until the process exits.
+//
+// In host code `g_na_scratch` is only a stand-in for the symbol, not a device
+// address, so the address the kernel gets comes from cudaGetSymbolAddress, asked
+// once per device (with that device current) on the first call there.
+// ---------------------------------------------------------------------------
+#define VUIB_NA_MAX_ROWS 8
+#define VUIB_NA_MAX_HEADS 16
+#define VUIB_NA_MAX_SEQ 2048
+#define VUIB_NA_MAX_DEVICES 64
+constexpr size_t NA_PART_BYTES = (size_t)VUIB_NA_MAX_ROWS * VUIB_NA_MAX_HEADS *
+                                 (VUIB_NA_MAX_SEQ / ATT_SPLIT) * PART_STRIDE * sizeof(float);
+constexpr size_t NA_COUNTER_BYTES = (size_t)VUIB_NA_MAX_ROWS * VUIB_NA_MAX_HEADS * sizeof(int32_t);
+static_assert(NA_PART_BYTES % 256 == 0, "counter block must stay 256-byte aligned");
+
+static __device__ __align__(256) unsigned char g_na_scratch[NA_PART_BYTES + NA_COUNTER_BYTES];
+
+static std::mutex g_na_mutex;
+static void* g_na_dev_ptr[VUIB_NA_MAX_DEVICES];  // per device: address of g_na_scratch there
+
+static int32_t na_fail(char* err, size_t n, int32_t code, const char* fmt, ...) {
+    if (err && n) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, n, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+extern "C" int32_t vuib_attention_noalloc(int32_t n_heads, int32_t n_kv_heads, int32_t max_seq,
+                                          int32_t n_rows, const void* q_dev, const void* k_cache_dev,
+                                          const void* v_cache_dev, const int32_t* row_slot_dev,
+                                          const int32_t* row_pos_dev, void* out_dev, void* stream,
+                                          char* err, size_t err_len) {
+    if (err && err_len) err[0] = 0;
+    if (!q_dev || !k_cache_dev || !v_cache_dev || !row_slot_dev || !row_pos_dev || !out_dev)
+        return na_fail(err, err_len, VUIB_ERR_NULL, "a required pointer is NULL");
+    if (n_rows < 1 || n_rows > VUIB_NA_MAX_ROWS)
+        return na_fail(err, err_len, VUIB_ERR_RANGE, "n_rows %d outside [1, %d]: the built-in scratch holds "
+                       "%d rows; use vuib_attention with a workspace for more", n_rows, VUIB_NA_MAX_ROWS,
+                       VUIB_NA_MAX_ROWS);
+    if (max_seq < 1 || max_seq > VUIB_NA_MAX_SEQ)
+        return na_fail(err, err_len, VUIB_ERR_RANGE, "max_seq %d outside [1, %d] (built-in scratch limit)",
+                       max_seq, VUIB_NA_MAX_SEQ);
+    if (n_heads < 1 || n_heads > VUIB_NA_MAX_HEADS || n_kv_heads < 1 || n_heads % n_kv_heads != 0 ||
+        n_heads / n_kv_heads > 2)
+        return na_fail(err, err_len, VUIB_ERR_RANGE, "n_heads %d / n_kv_heads %d unsupported (at most %d query "
+                       "heads, 1 or 2 per kv head)", n_heads, n_kv_heads, VUIB_NA_MAX_HEADS);
+    int dev = -1;
+    cudaError_t rc = cudaGetDevice(&dev);
+    if (rc != cudaSuccess || dev < 0 || dev >= VUIB_NA_MAX_DEVICES)
+        return na_fail(err, err_len, VUIB_ERR_CUDA, "cudaGetDevice: %s (device %d)", cudaGetErrorString(rc), dev);
+    void* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_na_mutex);
+        if (!g_na_dev_ptr[dev]) {
+            // set-up, once per device, with that device current
+            void* p = nullptr;
+            rc = cudaGetSymbolAddress(&p, g_na_scratch);
+            if (rc != cudaSuccess || !p)
+                return na_fail(err, err_len, VUIB_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(rc));
+            g_na_dev_ptr[dev] = p;
+        }
+        base = g_na_dev_ptr[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char* b = static_cast<unsigned char*>(base);
+    // the array keeps the previous call's contents: the arrival counters must start at zero
+    rc = cudaMemsetAsync(b + NA_PART_BYTES, 0, NA_COUNTER_BYTES, s);
+    if (rc != cudaSuccess)
+        return na_fail(err, err_len, VUIB_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(rc));
+    const int S = (max_seq + ATT_SPLIT - 1) / ATT_SPLIT;
+    AttnArgs aa{static_cast<const bf16*>(q_dev), static_cast<const bf16*>(k_cache_dev),
+                static_cast<const bf16*>(v_cache_dev), row_slot_dev, row_pos_dev,
+                reinterpret_cast<float*>(b), reinterpret_cast<int32_t*>(b + NA_PART_BYTES),
+                static_cast<bf16*>(out_dev), n_heads, n_kv_heads, max_seq, S};
+    k_attn_decode<<<dim3(S, n_kv_heads, n_rows), ATT_THREADS, 0, s>>>(aa);
+    rc = cudaGetLastError();
+    if (rc != cudaSuccess)
+        return na_fail(err, err_len, VUIB_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(rc));
     return VUIB_OK;
 }
