@@ -256,15 +256,12 @@ def run_b200(args):
         phase = {"backbone_ms_eager": tb / reps, "depth_ms_eager": td / reps}
 
     # ---- aggregate over ranks ----------------------------------------------------
-    t = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max, e2e_ms_max = t.tolist()
+    from vui_b200.replicas import aggregate_rate
+
+    fps, ms_max = aggregate_rate(B * K, ms, dev)
+    e2e_fps, _ = aggregate_rate(B * K, e2e_s * 1e3, dev)
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
-        frames = B * K * world
-        fps = frames / (ms_max * 1e-3)
-        e2e_fps = frames / (e2e_ms_max * 1e-3)
         w_bytes = model.weight_bytes_per_step()
         step_bytes = w_bytes + B * (GATHER_BYTES_PER_STREAM + KV_BYTES_PER_POS * (mean_T + 1))
         achieved = step_bytes / (ms_max / K * 1e-3) / 1e9
