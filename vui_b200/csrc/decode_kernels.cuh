@@ -52,6 +52,14 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return r;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization
+// attribute may start while its predecessor still runs.  pdl_trigger() lets the
+// successor be scheduled; pdl_wait() blocks until the predecessor has finished
+// and its writes are visible.  Everything a kernel does before pdl_wait() must
+// touch only constants (weights).  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
@@ -94,6 +102,8 @@ __global__ void __launch_bounds__(128) k_embed_codes(
     const int32_t* __restrict__ seq_lens, const bf16* __restrict__ table, bf16* __restrict__ x,
     int32_t* __restrict__ row_slot, int32_t* __restrict__ row_pos, int d, int Q, int CS,
     int n_slots, int max_seq, int32_t* __restrict__ flag) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     if (slots) {  // decode step: also publish the row's (slot, position)
         int slot = slots[r];
@@ -436,6 +446,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(Stage st, Epi ep, int M, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * GEMV_WARPS + warp;
     const bool live = item < n_items;
+    pdl_trigger();
 
     uint4 w[NC][IT];
     if (live) {
@@ -449,6 +460,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(Stage st, Epi ep, int M, 
                 w[c][it] = (k < K) ? ldg_stream(wr[c] + k) : make_uint4(0, 0, 0, 0);
             }
     }
+    pdl_wait();  // the weights above are constants; activations below come from the predecessor
     for (int r0 = 0; r0 < M; r0 += RT) {
         const int nr = min(RT, M - r0);
         if (r0) __syncthreads();
@@ -521,6 +533,8 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float (&acc)[8
 
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
     const int sp = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+    pdl_trigger();
+    pdl_wait();
     const int len = a.row_pos[r] + 1;
     const int nsplit = (len + ATT_SPLIT - 1) / ATT_SPLIT;
     if (sp >= nsplit) return;
@@ -673,6 +687,8 @@ __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restrict__ x,
                                                     const int32_t* __restrict__ row_slot,
                                                     const int32_t* __restrict__ seq_inc,
                                                     int32_t* __restrict__ seq_lens, int bump) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     __shared__ float red[4];
     const bf16* xr = x + (size_t)r * d;
@@ -711,6 +727,8 @@ __global__ void __launch_bounds__(64) k_rq_embed(const int32_t* __restrict__ cod
                                                  const bf16* __restrict__ pos_emb,
                                                  bf16* __restrict__ xout, int rd, int CS, int p,
                                                  int row_mul, int row_add) {
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x;
     const int code = code_cur[b];
     const bf16* e = code_emb + ((size_t)(p - 1) * CS + code) * rd;
@@ -774,6 +792,8 @@ struct SampleArgs {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
     constexpr int CS = SAMPLE_THREADS * SAMPLE_EL;
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slot = a.slots[r];
     const SamplingCtl ctl = *a.ctl;

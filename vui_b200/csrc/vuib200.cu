@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -84,6 +85,33 @@ static void make_layout(VuibEngine* e) {
     L.total = off;
 }
 
+// Launch with the programmatic-stream-serialization attribute (see pdl_wait in
+// decode_kernels.cuh) unless VUIB_NO_PDL is set in the environment.
+static bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* s = getenv("VUIB_NO_PDL");
+        v = (s && s[0] && s[0] != '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+template <class... KArgs, class... Args>
+static cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                          Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 template <class T>
 static T* wsp(VuibEngine* e, size_t off) { return reinterpret_cast<T*>(e->ws + off); }
 
@@ -95,16 +123,10 @@ static cudaError_t launch_gemv_k(VuibEngine* e, const Stage& st, const Epi& ep, 
                                  cudaStream_t s) {
     const int grid = (n_items + GEMV_WARPS - 1) / GEMV_WARPS;
     e->launches++;
-    if (M <= 1) {
-        k_gemv<K, 1, Stage, Epi><<<grid, GEMV_THREADS, 1 * K * 2, s>>>(st, ep, M, n_items);
-    } else if (M <= 2) {
-        k_gemv<K, 2, Stage, Epi><<<grid, GEMV_THREADS, 2 * K * 2, s>>>(st, ep, M, n_items);
-    } else if (M <= 4) {
-        k_gemv<K, 4, Stage, Epi><<<grid, GEMV_THREADS, 4 * K * 2, s>>>(st, ep, M, n_items);
-    } else {
-        k_gemv<K, 8, Stage, Epi><<<grid, GEMV_THREADS, 8 * K * 2, s>>>(st, ep, M, n_items);
-    }
-    return cudaGetLastError();
+    if (M <= 1) return launch(k_gemv<K, 1, Stage, Epi>, grid, GEMV_THREADS, 1 * K * 2, s, st, ep, M, n_items);
+    if (M <= 2) return launch(k_gemv<K, 2, Stage, Epi>, grid, GEMV_THREADS, 2 * K * 2, s, st, ep, M, n_items);
+    if (M <= 4) return launch(k_gemv<K, 4, Stage, Epi>, grid, GEMV_THREADS, 4 * K * 2, s, st, ep, M, n_items);
+    return launch(k_gemv<K, 8, Stage, Epi>, grid, GEMV_THREADS, 8 * K * 2, s, st, ep, M, n_items);
 }
 
 #define VUIB_GEMV(Kval, ...)                                                        \
@@ -294,7 +316,7 @@ static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
         AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
                     row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
                     c.n_heads, c.n_kv_heads, c.max_seq, e->S};
-        k_attn_decode<<<dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s>>>(aa);
+        CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
         e->launches++;
         CK(cudaGetLastError());
 
@@ -343,9 +365,9 @@ extern "C" int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* ro
     CK(cudaMemcpyAsync(e->ws + L.x, emb_dev, (size_t)n_rows * d * 2, cudaMemcpyDeviceToDevice, s));
     rc = run_layers(e, n_rows, s);
     if (rc) return rc;
-    k_final_norm<<<n_rows, 128, 0, s>>>(wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
+    CK(launch(k_final_norm, n_rows, 128, 0, s, wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
                                         e->cfg.norm_eps, static_cast<bf16*>(hidden_out_dev), d,
-                                        nullptr, nullptr, nullptr, 0);
+                                        nullptr, nullptr, nullptr, 0));
     e->launches++;
     CK(cudaGetLastError());
     return VUIB_OK;
@@ -364,18 +386,18 @@ extern "C" int32_t vuib_backbone_step(VuibEngine* e, int32_t B, const int32_t* s
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
-    k_embed_codes<<<B, 128, 0, s>>>(codes_in_dev, slots_dev, e->seq_lens,
+    CK(launch(k_embed_codes, B, 128, 0, s, codes_in_dev, slots_dev, e->seq_lens,
                                     static_cast<const bf16*>(e->w.audio_emb), wsp<bf16>(e, L.x),
                                     wsp<int32_t>(e, L.row_slot), wsp<int32_t>(e, L.row_pos), c.d_model,
                                     c.n_quantizers, c.codebook_size, c.n_slots, c.max_seq,
-                                    wsp<int32_t>(e, L.flag));
+                                    wsp<int32_t>(e, L.flag)));
     e->launches++;
     CK(cudaGetLastError());
     rc = run_layers(e, B, s);
     if (rc) return rc;
-    k_final_norm<<<B, 128, 0, s>>>(wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
+    CK(launch(k_final_norm, B, 128, 0, s, wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
                                    c.norm_eps, static_cast<bf16*>(hidden_out_dev), c.d_model,
-                                   wsp<int32_t>(e, L.row_slot), seq_inc_dev, e->seq_lens, 1);
+                                   wsp<int32_t>(e, L.row_slot), seq_inc_dev, e->seq_lens, 1));
     e->launches++;
     CK(cudaGetLastError());
     return run_heads(e, B, static_cast<const bf16*>(hidden_out_dev), static_cast<bf16*>(cb0_out_dev),
@@ -459,7 +481,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     sa.eos_prob = eos_prob;
     sa.bump_frame = 0;
     sa.zero_from = Qn < Q ? Qn : 0;
-    k_sample<<<B, SAMPLE_THREADS, 0, s>>>(sa);
+    CK(launch(k_sample, B, SAMPLE_THREADS, 0, s, sa));
     e->launches++;
     CK(cudaGetLastError());
     sa.eos_logit = nullptr;
@@ -477,7 +499,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
         EpiProjPos ep{static_cast<const bf16*>(e->w.rq_backbone_proj), c.d_model, pos_emb, x2, rd, 2};
         CK(VUIB_GEMV(c.d_model, e, sc, ep, B, rd, s));
     }
-    k_rq_embed<<<B, 64, 0, s>>>(code_cur, code_emb, pos_emb, x2, rd, CS, 1, 2, 1);
+    CK(launch(k_rq_embed, B, 64, 0, s, code_cur, code_emb, pos_emb, x2, rd, CS, 1, 2, 1));
     e->launches++;
     CK(cudaGetLastError());
     int32_t rc = rq_layers(e, 2 * B, x2, 2, 0, s);
@@ -487,7 +509,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     const bf16* head = static_cast<const bf16*>(e->w.rq_head);
     for (int i = 0; i < Qn - 1; ++i) {
         if (i > 0) {
-            k_rq_embed<<<B, 64, 0, s>>>(code_cur, code_emb, pos_emb, x1, rd, CS, i + 1, 1, 0);
+            CK(launch(k_rq_embed, B, 64, 0, s, code_cur, code_emb, pos_emb, x1, rd, CS, i + 1, 1, 0));
             e->launches++;
             CK(cudaGetLastError());
             rc = rq_layers(e, B, x1, 1, i + 1, s);
@@ -502,7 +524,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
         sa.codebook = i + 1;
         sa.out_col = i + 1;
         sa.bump_frame = (i == Qn - 2);
-        k_sample<<<B, SAMPLE_THREADS, 0, s>>>(sa);
+        CK(launch(k_sample, B, SAMPLE_THREADS, 0, s, sa));
         e->launches++;
         CK(cudaGetLastError());
     }
@@ -547,7 +569,7 @@ extern "C" int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, 
                 static_cast<const bf16*>(e->v[layer]), row_slot_dev, row_pos_dev,
                 wsp<float>(e, e->lay.part), wsp<int32_t>(e, e->lay.counters), static_cast<bf16*>(out_dev),
                 c.n_heads, c.n_kv_heads, c.max_seq, e->S};
-    k_attn_decode<<<dim3(e->S, c.n_kv_heads, n_rows), ATT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(aa);
+    CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, n_rows), ATT_THREADS, 0, static_cast<cudaStream_t>(stream), aa));
     e->launches++;
     CK(cudaGetLastError());
     return VUIB_OK;
@@ -559,10 +581,10 @@ extern "C" int32_t vuib_embed_codes(VuibEngine* e, int32_t n_rows, const int64_t
     if (!e->have_w || !e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind weights and workspace first");
     if (n_rows < 1) return fail(e, VUIB_ERR_RANGE, "n_rows %d < 1", n_rows);
     const VuibConfig& c = e->cfg;
-    k_embed_codes<<<n_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    CK(launch(k_embed_codes, n_rows, 128, 0, static_cast<cudaStream_t>(stream), 
         codes_dev, nullptr, nullptr, static_cast<const bf16*>(e->w.audio_emb), static_cast<bf16*>(out_dev),
         nullptr, nullptr, c.d_model, c.n_quantizers, c.codebook_size, c.n_slots, c.max_seq,
-        wsp<int32_t>(e, e->lay.flag));
+        wsp<int32_t>(e, e->lay.flag)));
     e->launches++;
     CK(cudaGetLastError());
     return VUIB_OK;
@@ -593,7 +615,7 @@ extern "C" int32_t vuib_sample_rows(VuibEngine* e, int32_t B, const int32_t* slo
     sa.Q = 1;
     sa.out_col = 0;
     sa.bump_frame = 1;
-    k_sample<<<B, SAMPLE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(sa);
+    CK(launch(k_sample, B, SAMPLE_THREADS, 0, static_cast<cudaStream_t>(stream), sa));
     e->launches++;
     CK(cudaGetLastError());
     return VUIB_OK;
