@@ -43,7 +43,7 @@ typedef enum VuibStatus {
     VUIB_ERR_UNBOUND = -4,     /* weights, KV, rope table or workspace not bound yet */
     VUIB_ERR_CUDA = -5,        /* a CUDA runtime call failed (text in last_error) */
     VUIB_ERR_WORKSPACE = -6,   /* workspace too small or misaligned */
-    VUIB_ERR_DEVICE_FLAG = -7  /* a kernel recorded a bad slot / position / code */
+    VUIB_ERR_DEVICE_FLAG = -7  /* a kernel recorded a bad slot / position / code, or a barrier timeout */
 } VuibStatus;
 
 /* Model + engine shape.  Mirrors vui.config.VuiConfig (src/vui/config.py:16-54)
@@ -227,6 +227,11 @@ int32_t vuib_sample_rows(VuibEngine* e, int32_t B, const int32_t* slots_dev, con
  * of every slot when slot == -1: Engine._rep_reset / _rep_reset_slot
  * (engine.py:555-569, 594-595).  Async on `stream`. */
 int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream);
+
+/* Zeroes the mutable sampler / bookkeeping state in the workspace: per-slot draw counters,
+ * repetition-penalty state, the device error flag.  Weights, KV and lengths are untouched.
+ * (The reference has no equivalent: its draws come from torch's global generator.) */
+int32_t vuib_reset_state(VuibEngine* e, void* stream);
 
 /* Position-only rewind / reset (engine.py:651-654).  Synchronous small copies. */
 int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len);

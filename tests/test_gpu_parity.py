@@ -276,6 +276,36 @@ def test_batch_invariance_and_ragged(eng8, eng1):
         r.close()
 
 
+def test_persistent_kernel_equals_per_phase_kernels(eng8):
+    """The one-launch persistent frame kernel and the graph of per-phase kernels run the same
+    arithmetic: identical codes, hidden states and logits, greedy and sampled, B = 1 and ragged B = 3."""
+    from vui_b200 import GenConfig
+
+    eng = eng8
+    cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4)
+    for lens, greedy in (([33], True), ([40, 150, 77], True), ([64, 200, 31], False)):
+        outs = []
+        for off in ("", "1"):
+            os.environ["VUIB_NO_PERSISTENT"] = off
+            eng._graphs = {}
+            eng.reset()
+            eng._ws_reset_counters()
+            rows = [eng.new_row() for _ in lens]
+            hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 50 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
+            h = torch.stack([x[-1] for x in hs])
+            codes = eng.generate_frames(rows, h, 5, cfg, greedy=greedy).cpu()
+            torch.cuda.synchronize()
+            outs.append((codes, eng._g_hidden_out[: len(lens)].clone(), eng._g_cb0_out[: len(lens)].clone(),
+                         eng._g_eos_prob[: len(lens)].clone()))
+            eng.check_device()
+            for r in rows:
+                r.close()
+        os.environ["VUIB_NO_PERSISTENT"] = ""
+        eng._graphs = {}
+        for a, b in zip(outs[0], outs[1]):
+            assert torch.equal(a, b), (lens, greedy)
+
+
 def test_prefill_chunking_equals_single_call(eng8):
     """A 300-token prompt (cut at max_prefill_rows=256) and token-by-token prefill give the same hidden."""
     eng = eng8

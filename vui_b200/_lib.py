@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libvuib200.so")
 SOURCES = [os.path.join(_HERE, "csrc", "vuib200.cu")]
 HEADERS = [
     os.path.join(_HERE, "csrc", "decode_kernels.cuh"),
+    os.path.join(_HERE, "csrc", "frame_kernel.cuh"),
     os.path.join(_ROOT, "include", "vuib200.h"),
 ]
 NVCC_FLAGS = [
@@ -89,6 +90,7 @@ SYMBOLS = {
     "vuib_embed_codes": (C.c_int32, [_P, C.c_int32, _P, _P, _P]),
     "vuib_sample_rows": (C.c_int32, [_P, C.c_int32, _P, _P, C.c_int32, _P, _P]),
     "vuib_rep_reset": (C.c_int32, [_P, C.c_int32, _P]),
+    "vuib_reset_state": (C.c_int32, [_P, _P]),
     "vuib_set_seq_len": (C.c_int32, [_P, C.c_int32, C.c_int32]),
     "vuib_get_seq_len": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_int32)]),
     "vuib_check_device_flag": (C.c_int32, [_P, _P]),

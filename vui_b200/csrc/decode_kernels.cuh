@@ -154,7 +154,7 @@ struct StageNorm {
     template <int K>
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        for (int rr = warp; rr < nr; rr += GEMV_WARPS) {
+        for (int rr = warp; rr < nr; rr += (int)(blockDim.x >> 5)) {
             const bf16* xr = x + ((size_t)(r0 + rr) * row_mul + row_add) * K;
             constexpr int IT = (K + 255) / 256;
             float v[IT][8];
@@ -163,7 +163,7 @@ struct StageNorm {
             for (int it = 0; it < IT; ++it) {
                 const int k = it * 256 + lane * 8;
                 if (k < K) {
-                    uint4 u = *reinterpret_cast<const uint4*>(xr + k);
+                    uint4 u = __ldcg(reinterpret_cast<const uint4*>(xr + k));
                     unpack8(u, v[it]);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) ss = fmaf(v[it][j], v[it][j], ss);
@@ -192,7 +192,7 @@ struct StageCopy {
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
         const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r0 * K);
         uint4* dst = reinterpret_cast<uint4*>(Xs);
-        for (int i = threadIdx.x; i < nr * (K / 8); i += GEMV_THREADS) dst[i] = src[i];
+        for (int i = threadIdx.x; i < nr * (K / 8); i += blockDim.x) dst[i] = __ldcg(src + i);
     }
 };
 
@@ -217,9 +217,9 @@ struct StageRqAttn {
         for (int rr = 0; rr < nr; ++rr) {
             const int r = r0 + rr;
             const int b = r / rows_per_b, pos = pos_base + r % rows_per_b;
-            for (int h = warp; h < H; h += GEMV_WARPS) {
+            for (int h = warp; h < H; h += (int)(blockDim.x >> 5)) {
                 float qf[8];
-                unpack8(*reinterpret_cast<const uint4*>(q + (size_t)r * K + h * HD + s * 8), qf);
+                unpack8(__ldcg(reinterpret_cast<const uint4*>(q + (size_t)r * K + h * HD + s * 8)), qf);
                 float m = NEG_BIG, l = 0.f, acc[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -228,8 +228,8 @@ struct StageRqAttn {
                     const bool ok = t <= pos;
                     const size_t off = ((size_t)b * Qpos + (ok ? t : 0)) * K + h * HD + s * 8;
                     float kf[8], vf[8];
-                    unpack8(*reinterpret_cast<const uint4*>(kc + off), kf);
-                    unpack8(*reinterpret_cast<const uint4*>(vc + off), vf);
+                    unpack8(__ldcg(reinterpret_cast<const uint4*>(kc + off)), kf);
+                    unpack8(__ldcg(reinterpret_cast<const uint4*>(vc + off)), vf);
                     float d = 0.f;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) d = fmaf(qf[j], kf[j], d);
@@ -306,8 +306,8 @@ struct EpiQkv {
         float t0 = rbf(pick<RT>(acc[0], lane)), t1 = rbf(pick<RT>(acc[1], lane));
         int slot, pos;
         if (row_slot) {
-            slot = row_slot[r];
-            pos = row_pos[r];
+            slot = __ldcg(row_slot + r);
+            pos = __ldcg(row_pos + r);
         } else {
             slot = r / rows_per_b;
             pos = pos_base + r % rows_per_b;
@@ -351,7 +351,8 @@ struct EpiResidual {
                                           const float (&acc)[1][RT]) const {
         if (lane >= nr) return;
         const size_t idx = (size_t)(r0 + lane) * N + item;
-        const bf16 o = f2bf(bf2f(x[idx]) + rbf(pick<RT>(acc[0], lane)));
+        const unsigned short xb = __ldcg(reinterpret_cast<const unsigned short*>(x) + idx);
+        const bf16 o = f2bf(bf2f(__ushort_as_bfloat16(xb)) + rbf(pick<RT>(acc[0], lane)));
         x[idx] = o;
         if (tap) tap[idx] = o;
     }
@@ -531,15 +532,25 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float (&acc)[8
     m = mn;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
-    const int sp = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
-    pdl_trigger();
-    pdl_wait();
-    const int len = a.row_pos[r] + 1;
+// Named barrier over `n` threads (id 0 with n = blockDim.x is __syncthreads()).
+__device__ __forceinline__ void bar_named(int id, int n) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
+struct AttnSmem {
+    float sm[4][2][8][10];  // [warp][head][s][acc8, m, l]
+    int s_last;
+};
+
+// One (split, kv head, row) unit of work for a group of ATT_THREADS threads whose
+// index within the group is `tid`; the group synchronises on named barrier bar_id.
+__device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, int r, int tid,
+                                          AttnSmem& S_, int bar_id) {
+    const int len = __ldcg(a.row_pos + r) + 1;
     const int nsplit = (len + ATT_SPLIT - 1) / ATT_SPLIT;
     if (sp >= nsplit) return;
-    const int slot = a.row_slot[r];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = __ldcg(a.row_slot + r);
+    const int warp = tid >> 5, lane = tid & 31;
     const int s = lane & 7, g = lane >> 3;
     const int G = a.Hq / a.Hkv;  // q heads per kv head (2)
     const int t_begin = sp * ATT_SPLIT, t_end = min(len, t_begin + ATT_SPLIT);
@@ -560,13 +571,13 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
             vr[it] = make_uint4(0, 0, 0, 0);
         }
     }
-    __shared__ float sm[4][2][8][10];  // [warp][head][s][acc8, m, l]
-    __shared__ int s_last;
+    float (&sm)[4][2][8][10] = S_.sm;
+    int& s_last = S_.s_last;
     float qf[2][8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int hq = kvh * G + (h < G ? h : 0);
-        unpack8(*reinterpret_cast<const uint4*>(a.q + (size_t)r * a.Hq * HD + hq * HD + s * 8), qf[h]);
+        unpack8(__ldcg(reinterpret_cast<const uint4*>(a.q + (size_t)r * a.Hq * HD + hq * HD + s * 8)), qf[h]);
     }
     float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f}, acc[2][8];
 #pragma unroll
@@ -625,9 +636,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
             sm[warp][h][s][9] = l[h];
         }
     }
-    __syncthreads();
+    bar_named(bar_id, ATT_THREADS);
     // thread (h, dim): merge the 4 warps
-    const int h = threadIdx.x >> 6, dim = threadIdx.x & 63;
+    const int h = tid >> 6, dim = tid & 63;
     const int ds = dim >> 3, dj = dim & 7;
     float M_ = NEG_BIG;
 #pragma unroll
@@ -654,12 +665,12 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
         }
     }
     __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    bar_named(bar_id, ATT_THREADS);
+    if (tid == 0) {
         const int old = atomicAdd(a.counters + r * a.Hkv + kvh, 1);
         s_last = (old == nsplit - 1);
     }
-    __syncthreads();
+    bar_named(bar_id, ATT_THREADS);
     if (!s_last) return;
     __threadfence();
     if (head_ok) {
@@ -674,7 +685,14 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
         }
         a.out[(size_t)r * a.Hq * HD + hq * HD + dim] = f2bf(Os / Ls);
     }
-    if (threadIdx.x == 0) a.counters[r * a.Hkv + kvh] = 0;
+    if (tid == 0) a.counters[r * a.Hkv + kvh] = 0;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ AttnSmem S_;
+    attn_unit(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, S_, 0);
 }
 
 // ---------------------------------------------------------------------------
@@ -790,22 +808,32 @@ struct SampleArgs {
     int zero_from;            // >0: also zero codes_out[r, zero_from..Q)
 };
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
+struct SampleSmem {
+    float s_f[8];
+    int s_i[8];
+    uint32_t hist[256];
+    uint32_t s_prefix, s_krem;
+    int s_pick, s_lastkept;
+};
+
+// Samples row r with a group of SAMPLE_THREADS threads (index `tid` in the group,
+// named barrier bar_id).  Returns the chosen code to every thread of the group.
+__device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, SampleSmem& S_, int bar_id) {
     constexpr int CS = SAMPLE_THREADS * SAMPLE_EL;
-    pdl_trigger();
-    pdl_wait();
-    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slot = a.slots[r];
+    const int warp = tid >> 5, lane = tid & 31;
+    const int slot = __ldcg(a.slots + r);
     const SamplingCtl ctl = *a.ctl;
     const bool is_cb0 = a.codebook == 0;
-    __shared__ float s_f[8];
-    __shared__ int s_i[8];
-    __shared__ uint32_t hist[256];
-    __shared__ uint32_t s_prefix, s_krem;
-    __shared__ int s_pick, s_lastkept;
+    float (&s_f)[8] = S_.s_f;
+    int (&s_i)[8] = S_.s_i;
+    uint32_t (&hist)[256] = S_.hist;
+    uint32_t& s_prefix = S_.s_prefix;
+    uint32_t& s_krem = S_.s_krem;
+    int& s_pick = S_.s_pick;
+    int& s_lastkept = S_.s_lastkept;
 
     float v[SAMPLE_EL];
-    unpack8(*reinterpret_cast<const uint4*>(a.logits + (size_t)r * a.stride + tid * SAMPLE_EL), v);
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(a.logits + (size_t)r * a.stride + tid * SAMPLE_EL)), v);
     if (is_cb0 && ctl.rep_penalty > 1.0f) {
         const float* cnt = a.rep_counts + (size_t)slot * CS + tid * SAMPLE_EL;
 #pragma unroll
@@ -833,12 +861,12 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (lane == 0) { s_f[warp] = bv; s_i[warp] = bi; }
-    __syncthreads();
+    bar_named(bar_id, SAMPLE_THREADS);
     bv = s_f[0]; bi = s_i[0];
 #pragma unroll
     for (int w = 1; w < 8; ++w)
         if (s_f[w] > bv || (s_f[w] == bv && s_i[w] < bi)) { bv = s_f[w]; bi = s_i[w]; }
-    __syncthreads();
+    bar_named(bar_id, SAMPLE_THREADS);
 
     int choice = bi;
     if (top_k != 1) {
@@ -859,13 +887,13 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
             for (int pass = 0; pass < 4; ++pass) {
                 const int shift = 24 - 8 * pass;
                 hist[tid] = 0u;
-                __syncthreads();
+                bar_named(bar_id, SAMPLE_THREADS);
                 const uint32_t prefix = s_prefix;
                 const uint32_t pmask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
 #pragma unroll
                 for (int j = 0; j < SAMPLE_EL; ++j)
                     if ((key[j] & pmask) == prefix) atomicAdd(&hist[(key[j] >> shift) & 255u], 1u);
-                __syncthreads();
+                bar_named(bar_id, SAMPLE_THREADS);
                 if (warp == 0) {
                     // lane covers digits 255-8*lane .. 248-8*lane (descending)
                     uint32_t c8[8], tot = 0u;
@@ -890,7 +918,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
                         }
                     }
                 }
-                __syncthreads();
+                bar_named(bar_id, SAMPLE_THREADS);
             }
             const uint32_t thr = s_prefix;
 #pragma unroll
@@ -911,7 +939,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
         }
         if (lane == 31) s_f[warp] = inc;
         if (tid == 0) { s_pick = 0x7fffffff; s_lastkept = -1; }
-        __syncthreads();
+        bar_named(bar_id, SAMPLE_THREADS);
         float wbase = 0.f, total = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
@@ -934,7 +962,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
         }
         if (mine != 0x7fffffff) atomicMin(&s_pick, mine);
         if (lastk >= 0) atomicMax(&s_lastkept, lastk);
-        __syncthreads();
+        bar_named(bar_id, SAMPLE_THREADS);
         choice = s_pick != 0x7fffffff ? s_pick : s_lastkept;
     }
     if (tid == 0) {
@@ -966,6 +994,14 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
         }
         if (a.bump_frame) a.frame_ctr[slot] += 1;
     }
+    return choice;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ SampleSmem S_;
+    sample_row(a, blockIdx.x, threadIdx.x, S_, 0);
 }
 
 }  // namespace vuib

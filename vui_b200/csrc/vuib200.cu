@@ -11,6 +11,7 @@
 #include <new>
 
 #include "decode_kernels.cuh"
+#include "frame_kernel.cuh"
 
 using namespace vuib;
 
@@ -18,6 +19,7 @@ struct WsLayout {
     size_t flag, ctl, row_slot, row_pos, x, q, attn, act, part, counters;
     size_t rq_x2, rq_x, rq_q, rq_act, rq_k, rq_v, rq_logits, code_cur;
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
+    size_t bar, devmodel;
     size_t total;
 };
 
@@ -37,6 +39,9 @@ struct VuibEngine {
     bf16* tap_layers;
     bf16* tap_rq;
     long long launches;
+    DevModel dm;        // host copy of what the persistent kernel reads from the workspace
+    int num_sms;        // 0 until the first persistent launch asks the device
+    int coop;           // launch the frame kernel cooperatively
     char err[256];
 };
 
@@ -82,6 +87,8 @@ static void make_layout(VuibEngine* e) {
     L.rep_hist = take((size_t)c.n_slots * REP_HIST_MAX * 4);
     L.rep_head = take((size_t)c.n_slots * 4);
     L.rep_filled = take((size_t)c.n_slots * 4);
+    L.bar = take(256);
+    L.devmodel = take(sizeof(DevModel));
     L.total = off;
 }
 
@@ -114,6 +121,25 @@ static cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
 
 template <class T>
 static T* wsp(VuibEngine* e, size_t off) { return reinterpret_cast<T*>(e->ws + off); }
+
+// The persistent frame kernel reads the bound pointers from a copy in the workspace.
+static int32_t sync_devmodel(VuibEngine* e) {
+    if (!e->have_ws) return VUIB_OK;
+    e->dm.w = e->w;
+    for (int i = 0; i < VUIB_MAX_LAYERS; ++i) {
+        e->dm.k[i] = e->k[i];
+        e->dm.v[i] = e->v[i];
+    }
+    e->dm.rope = e->rope;
+    e->dm.seq_lens = e->seq_lens;
+    cudaError_t rc = cudaMemcpy(e->ws + e->lay.devmodel, &e->dm, sizeof(DevModel), cudaMemcpyHostToDevice);
+    if (rc != cudaSuccess) {
+        snprintf(e->err, sizeof(e->err), "copying the pointer table to the workspace failed: %s",
+                 cudaGetErrorString(rc));
+        return VUIB_ERR_CUDA;
+    }
+    return VUIB_OK;
+}
 
 // ---------------------------------------------------------------------------
 // GEMV launch: pick the row-tile size from M, K from the supported set.
@@ -182,6 +208,7 @@ extern "C" int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out) {
     e->samp.top_k_cb0 = 1;
     e->samp.top_k_rq = 1;
     e->samp.rep_penalty = 1.0f;
+    e->coop = 1;
     make_layout(e);
     *out = e;
     return VUIB_OK;
@@ -214,7 +241,7 @@ extern "C" int32_t vuib_bind_workspace(VuibEngine* e, void* dev, size_t bytes) {
                     e->lay.total, bytes, dev);
     e->ws = static_cast<unsigned char*>(dev);
     e->have_ws = true;
-    return VUIB_OK;
+    return sync_devmodel(e);
 }
 
 extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
@@ -231,7 +258,7 @@ extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
     if (!ok) return fail(e, VUIB_ERR_NULL, "a weight pointer is NULL");
     e->w = *w;
     e->have_w = true;
-    return VUIB_OK;
+    return sync_devmodel(e);
 }
 
 extern "C" int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* v_dev,
@@ -244,14 +271,14 @@ extern "C" int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* 
     }
     e->seq_lens = seq_lens_dev;
     e->have_kv = true;
-    return VUIB_OK;
+    return sync_devmodel(e);
 }
 
 extern "C" int32_t vuib_bind_rope(VuibEngine* e, const void* freqs_cis_dev) {
     if (!e || !freqs_cis_dev) return VUIB_ERR_NULL;
     e->rope = static_cast<const bf16*>(freqs_cis_dev);
     e->have_rope = true;
-    return VUIB_OK;
+    return sync_devmodel(e);
 }
 
 static int32_t ready(VuibEngine* e) {
@@ -531,6 +558,124 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     return VUIB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Persistent frame kernel (frame_kernel.cuh): one launch per frame for B <= 8.
+// ---------------------------------------------------------------------------
+static bool env_off(const char* name) {
+    const char* s = getenv(name);
+    return s && s[0] && s[0] != '0';
+}
+
+static bool persistent_ok(VuibEngine* e, int B) {
+    const VuibConfig& c = e->cfg;
+    return B <= 8 && c.d_model == 1024 && c.ffn == 3072 && c.rq_d_model == 512 &&
+           (c.rq_ffn == 1408 || c.rq_ffn == 1536) && !env_off("VUIB_NO_PERSISTENT");
+}
+
+typedef void (*FrameKernel)(FrameArgs);
+
+static FrameKernel frame_kernel_for(int rt, int rqf) {
+    if (rqf == 1408) {
+        switch (rt) {
+            case 1: return k_frame<1, 1408>;
+            case 2: return k_frame<2, 1408>;
+            case 4: return k_frame<4, 1408>;
+            default: return k_frame<8, 1408>;
+        }
+    }
+    switch (rt) {
+        case 1: return k_frame<1, 1536>;
+        case 2: return k_frame<2, 1536>;
+        case 4: return k_frame<4, 1536>;
+        default: return k_frame<8, 1536>;
+    }
+}
+
+static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc,
+                            int64_t* codes_io, bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob,
+                            int do_backbone, int first_frame, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    if (e->num_sms == 0) {
+        int dev = 0;
+        CK(cudaGetDevice(&dev));
+        CK(cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    FrameArgs fa;
+    memset(&fa, 0, sizeof(fa));
+    fa.m = wsp<DevModel>(e, L.devmodel);
+    FrameBufs& b = fa.b;
+    b.row_slot = wsp<int32_t>(e, L.row_slot);
+    b.row_pos = wsp<int32_t>(e, L.row_pos);
+    b.x = wsp<bf16>(e, L.x);
+    b.q = wsp<bf16>(e, L.q);
+    b.attn = wsp<bf16>(e, L.attn);
+    b.act = wsp<bf16>(e, L.act);
+    b.part = wsp<float>(e, L.part);
+    b.counters = wsp<int32_t>(e, L.counters);
+    b.rq_x2 = wsp<bf16>(e, L.rq_x2);
+    b.rq_x = wsp<bf16>(e, L.rq_x);
+    b.rq_q = wsp<bf16>(e, L.rq_q);
+    b.rq_act = wsp<bf16>(e, L.rq_act);
+    b.rq_k = wsp<bf16>(e, L.rq_k);
+    b.rq_v = wsp<bf16>(e, L.rq_v);
+    b.rq_logits = wsp<bf16>(e, L.rq_logits);
+    b.code_cur = wsp<int32_t>(e, L.code_cur);
+    b.ctl = wsp<SamplingCtl>(e, L.ctl);
+    b.frame_ctr = wsp<int32_t>(e, L.frame_ctr);
+    b.rep_counts = wsp<float>(e, L.rep_counts);
+    b.rep_hist = wsp<int32_t>(e, L.rep_hist);
+    b.rep_head = wsp<int32_t>(e, L.rep_head);
+    b.rep_filled = wsp<int32_t>(e, L.rep_filled);
+    b.flag = wsp<int32_t>(e, L.flag);
+    b.bar = wsp<unsigned>(e, L.bar);
+    fa.B = B;
+    fa.slots = slots;
+    fa.seq_inc = seq_inc;
+    fa.codes_io = codes_io;
+    fa.hidden_out = hidden;
+    fa.cb0_out = cb0;
+    fa.eos_out = eos;
+    fa.eos_prob = eos_prob;
+    fa.tap_layers = e->tap_layers;
+    fa.tap_rq = e->tap_rq;
+    fa.n_layers = c.n_layers;
+    fa.n_heads = c.n_heads;
+    fa.n_kv_heads = c.n_kv_heads;
+    fa.max_seq = c.max_seq;
+    fa.n_slots = c.n_slots;
+    fa.S = e->S;
+    fa.Q = c.n_quantizers;
+    fa.CS = c.codebook_size;
+    fa.rq_n_layers = c.rq_n_layers;
+    fa.rq_n_heads = c.rq_n_heads;
+    fa.max_rows = c.max_rows;
+    fa.norm_eps = c.norm_eps;
+    fa.rq_norm_eps = c.rq_norm_eps;
+    fa.n_codebooks = e->samp.n_codebooks > 0 ? e->samp.n_codebooks : c.n_quantizers;
+    fa.do_backbone = do_backbone;
+    fa.first_frame = first_frame;
+
+    const int rt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
+    FrameKernel kern = frame_kernel_for(rt, c.rq_ffn);
+    const size_t smem = (size_t)rt * 3072 * sizeof(bf16);
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CK(cudaMemsetAsync(e->ws + L.bar, 0, 4, s));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(e->num_sms);
+    cfg.blockDim = dim3(PF_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (e->coop && !env_off("VUIB_NO_COOP")) ? 1 : 0;
+    CK(cudaLaunchKernelEx(&cfg, kern, fa));
+    e->launches++;
+    return VUIB_OK;
+}
+
 extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
                                    const void* hidden_dev, const void* cb0_logits_dev,
                                    const void* eos_logit_dev, int32_t first_frame,
@@ -540,6 +685,12 @@ extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slot
     if (!slots_dev || !hidden_dev || !cb0_logits_dev || !codes_out_dev) return VUIB_ERR_NULL;
     if (B < 1 || B > e->cfg.max_rows)
         return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    if (persistent_ok(e, B))
+        return launch_frame(e, B, slots_dev, nullptr, codes_out_dev,
+                            const_cast<bf16*>(static_cast<const bf16*>(hidden_dev)),
+                            const_cast<bf16*>(static_cast<const bf16*>(cb0_logits_dev)),
+                            const_cast<bf16*>(static_cast<const bf16*>(eos_logit_dev)), eos_prob_out_dev, 0,
+                            first_frame, static_cast<cudaStream_t>(stream));
     return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_dev),
                      static_cast<const bf16*>(cb0_logits_dev), static_cast<const bf16*>(eos_logit_dev),
                      first_frame, codes_out_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
@@ -549,8 +700,17 @@ extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* sl
                                      const int32_t* seq_inc_dev, int64_t* codes_io_dev,
                                      void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
                                      float* eos_prob_out_dev, void* stream) {
-    int32_t rc = vuib_backbone_step(e, B, slots_dev, seq_inc_dev, codes_io_dev, hidden_out_dev,
-                                    cb0_out_dev, eos_out_dev, stream);
+    int32_t rc = ready(e);
+    if (rc) return rc;
+    if (!slots_dev || !codes_io_dev || !hidden_out_dev || !cb0_out_dev || !eos_out_dev) return VUIB_ERR_NULL;
+    if (B < 1 || B > e->cfg.max_rows)
+        return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    if (persistent_ok(e, B))
+        return launch_frame(e, B, slots_dev, seq_inc_dev, codes_io_dev, static_cast<bf16*>(hidden_out_dev),
+                            static_cast<bf16*>(cb0_out_dev), static_cast<bf16*>(eos_out_dev), eos_prob_out_dev,
+                            1, 0, static_cast<cudaStream_t>(stream));
+    rc = vuib_backbone_step(e, B, slots_dev, seq_inc_dev, codes_io_dev, hidden_out_dev,
+                            cb0_out_dev, eos_out_dev, stream);
     if (rc) return rc;
     return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
                      static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
@@ -636,6 +796,19 @@ extern "C" int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream) {
     return VUIB_OK;
 }
 
+extern "C" int32_t vuib_reset_state(VuibEngine* e, void* stream) {
+    if (!e) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CK(cudaMemsetAsync(e->ws + L.flag, 0, 256, s));
+    CK(cudaMemsetAsync(e->ws + L.counters, 0, (size_t)e->R * c.n_kv_heads * 4, s));
+    CK(cudaMemsetAsync(e->ws + L.frame_ctr, 0, (size_t)c.n_slots * 4, s));
+    CK(cudaMemsetAsync(e->ws + L.bar, 0, 256, s));
+    return vuib_rep_reset(e, -1, stream);
+}
+
 extern "C" int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len) {
     if (!e) return VUIB_ERR_NULL;
     if (!e->have_kv) return fail(e, VUIB_ERR_UNBOUND, "bind kv first");
@@ -662,7 +835,7 @@ extern "C" int32_t vuib_check_device_flag(VuibEngine* e, void* stream) {
     CK(cudaStreamSynchronize(s));
     if (flag) {
         CK(cudaMemsetAsync(e->ws + e->lay.flag, 0, 4, s));
-        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code)", flag);
+        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code, 8 = grid barrier timed out)", flag);
     }
     return VUIB_OK;
 }

@@ -577,11 +577,8 @@ class Engine:
         return out.cpu()
 
     def _ws_reset_counters(self) -> None:
-        """Zero the workspace (draw counters, penalty state) and re-send the sampling block."""
-        self._ws.zero_()
-        key, self._sampling_key = self._sampling_key, None
-        if key:
-            self._set_sampling(*key[:6])
+        """Zero the sampler state (draw counters, penalty state, error flag)."""
+        self._ck(self._lib.vuib_reset_state(self._handle, self._stream))
 
     def _embed_speaker(self, spk_emb):
         if spk_emb is None or "spk_proj.weight" not in self.model.sd:
