@@ -233,6 +233,14 @@ int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream);
  * (The reference has no equivalent: its draws come from torch's global generator.) */
 int32_t vuib_reset_state(VuibEngine* e, void* stream);
 
+/* Profiling aid for the persistent frame kernel: when the environment variable VUIB_TRACE is
+ * set, CTA 0 records the device clock (ns) when it arrives at and when it leaves each grid
+ * barrier of the last launch.  Copies up to max_entries (arrive, leave) pairs to out_host
+ * (2 uint64 each) and their count to *n_out, then 8 stamps taken inside one attention unit
+ * to out_host[2*max_entries .. 2*max_entries+8).  out_host holds 2*max_entries+8 values.
+ * Synchronous. */
+int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t max_entries, int32_t* n_out);
+
 /* Position-only rewind / reset (engine.py:651-654).  Synchronous small copies. */
 int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len);
 int32_t vuib_get_seq_len(VuibEngine* e, int32_t slot, int32_t* len);

@@ -285,8 +285,8 @@ def test_persistent_kernel_equals_per_phase_kernels(eng8):
     cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4)
     for lens, greedy in (([33], True), ([40, 150, 77], True), ([64, 200, 31], False)):
         outs = []
-        for off in ("", "1"):
-            os.environ["VUIB_NO_PERSISTENT"] = off
+        for on in ("1", ""):
+            os.environ["VUIB_PERSISTENT"] = on
             eng._graphs = {}
             eng.reset()
             eng._ws_reset_counters()
@@ -300,7 +300,7 @@ def test_persistent_kernel_equals_per_phase_kernels(eng8):
             eng.check_device()
             for r in rows:
                 r.close()
-        os.environ["VUIB_NO_PERSISTENT"] = ""
+        os.environ["VUIB_PERSISTENT"] = ""
         eng._graphs = {}
         for a, b in zip(outs[0], outs[1]):
             assert torch.equal(a, b), (lens, greedy)

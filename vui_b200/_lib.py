@@ -91,6 +91,7 @@ SYMBOLS = {
     "vuib_sample_rows": (C.c_int32, [_P, C.c_int32, _P, _P, C.c_int32, _P, _P]),
     "vuib_rep_reset": (C.c_int32, [_P, C.c_int32, _P]),
     "vuib_reset_state": (C.c_int32, [_P, _P]),
+    "vuib_read_trace": (C.c_int32, [_P, C.POINTER(C.c_uint64), C.c_int32, C.POINTER(C.c_int32)]),
     "vuib_set_seq_len": (C.c_int32, [_P, C.c_int32, C.c_int32]),
     "vuib_get_seq_len": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_int32)]),
     "vuib_check_device_flag": (C.c_int32, [_P, _P]),

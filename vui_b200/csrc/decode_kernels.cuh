@@ -292,10 +292,29 @@ struct EpiQkv {
     int max_seq;              // positions per slot in the cache
     const bf16* rope;         // (max_seq, 64, 2) or NULL
     int rows_per_b, pos_base; // used when row_slot == NULL
+    int kv_hint;              // 1: prefetch the K/V rows of the attention that follows into L2
     static constexpr int NC = 2;
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
         wr[0] = W + (size_t)(2 * item) * K;
         wr[1] = wr[0] + K;
+    }
+    // Warm L2 (and the TLB) with the K/V rows the attention kernel that follows will read: the
+    // rows before each stream's current position do not change during the frame.  The whole
+    // grid shares the work, one 128-byte line per thread and step.
+    __device__ __forceinline__ void hint(int M) const {
+        if (!row_slot || !kv_hint) return;
+        const size_t row_bytes = (size_t)kv_cols * sizeof(bf16);
+        const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+        for (int r = 0; r < M; ++r) {
+            const int slot = __ldcg(row_slot + r), pos = __ldcg(row_pos + r);
+            const size_t lines = (size_t)pos * row_bytes / 128;
+            const char* kb = reinterpret_cast<const char*>(k_cache) + (size_t)slot * max_seq * row_bytes;
+            const char* vb = reinterpret_cast<const char*>(v_cache) + (size_t)slot * max_seq * row_bytes;
+            for (size_t i = tid; i < 2 * lines; i += nth) {
+                const char* p = i < lines ? kb + i * 128 : vb + (i - lines) * 128;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+            }
+        }
     }
     template <int RT>
     __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
@@ -343,6 +362,7 @@ struct EpiResidual {
     int N;
     bf16* tap;      // optional copy of the new x (M, N)
     static constexpr int NC = 1;
+    __device__ __forceinline__ void hint(int) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = W + (size_t)item * K;
     }
@@ -366,6 +386,7 @@ struct EpiSwiGLU {
     bf16* act;  // (M, F)
     int F;
     static constexpr int NC = 2;
+    __device__ __forceinline__ void hint(int) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
         wr[0] = W1 + (size_t)item * K;
         wr[1] = W3 + (size_t)item * K;
@@ -393,6 +414,7 @@ struct EpiLogits {
     bf16* tap;            // optional second copy of out with its own row stride
     int tap_stride;
     static constexpr int NC = 1;
+    __device__ __forceinline__ void hint(int) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = item < n_main ? W + (size_t)item * K : W_extra;
     }
@@ -420,6 +442,7 @@ struct EpiProjPos {
     bf16* out;        // (rows_out, rd); row of stream b is b*row_mul
     int rd, row_mul;
     static constexpr int NC = 1;
+    __device__ __forceinline__ void hint(int) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = W + (size_t)item * K;
     }
@@ -462,6 +485,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(Stage st, Epi ep, int M, 
             }
     }
     pdl_wait();  // the weights above are constants; activations below come from the predecessor
+    ep.hint(M);
     for (int r0 = 0; r0 < M; r0 += RT) {
         const int nr = min(RT, M - r0);
         if (r0) __syncthreads();
@@ -520,7 +544,16 @@ struct AttnArgs {
     int32_t* counters;    // (R, Hkv), zero between launches
     bf16* out;            // (R, Hq*64)
     int Hq, Hkv, max_seq, S;
+    unsigned long long* dbg;  // optional: 8 device-clock stamps of one unit (profiling aid)
 };
+
+__device__ __forceinline__ void attn_stamp(const AttnArgs& a, int tid, int i) {
+    if (a.dbg && tid == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        a.dbg[i] = t;
+    }
+}
 
 __device__ __forceinline__ void softmax_merge(float& m, float& l, float (&acc)[8], float mo,
                                               float lo, const float (&ao)[8]) {
@@ -546,6 +579,7 @@ struct AttnSmem {
 // index within the group is `tid`; the group synchronises on named barrier bar_id.
 __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, int r, int tid,
                                           AttnSmem& S_, int bar_id) {
+    attn_stamp(a, tid, 0);
     const int len = __ldcg(a.row_pos + r) + 1;
     const int nsplit = (len + ATT_SPLIT - 1) / ATT_SPLIT;
     if (sp >= nsplit) return;
@@ -579,6 +613,7 @@ __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, in
         const int hq = kvh * G + (h < G ? h : 0);
         unpack8(__ldcg(reinterpret_cast<const uint4*>(a.q + (size_t)r * a.Hq * HD + hq * HD + s * 8)), qf[h]);
     }
+    attn_stamp(a, tid, 1);
     float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f}, acc[2][8];
 #pragma unroll
     for (int h = 0; h < 2; ++h)
@@ -614,6 +649,7 @@ __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, in
             }
         }
     }
+    attn_stamp(a, tid, 2);
     // merge the 4 key groups of the warp
 #pragma unroll
     for (int o = 8; o <= 16; o <<= 1) {
@@ -636,6 +672,7 @@ __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, in
             sm[warp][h][s][9] = l[h];
         }
     }
+    attn_stamp(a, tid, 3);
     bar_named(bar_id, ATT_THREADS);
     // thread (h, dim): merge the 4 warps
     const int h = tid >> 6, dim = tid & 63;
@@ -664,13 +701,16 @@ __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, in
             pp[HD + 1] = L_;
         }
     }
+    attn_stamp(a, tid, 4);
     __threadfence();
     bar_named(bar_id, ATT_THREADS);
+    attn_stamp(a, tid, 5);
     if (tid == 0) {
         const int old = atomicAdd(a.counters + r * a.Hkv + kvh, 1);
         s_last = (old == nsplit - 1);
     }
     bar_named(bar_id, ATT_THREADS);
+    attn_stamp(a, tid, 6);
     if (!s_last) return;
     __threadfence();
     if (head_ok) {

@@ -25,6 +25,13 @@ constexpr int PF_WARPS = PF_THREADS / 32;
 constexpr int PF_ATT_GROUPS = PF_THREADS / ATT_THREADS;
 constexpr unsigned BAR_SPIN_LIMIT = 1u << 21;  // ~1 s of polling at ~0.5 us per poll
 constexpr int FLAG_BARRIER_TIMEOUT = 8;
+constexpr int TRACE_MAX = 1024;  // barrier records kept per launch
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 struct DevModel {   // device-resident copy of the bound pointers
     VuibWeights w;
@@ -47,6 +54,7 @@ struct FrameBufs {  // workspace regions
     int32_t *rep_hist, *rep_head, *rep_filled;
     int32_t* flag;
     unsigned* bar;
+    unsigned long long* trace;  // [0] = entries written; then (arrive, release) globaltimer pairs of CTA 0
 };
 
 struct FrameArgs {
@@ -73,11 +81,15 @@ struct GridBarrier {
     unsigned n;
     int32_t* flag;
     bool dead;
+    unsigned long long* trace;  // CTA 0 only, may be NULL
+    unsigned n_sync;
     __device__ __forceinline__ void sync() {
         __syncthreads();
         if (threadIdx.x == 0) {
             target += n;
-            __threadfence();
+            const bool rec = trace && blockIdx.x == 0 && n_sync < TRACE_MAX;
+            if (rec) trace[1 + 2 * n_sync] = globaltimer_ns();
+            // release: the bar.sync above ordered the CTA's writes before this thread
             asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(counter), "r"(1u) : "memory");
             if (!dead) {
                 unsigned v, spins = 0;
@@ -91,7 +103,11 @@ struct GridBarrier {
                     }
                 }
             }
-            __threadfence();
+            if (rec) {
+                trace[2 + 2 * n_sync] = globaltimer_ns();
+                trace[0] = n_sync + 1;
+            }
+            ++n_sync;
         }
         __syncthreads();
     }
@@ -199,7 +215,7 @@ __device__ __forceinline__ void rq_layers_phase(const FrameArgs& a, GridBarrier&
         bf16* kc = b.rq_k + li * layer_kv;
         bf16* vc = b.rq_v + li * layer_kv;
         EpiQkv eq{static_cast<const bf16*>(m.w.rq_wqkv[li]), RD, b.rq_q, RD, RD, kc, vc,
-                  nullptr, nullptr, a.Q, nullptr, rows_per_b, pos_base};
+                  nullptr, nullptr, a.Q, nullptr, rows_per_b, pos_base, 0};
         WPref<RD, EpiQkv> wq;
         wprefetch<RD>(eq, 3 * RD / 2, wq);
         bar.sync();
@@ -239,7 +255,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_frame(FrameArgs a) {
     constexpr int D = 1024, F = 3072, RD = 512;
     const DevModel& m = *a.m;
     const FrameBufs& b = a.b;
-    GridBarrier bar{b.bar, 0u, gridDim.x, b.flag, false};
+    GridBarrier bar{b.bar, 0u, gridDim.x, b.flag, false, b.trace, 0u};
     const int B = a.B, cta = blockIdx.x, tid = threadIdx.x;
     const int qc = a.n_heads * HD, kvc = a.n_kv_heads * HD;
 
@@ -283,7 +299,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_frame(FrameArgs a) {
         for (int li = 0; li < a.n_layers; ++li) {
             EpiQkv eq{static_cast<const bf16*>(m.w.wqkv[li]), D, b.q, qc, kvc,
                       static_cast<bf16*>(m.k[li]), static_cast<bf16*>(m.v[li]),
-                      b.row_slot, b.row_pos, a.max_seq, m.rope, 1, 0};
+                      b.row_slot, b.row_pos, a.max_seq, m.rope, 1, 0, 0};
             WPref<D, EpiQkv> wq;
             wprefetch<D>(eq, (qc + 2 * kvc) / 2, wq);
             bar.sync();
@@ -297,7 +313,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_frame(FrameArgs a) {
             {   // attention: a group of 128 threads per (split, kv head, row) unit
                 AttnArgs aa{b.q, static_cast<const bf16*>(m.k[li]), static_cast<const bf16*>(m.v[li]),
                             b.row_slot, b.row_pos, b.part, b.counters, b.attn,
-                            a.n_heads, a.n_kv_heads, a.max_seq, a.S};
+                            a.n_heads, a.n_kv_heads, a.max_seq, a.S,
+                            (b.trace && cta == 1 && li == 5 && tid < ATT_THREADS) ? b.trace + 1 + 2 * TRACE_MAX : nullptr};
                 const int group = tid / ATT_THREADS, gt = tid % ATT_THREADS;
                 const int units = a.S * a.n_kv_heads * B;
                 for (int u = cta * PF_ATT_GROUPS + group; u < units; u += gridDim.x * PF_ATT_GROUPS) {

@@ -19,7 +19,7 @@ struct WsLayout {
     size_t flag, ctl, row_slot, row_pos, x, q, attn, act, part, counters;
     size_t rq_x2, rq_x, rq_q, rq_act, rq_k, rq_v, rq_logits, code_cur;
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
-    size_t bar, devmodel;
+    size_t bar, devmodel, trace;
     size_t total;
 };
 
@@ -89,11 +89,17 @@ static void make_layout(VuibEngine* e) {
     L.rep_filled = take((size_t)c.n_slots * 4);
     L.bar = take(256);
     L.devmodel = take(sizeof(DevModel));
+    L.trace = take((size_t)(1 + 2 * TRACE_MAX + 16) * 8);
     L.total = off;
 }
 
 // Launch with the programmatic-stream-serialization attribute (see pdl_wait in
 // decode_kernels.cuh) unless VUIB_NO_PDL is set in the environment.
+static bool env_off(const char* name) {
+    const char* s = getenv(name);
+    return s && s[0] && s[0] != '0';
+}
+
 static bool pdl_enabled() {
     static int v = -1;
     if (v < 0) {
@@ -337,12 +343,12 @@ static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
         StageNorm sn{x, static_cast<const bf16*>(e->w.attn_norm[li]), c.norm_eps, 1, 0};
         EpiQkv eq{static_cast<const bf16*>(e->w.wqkv[li]), d, q, qc, kvc,
                   static_cast<bf16*>(e->k[li]), static_cast<bf16*>(e->v[li]),
-                  row_slot, row_pos, c.max_seq, e->rope, 1, 0};
+                  row_slot, row_pos, c.max_seq, e->rope, 1, 0, env_off("VUIB_NO_KVHINT") ? 0 : 1};
         CK(VUIB_GEMV(d, e, sn, eq, M, (qc + 2 * kvc) / 2, s));
 
         AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
                     row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
-                    c.n_heads, c.n_kv_heads, c.max_seq, e->S};
+                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr};
         CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
         e->launches++;
         CK(cudaGetLastError());
@@ -458,7 +464,7 @@ static int32_t rq_layers(VuibEngine* e, int M, bf16* x, int rows_per_b, int pos_
         bf16* vc = wsp<bf16>(e, L.rq_v) + li * layer_kv;
         StageNorm sn{x, static_cast<const bf16*>(e->w.rq_attn_norm[li]), c.rq_norm_eps, 1, 0};
         EpiQkv eq{static_cast<const bf16*>(e->w.rq_wqkv[li]), rd, q, rd, rd, kc, vc,
-                  nullptr, nullptr, Q, nullptr, rows_per_b, pos_base};
+                  nullptr, nullptr, Q, nullptr, rows_per_b, pos_base, 0};
         CK(VUIB_GEMV(rd, e, sn, eq, M, 3 * rd / 2, s));
 
         StageRqAttn sa{q, kc, vc, c.rq_n_heads, Q, rows_per_b, pos_base};
@@ -561,15 +567,12 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
 // ---------------------------------------------------------------------------
 // Persistent frame kernel (frame_kernel.cuh): one launch per frame for B <= 8.
 // ---------------------------------------------------------------------------
-static bool env_off(const char* name) {
-    const char* s = getenv(name);
-    return s && s[0] && s[0] != '0';
-}
 
 static bool persistent_ok(VuibEngine* e, int B) {
     const VuibConfig& c = e->cfg;
+    // opt-in: with one sync point per GEMV it is not faster than the graph of per-phase kernels
     return B <= 8 && c.d_model == 1024 && c.ffn == 3072 && c.rq_d_model == 512 &&
-           (c.rq_ffn == 1408 || c.rq_ffn == 1536) && !env_off("VUIB_NO_PERSISTENT");
+           (c.rq_ffn == 1408 || c.rq_ffn == 1536) && env_off("VUIB_PERSISTENT");
 }
 
 typedef void (*FrameKernel)(FrameArgs);
@@ -629,6 +632,7 @@ static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const in
     b.rep_filled = wsp<int32_t>(e, L.rep_filled);
     b.flag = wsp<int32_t>(e, L.flag);
     b.bar = wsp<unsigned>(e, L.bar);
+    b.trace = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) : nullptr;
     fa.B = B;
     fa.slots = slots;
     fa.seq_inc = seq_inc;
@@ -728,7 +732,7 @@ extern "C" int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, 
     AttnArgs aa{static_cast<const bf16*>(q_dev), static_cast<const bf16*>(e->k[layer]),
                 static_cast<const bf16*>(e->v[layer]), row_slot_dev, row_pos_dev,
                 wsp<float>(e, e->lay.part), wsp<int32_t>(e, e->lay.counters), static_cast<bf16*>(out_dev),
-                c.n_heads, c.n_kv_heads, c.max_seq, e->S};
+                c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr};
     CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, n_rows), ATT_THREADS, 0, static_cast<cudaStream_t>(stream), aa));
     e->launches++;
     CK(cudaGetLastError());
@@ -807,6 +811,20 @@ extern "C" int32_t vuib_reset_state(VuibEngine* e, void* stream) {
     CK(cudaMemsetAsync(e->ws + L.frame_ctr, 0, (size_t)c.n_slots * 4, s));
     CK(cudaMemsetAsync(e->ws + L.bar, 0, 256, s));
     return vuib_rep_reset(e, -1, stream);
+}
+
+extern "C" int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t max_entries, int32_t* n_out) {
+    if (!e || !out_host || !n_out) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    unsigned long long n = 0;
+    CK(cudaMemcpy(&n, e->ws + e->lay.trace, 8, cudaMemcpyDeviceToHost));
+    if (n > (unsigned long long)TRACE_MAX) n = TRACE_MAX;
+    if ((long long)n > max_entries) n = max_entries;
+    if (n) CK(cudaMemcpy(out_host, e->ws + e->lay.trace + 8, n * 16, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(out_host + 2 * (size_t)max_entries, e->ws + e->lay.trace + 8 + (size_t)2 * TRACE_MAX * 8, 8 * 8,
+                  cudaMemcpyDeviceToHost));
+    *n_out = (int32_t)n;
+    return VUIB_OK;
 }
 
 extern "C" int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len) {
@@ -925,7 +943,7 @@ extern "C" int32_t vuib_attention_noalloc(int32_t n_heads, int32_t n_kv_heads, i
     AttnArgs aa{static_cast<const bf16*>(q_dev), static_cast<const bf16*>(k_cache_dev),
                 static_cast<const bf16*>(v_cache_dev), row_slot_dev, row_pos_dev,
                 reinterpret_cast<float*>(b), reinterpret_cast<int32_t*>(b + NA_PART_BYTES),
-                static_cast<bf16*>(out_dev), n_heads, n_kv_heads, max_seq, S};
+                static_cast<bf16*>(out_dev), n_heads, n_kv_heads, max_seq, S, nullptr};
     k_attn_decode<<<dim3(S, n_kv_heads, n_rows), ATT_THREADS, 0, s>>>(aa);
     rc = cudaGetLastError();
     if (rc != cudaSuccess)
