@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 BF16_ULP_AT_1 = 2.0 ** -7  # spacing of bf16 values in [1, 2)
 REL_TOL = 2e-2             # max-abs error / max-abs value against the fp32 result of the same algorithm
-REL_TOL_BF16 = 3e-2        # against another bf16 evaluation: both sit ~1.5e-2 from fp32 after 24 blocks
+REL_TOL_BF16 = 4e-2        # against another bf16 evaluation (both sit ~1.5-2e-2 from fp32 after 24 blocks; max over many frames)
 COS_TOL = 0.999
 
 
@@ -304,6 +304,64 @@ def test_persistent_kernel_equals_per_phase_kernels(eng8):
         eng._graphs = {}
         for a, b in zip(outs[0], outs[1]):
             assert torch.equal(a, b), (lens, greedy)
+
+
+def test_tensor_core_path_matches_gemv_path(nano_model, oracle_fp32):
+    """More than 8 rows run on the tcgen05 GEMM (TMA-fed, accumulators in tensor memory); up to 8
+    on the register-tile GEMV.  Same rounding points, different fp32 summation order: a 40-token
+    prefill must agree between the two and with the fp32 oracle within the bf16 tolerance, and a
+    16-stream decode step must agree with the same streams decoded one by one."""
+    from vui_b200 import Engine
+
+    eng = Engine(model=nano_model, max_rows=16, max_seq=256)
+    ids = _ids(40, 77)
+    outs = {}
+    for off in ("", "1"):
+        os.environ["VUIB_NO_TC"] = off
+        eng.reset()
+        row = eng.new_row()
+        outs[off] = eng._prefill_emb(row, eng.model.token_emb(ids[None]))[0].clone()
+        eng.check_device()
+        row.close()
+    os.environ["VUIB_NO_TC"] = ""
+    tc, gemv = outs[""], outs["1"]
+    oracle_fp32.seq_lens = [0]
+    ref = oracle_fp32.prefill_text(0, ids)
+    print(f"\n[tc vs gemv] prefill hidden: tc vs fp32 {_rel(tc, ref):.4f}, gemv vs fp32 {_rel(gemv, ref):.4f}, "
+          f"tc vs gemv {_rel(tc, gemv):.4f}")
+    # The maximum over 40x1024 elements after 24 blocks sits at 2-2.5e-2 from fp32 for ANY bf16
+    # evaluation (the GEMV path included), so the bound here is relative: the tensor-core result
+    # must be as close to fp32 as the GEMV result is, and both within the two-bf16-paths bound.
+    assert _cos(tc, ref) > COS_TOL and _cos(tc, gemv) > COS_TOL
+    assert _rel(tc, ref) < REL_TOL_BF16 and _rel(tc, ref) < 1.25 * _rel(gemv, ref) + 2e-3
+    assert _rel(tc, gemv) < REL_TOL_BF16
+    # 16 streams in one step (tensor cores) vs each alone (GEMV)
+    lens = [20 + 3 * i for i in range(16)]
+    eng.reset()
+    rows = [eng.new_row() for _ in lens]
+    hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 200 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
+    codes_in = torch.randint(0, 2048, (16, 16), generator=torch.Generator().manual_seed(9))
+    eng._g_codes_in.copy_(codes_in.cuda())
+    hidden_b, cb0_b, eos_b = (t.clone() for t in eng._decode_step())
+    torch.cuda.synchronize()
+    eng.check_device()
+    assert [r.offset for r in rows] == [n + 1 for n in lens]
+    eng1 = Engine(model=nano_model, max_rows=1, max_seq=256)
+    for i in (0, 7, 15):
+        eng1.reset()
+        r1 = eng1.new_row()
+        eng1.prefill_ids(r1, _ids(lens[i], 200 + i))
+        eng1._g_codes_in[0] = codes_in[i].cuda()
+        h1, c1, e1 = eng1._decode_step()
+        assert _rel(hidden_b[i], h1[0]) < REL_TOL_BF16 and _cos(hidden_b[i], h1[0]) > COS_TOL, i
+        assert _rel(cb0_b[i], c1[0]) < REL_TOL_BF16, i
+        r1.close()
+    # a whole sampled frame for 16 streams runs and yields valid codes
+    from vui_b200 import GenConfig
+    h = torch.stack([x[-1] for x in hs])
+    codes = eng.generate_frames(rows, h, 3, GenConfig(temperature=0.8, top_k=50, rep_penalty=1.0)).cpu()
+    eng.check_device()
+    assert codes.shape == (16, 3, 16) and codes.min() >= 0 and codes.max() < 2048
 
 
 def test_prefill_chunking_equals_single_call(eng8):

@@ -18,6 +18,7 @@ SOURCES = [os.path.join(_HERE, "csrc", "vuib200.cu")]
 HEADERS = [
     os.path.join(_HERE, "csrc", "decode_kernels.cuh"),
     os.path.join(_HERE, "csrc", "frame_kernel.cuh"),
+    os.path.join(_HERE, "csrc", "tc_gemm.cuh"),
     os.path.join(_ROOT, "include", "vuib200.h"),
 ]
 NVCC_FLAGS = [

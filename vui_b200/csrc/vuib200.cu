@@ -12,6 +12,7 @@
 
 #include "decode_kernels.cuh"
 #include "frame_kernel.cuh"
+#include "tc_gemm.cuh"
 
 using namespace vuib;
 
@@ -20,7 +21,19 @@ struct WsLayout {
     size_t rq_x2, rq_x, rq_q, rq_act, rq_k, rq_v, rq_logits, code_cur;
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
     size_t bar, devmodel, trace;
+    size_t xn, rq_xn, rq_attn, tc_partial, tc_counters;
     size_t total;
+};
+
+constexpr int TC_PARTIAL_TILES = 224;  // most (tile, split) pairs of one GEMM launch
+
+// Tensor maps (TMA descriptors) of every weight matrix, built when the weights are bound.
+struct TcMaps {
+    CUtensorMap wqkv[VUIB_MAX_LAYERS], out_proj[VUIB_MAX_LAYERS], w1[VUIB_MAX_LAYERS], w3[VUIB_MAX_LAYERS],
+        w2[VUIB_MAX_LAYERS];
+    CUtensorMap rq_wqkv[VUIB_MAX_LAYERS], rq_out[VUIB_MAX_LAYERS], rq_w1[VUIB_MAX_LAYERS], rq_w3[VUIB_MAX_LAYERS],
+        rq_w2[VUIB_MAX_LAYERS];
+    CUtensorMap codec_head, rq_proj, rq_head;
 };
 
 struct VuibEngine {
@@ -42,6 +55,7 @@ struct VuibEngine {
     DevModel dm;        // host copy of what the persistent kernel reads from the workspace
     int num_sms;        // 0 until the first persistent launch asks the device
     int coop;           // launch the frame kernel cooperatively
+    TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
     char err[256];
 };
 
@@ -90,6 +104,11 @@ static void make_layout(VuibEngine* e) {
     L.bar = take(256);
     L.devmodel = take(sizeof(DevModel));
     L.trace = take((size_t)(1 + 2 * TRACE_MAX + 16) * 8);
+    L.xn = take(R * (size_t)(c.ffn > c.d_model ? c.ffn : c.d_model) * 2);
+    L.rq_xn = take(2 * RB * rd * 2);
+    L.rq_attn = take(2 * RB * rd * 2);
+    L.tc_partial = take((size_t)TC_PARTIAL_TILES * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
+    L.tc_counters = take(256 * 4);
     L.total = off;
 }
 
@@ -127,6 +146,8 @@ static cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
 
 template <class T>
 static T* wsp(VuibEngine* e, size_t off) { return reinterpret_cast<T*>(e->ws + off); }
+
+static void build_tc_maps(VuibEngine* e);
 
 // The persistent frame kernel reads the bound pointers from a copy in the workspace.
 static int32_t sync_devmodel(VuibEngine* e) {
@@ -221,6 +242,7 @@ extern "C" int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out) {
 }
 
 extern "C" int32_t vuib_destroy(VuibEngine* e) {
+    if (e) delete e->tc;
     delete e;
     return VUIB_OK;
 }
@@ -264,6 +286,7 @@ extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
     if (!ok) return fail(e, VUIB_ERR_NULL, "a weight pointer is NULL");
     e->w = *w;
     e->have_w = true;
+    build_tc_maps(e);
     return sync_devmodel(e);
 }
 
@@ -326,10 +349,214 @@ extern "C" int32_t vuib_set_taps(VuibEngine* e, void* layer_hidden_dev, void* rq
     return VUIB_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// Tensor-core path (tc_gemm.cuh) for more than 8 rows: many streams, prefill.
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major (rows, cols) tensor, boxes of box_rows x 64 columns, 128-byte swizzle.
+static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {TC_KCHUNK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static void build_tc_maps(VuibEngine* e) {
+    delete e->tc;
+    e->tc = nullptr;
+    const VuibConfig& c = e->cfg;
+    if (c.d_model % 128 || c.ffn % 64 || c.rq_d_model % 128 || c.rq_ffn % 64 || c.codebook_size % 128) return;
+    TcMaps* t = new (std::nothrow) TcMaps();
+    if (!t) return;
+    bool ok = true;
+    const int d = c.d_model, qkv = (c.n_heads + 2 * c.n_kv_heads) * HD, rd = c.rq_d_model;
+    for (int i = 0; i < c.n_layers && ok; ++i) {
+        ok = ok && make_map(&t->wqkv[i], e->w.wqkv[i], qkv, d, 64) && make_map(&t->out_proj[i], e->w.out_proj[i], d, d, 64) &&
+             make_map(&t->w1[i], e->w.w1[i], c.ffn, d, 64) && make_map(&t->w3[i], e->w.w3[i], c.ffn, d, 64) &&
+             make_map(&t->w2[i], e->w.w2[i], d, c.ffn, 64);
+    }
+    for (int i = 0; i < c.rq_n_layers && ok; ++i) {
+        ok = ok && make_map(&t->rq_wqkv[i], e->w.rq_wqkv[i], 3 * rd, rd, 64) &&
+             make_map(&t->rq_out[i], e->w.rq_out_proj[i], rd, rd, 64) &&
+             make_map(&t->rq_w1[i], e->w.rq_w1[i], c.rq_ffn, rd, 64) &&
+             make_map(&t->rq_w3[i], e->w.rq_w3[i], c.rq_ffn, rd, 64) &&
+             make_map(&t->rq_w2[i], e->w.rq_w2[i], rd, c.rq_ffn, 64);
+    }
+    ok = ok && make_map(&t->codec_head, e->w.codec_head, c.codebook_size, d, 64) &&
+         make_map(&t->rq_proj, e->w.rq_backbone_proj, rd, d, 64) &&
+         make_map(&t->rq_head, e->w.rq_head, (uint64_t)(c.n_quantizers - 1) * c.codebook_size, rd, 64);
+    if (ok) e->tc = t;
+    else delete t;
+}
+
+static bool tc_ok(VuibEngine* e, int M) {
+    return M > 8 && e->tc && !env_off("VUIB_NO_TC");
+}
+
+// D = W X^T over all M rows in blocks of <= 256, epilogue ep (see tc_gemm.cuh).
+//  units: weight rows (N, multiple of 128) or, for the paired SwiGLU form, hidden units (multiple of 64).
+template <class Epi>
+static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& a1, const bf16* X, int M, int K,
+                       int units, int row_off, const Epi& ep, cudaStream_t s) {
+    const WsLayout& L = e->lay;
+    const int tiles = Epi::PAIRED ? units / 64 : units / TC_TILE_N;
+    const int chunks_total = K / TC_KCHUNK;
+    int splits = chunks_total;
+    for (int d = 1; d <= chunks_total; ++d)  // enough CTAs to keep HBM busy, few enough partial tiles to add up
+        if (chunks_total % d == 0 && tiles * d >= 64) { splits = d; break; }
+    while (tiles * splits > TC_PARTIAL_TILES && splits > 1) {  // stay inside the partial scratch
+        int d = splits - 1;
+        while (d > 1 && chunks_total % d) --d;
+        splits = d;
+    }
+    static bool attr_set = false;
+    const int max_smem = TC_MAX_STAGES * (TC_TILE_N * TC_KCHUNK * 2 + 256 * TC_KCHUNK * 2) + 1024;
+    if (!attr_set) {
+        CK(cudaFuncSetAttribute(k_gemm_tc<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        attr_set = true;
+    }
+    for (int m0 = 0; m0 < M; m0 += 256) {
+        const int Mb = M - m0 < 256 ? M - m0 : 256;
+        const int Mpad = (Mb + 15) / 16 * 16;
+        CUtensorMap mx;
+        if (!make_map(&mx, X + (size_t)m0 * K, Mb, K, Mpad)) return fail(e, VUIB_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+        TcArgs ta;
+        ta.N = units;
+        ta.row_off = row_off;
+        ta.M = Mb;
+        ta.Mpad = Mpad;
+        ta.chunks = chunks_total / splits;
+        ta.splits = splits;
+        ta.partial = wsp<float>(e, L.tc_partial);
+        ta.counters = wsp<int32_t>(e, L.tc_counters);
+        ta.flag = wsp<int32_t>(e, L.flag);
+        const int stages = ta.chunks < TC_MAX_STAGES ? ta.chunks : TC_MAX_STAGES;
+        size_t smem = (size_t)stages * (TC_TILE_N * TC_KCHUNK * 2 + ((Mpad * TC_KCHUNK * 2 + 1023) & ~1023));
+        smem += 1024;
+        CK(launch(k_gemm_tc<Epi>, dim3(tiles, splits), TC_THREADS, smem, s, a0, a1, mx, ta, ep.shifted(m0)));
+        e->launches++;
+    }
+    return VUIB_OK;
+}
+
+static int32_t norm_rows(VuibEngine* e, const bf16* x, const void* w, float eps, bf16* out, int M, int K, int row_mul,
+                         int row_add, cudaStream_t s) {
+    CK(launch(k_rmsnorm_rows, M, 128, 0, s, x, static_cast<const bf16*>(w), eps, out, K, row_mul, row_add));
+    e->launches++;
+    return VUIB_OK;
+}
+
+static int32_t run_layers_tc(VuibEngine* e, int M, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    bf16* x = wsp<bf16>(e, L.x);
+    bf16* xn = wsp<bf16>(e, L.xn);
+    bf16* q = wsp<bf16>(e, L.q);
+    bf16* attn = wsp<bf16>(e, L.attn);
+    bf16* act = wsp<bf16>(e, L.act);
+    const int32_t* row_slot = wsp<int32_t>(e, L.row_slot);
+    const int32_t* row_pos = wsp<int32_t>(e, L.row_pos);
+    const int d = c.d_model, qc = c.n_heads * HD, kvc = c.n_kv_heads * HD;
+    int32_t rc;
+    for (int li = 0; li < c.n_layers; ++li) {
+        if ((rc = norm_rows(e, x, e->w.attn_norm[li], c.norm_eps, xn, M, d, 1, 0, s))) return rc;
+        TcEpiQkv eq{q, qc, kvc, static_cast<bf16*>(e->k[li]), static_cast<bf16*>(e->v[li]), row_slot, row_pos,
+                    c.max_seq, e->rope, 1, 0, 0};
+        if ((rc = tc_gemm(e, e->tc->wqkv[li], e->tc->wqkv[li], xn, M, d, qc + 2 * kvc, 0, eq, s))) return rc;
+
+        AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
+                    row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
+                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr};
+        CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
+        e->launches++;
+
+        TcEpiResidual eo{x, d, nullptr};
+        if ((rc = tc_gemm(e, e->tc->out_proj[li], e->tc->out_proj[li], attn, M, qc, d, 0, eo, s))) return rc;
+
+        if ((rc = norm_rows(e, x, e->w.mlp_norm[li], c.norm_eps, xn, M, d, 1, 0, s))) return rc;
+        TcEpiSwiGLU eg{act, c.ffn};
+        if ((rc = tc_gemm(e, e->tc->w1[li], e->tc->w3[li], xn, M, d, c.ffn, 0, eg, s))) return rc;
+
+        bf16* tap = (e->tap_layers && M <= c.max_rows) ? e->tap_layers + (size_t)li * c.max_rows * d : nullptr;
+        TcEpiResidual ew{x, d, tap};
+        if ((rc = tc_gemm(e, e->tc->w2[li], e->tc->w2[li], act, M, c.ffn, d, 0, ew, s))) return rc;
+    }
+    return VUIB_OK;
+}
+
+static int32_t run_heads_tc(VuibEngine* e, int B, const bf16* hidden, bf16* cb0, bf16* eos, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    TcEpiLogits el{cb0, c.codebook_size, nullptr, 0};
+    int32_t rc = tc_gemm(e, e->tc->codec_head, e->tc->codec_head, hidden, B, c.d_model, c.codebook_size, 0, el, s);
+    if (rc) return rc;
+    CK(launch(k_eos_rows, (B + 3) / 4, 128, 0, s, hidden, static_cast<const bf16*>(e->w.eos_w),
+              static_cast<const bf16*>(e->w.eos_b), eos, B, c.d_model));
+    e->launches++;
+    return VUIB_OK;
+}
+
+static int32_t rq_layers_tc(VuibEngine* e, int M, bf16* x, int rows_per_b, int pos_base, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    const int rd = c.rq_d_model, Q = c.n_quantizers;
+    bf16* q = wsp<bf16>(e, L.rq_q);
+    bf16* act = wsp<bf16>(e, L.rq_act);
+    bf16* xn = wsp<bf16>(e, L.rq_xn);
+    bf16* attn = wsp<bf16>(e, L.rq_attn);
+    const size_t layer_kv = (size_t)c.max_rows * Q * rd;
+    int32_t rc;
+    for (int li = 0; li < c.rq_n_layers; ++li) {
+        bf16* kc = wsp<bf16>(e, L.rq_k) + li * layer_kv;
+        bf16* vc = wsp<bf16>(e, L.rq_v) + li * layer_kv;
+        if ((rc = norm_rows(e, x, e->w.rq_attn_norm[li], c.rq_norm_eps, xn, M, rd, 1, 0, s))) return rc;
+        TcEpiQkv eq{q, rd, rd, kc, vc, nullptr, nullptr, Q, nullptr, rows_per_b, pos_base, 0};
+        if ((rc = tc_gemm(e, e->tc->rq_wqkv[li], e->tc->rq_wqkv[li], xn, M, rd, 3 * rd, 0, eq, s))) return rc;
+
+        StageRqAttn sa{q, kc, vc, c.rq_n_heads, Q, rows_per_b, pos_base};
+        CK(launch(k_rq_attn_rows, M, 256, 0, s, sa, attn));
+        e->launches++;
+
+        TcEpiResidual eo{x, rd, nullptr};
+        if ((rc = tc_gemm(e, e->tc->rq_out[li], e->tc->rq_out[li], attn, M, rd, rd, 0, eo, s))) return rc;
+
+        if ((rc = norm_rows(e, x, e->w.rq_mlp_norm[li], c.rq_norm_eps, xn, M, rd, 1, 0, s))) return rc;
+        TcEpiSwiGLU eg{act, c.rq_ffn};
+        if ((rc = tc_gemm(e, e->tc->rq_w1[li], e->tc->rq_w3[li], xn, M, rd, c.rq_ffn, 0, eg, s))) return rc;
+
+        TcEpiResidual ew{x, rd, nullptr};
+        if ((rc = tc_gemm(e, e->tc->rq_w2[li], e->tc->rq_w2[li], act, M, c.rq_ffn, rd, 0, ew, s))) return rc;
+    }
+    return VUIB_OK;
+}
+
 // ---------------------------------------------------------------------------
 // Backbone: 24 blocks over M rows whose (slot, position) are in the workspace.
 // ---------------------------------------------------------------------------
 static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
+    if (tc_ok(e, M)) return run_layers_tc(e, M, s);
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
     bf16* x = wsp<bf16>(e, L.x);
@@ -373,6 +600,7 @@ static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
 
 static int32_t run_heads(VuibEngine* e, int B, const bf16* hidden, bf16* cb0, bf16* eos,
                          cudaStream_t s) {
+    if (tc_ok(e, B)) return run_heads_tc(e, B, hidden, cb0, eos, s);
     const VuibConfig& c = e->cfg;
     StageCopy sc{hidden};
     EpiLogits el{static_cast<const bf16*>(e->w.codec_head), c.d_model, c.codebook_size, cb0,
@@ -527,7 +755,12 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     bf16* x1 = wsp<bf16>(e, L.rq_x);
     const bf16* pos_emb = static_cast<const bf16*>(e->w.rq_pos_emb);
     const bf16* code_emb = static_cast<const bf16*>(e->w.rq_code_emb);
-    {
+    const bool tc = tc_ok(e, B);
+    int32_t rc;
+    if (tc) {
+        TcEpiProjPos ep{pos_emb, x2, rd, 2};
+        if ((rc = tc_gemm(e, e->tc->rq_proj, e->tc->rq_proj, hidden, B, c.d_model, rd, 0, ep, s))) return rc;
+    } else {
         StageCopy sc{hidden};
         EpiProjPos ep{static_cast<const bf16*>(e->w.rq_backbone_proj), c.d_model, pos_emb, x2, rd, 2};
         CK(VUIB_GEMV(c.d_model, e, sc, ep, B, rd, s));
@@ -535,7 +768,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     CK(launch(k_rq_embed, B, 64, 0, s, code_cur, code_emb, pos_emb, x2, rd, CS, 1, 2, 1));
     e->launches++;
     CK(cudaGetLastError());
-    int32_t rc = rq_layers(e, 2 * B, x2, 2, 0, s);
+    rc = tc ? rq_layers_tc(e, 2 * B, x2, 2, 0, s) : rq_layers(e, 2 * B, x2, 2, 0, s);
     if (rc) return rc;
 
     bf16* logits = wsp<bf16>(e, L.rq_logits);
@@ -545,14 +778,23 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
             CK(launch(k_rq_embed, B, 64, 0, s, code_cur, code_emb, pos_emb, x1, rd, CS, i + 1, 1, 0));
             e->launches++;
             CK(cudaGetLastError());
-            rc = rq_layers(e, B, x1, 1, i + 1, s);
+            rc = tc ? rq_layers_tc(e, B, x1, 1, i + 1, s) : rq_layers(e, B, x1, 1, i + 1, s);
             if (rc) return rc;
         }
-        StageNorm sn{i == 0 ? x2 : x1, static_cast<const bf16*>(e->w.rq_norm), c.rq_norm_eps,
-                     i == 0 ? 2 : 1, i == 0 ? 1 : 0};
-        EpiLogits el{head + (size_t)i * CS * rd, rd, CS, logits, nullptr, nullptr, nullptr,
-                     e->tap_rq ? e->tap_rq + (size_t)i * CS : nullptr, (Q - 1) * CS};
-        CK(VUIB_GEMV(rd, e, sn, el, B, CS, s));
+        if (tc) {
+            bf16* xn = wsp<bf16>(e, L.rq_xn);
+            if ((rc = norm_rows(e, i == 0 ? x2 : x1, e->w.rq_norm, c.rq_norm_eps, xn, B, rd, i == 0 ? 2 : 1,
+                                i == 0 ? 1 : 0, s)))
+                return rc;
+            TcEpiLogits el{logits, CS, e->tap_rq ? e->tap_rq + (size_t)i * CS : nullptr, (Q - 1) * CS};
+            if ((rc = tc_gemm(e, e->tc->rq_head, e->tc->rq_head, xn, B, rd, CS, i * CS, el, s))) return rc;
+        } else {
+            StageNorm sn{i == 0 ? x2 : x1, static_cast<const bf16*>(e->w.rq_norm), c.rq_norm_eps,
+                         i == 0 ? 2 : 1, i == 0 ? 1 : 0};
+            EpiLogits el{head + (size_t)i * CS * rd, rd, CS, logits, nullptr, nullptr, nullptr,
+                         e->tap_rq ? e->tap_rq + (size_t)i * CS : nullptr, (Q - 1) * CS};
+            CK(VUIB_GEMV(rd, e, sn, el, B, CS, s));
+        }
         sa.logits = logits;
         sa.codebook = i + 1;
         sa.out_col = i + 1;
@@ -853,7 +1095,7 @@ extern "C" int32_t vuib_check_device_flag(VuibEngine* e, void* stream) {
     CK(cudaStreamSynchronize(s));
     if (flag) {
         CK(cudaMemsetAsync(e->ws + e->lay.flag, 0, 4, s));
-        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code, 8 = grid barrier timed out)", flag);
+        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code, 8 = grid barrier timed out, 16 = tensor-core pipeline wait timed out)", flag);
     }
     return VUIB_OK;
 }
