@@ -236,8 +236,9 @@ int32_t vuib_reset_state(VuibEngine* e, void* stream);
 /* Profiling aid for the persistent frame kernel: when the environment variable VUIB_TRACE is
  * set, CTA 0 records the device clock (ns) when it arrives at and when it leaves each grid
  * barrier of the last launch.  Copies up to max_entries (arrive, leave) pairs to out_host
- * (2 uint64 each) and their count to *n_out, then 8 stamps taken inside one attention unit
- * to out_host[2*max_entries .. 2*max_entries+8).  out_host holds 2*max_entries+8 values.
+ * (2 uint64 each) and their count to *n_out, then 16 stamps taken inside one attention unit or
+ * tensor-core GEMM CTA to out_host[2*max_entries .. 2*max_entries+16).  out_host holds
+ * 2*max_entries+16 values.
  * Synchronous. */
 int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t max_entries, int32_t* n_out);
 

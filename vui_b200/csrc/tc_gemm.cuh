@@ -9,9 +9,12 @@
 //    accumulator tile lives in tensor memory and is read back with tcgen05.ld for the epilogue;
 //  * an mbarrier ring (full / empty per stage) decouples the TMA thread from the MMA thread; every
 //    wait is bounded and records FLAG_TC_TIMEOUT instead of hanging;
-//  * the grid is (weight tiles) x (K splits) so that ~all SMs stream weights even when N is small;
-//    split partial tiles go to scratch and the LAST CTA to finish a tile adds them in split order
-//    (deterministic) and runs the epilogue functor (RoPE + KV append, residual add, SwiGLU, logits);
+//  * one tcgen05.mma of this shape costs ~96 ns whatever the batch, i.e. an SM consumes weights at
+//    only ~42 GB/s, so the K dimension is split over enough CTAs to occupy every SM; the CTAs of a
+//    tile (all resident: the grid never exceeds the SM count times two) publish their partial tile,
+//    meet on a counter with a bounded wait, and EACH adds the splits - in index order, so the result
+//    is deterministic - for its own 1/splits slice of the rows and runs the epilogue functor there
+//    (RoPE + KV append, residual add, SwiGLU, logits);
 //  * launched with programmatic dependent launch: the weight tiles of the first stages are
 //    requested before the kernel waits for its predecessor, the activations after.
 // No TMA load here uses cluster multicast.
@@ -25,7 +28,8 @@ namespace vuib {
 constexpr int TC_THREADS = 128;
 constexpr int TC_TILE_N = 128;      // weight rows per CTA (two TMA boxes of 64 rows)
 constexpr int TC_KCHUNK = 64;       // bf16 per row per stage = 128 bytes = one swizzle span
-constexpr int TC_MAX_STAGES = 4;
+constexpr int TC_MAX_STAGES = 12;     // ring depth is set per launch from the shared memory left
+constexpr int TC_EPI_BYTES_PER_M = 256;  // epilogue staging per activation row (128 bf16)
 constexpr int FLAG_TC_TIMEOUT = 16;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
 
@@ -119,6 +123,17 @@ struct TcEpiQkv {      // RoPE on q,k + K/V append (EpiQkv of the GEMV path)
     int rows_per_b, pos_base;
     int m_off;  // row index of m = 0 in the depth-transformer addressing
     static constexpr bool PAIRED = false;
+    static constexpr bool STAGED = true;
+    // While the MMAs run: RoPE rows [cos,sin] x 64 of every activation row's position -> es[m][128].
+    __device__ __forceinline__ void stage(unsigned char* es, int tile, int M, int tid) const {
+        if (!rope) return;
+        uint4* dst = reinterpret_cast<uint4*>(es);
+        for (int i = tid; i < M * 16; i += TC_THREADS) {
+            const int m = i >> 4, c = i & 15;
+            const int pos = row_slot ? __ldcg(row_pos + m) : pos_base + (m + m_off) % rows_per_b;
+            dst[i] = __ldg(reinterpret_cast<const uint4*>(rope + (size_t)pos * HD * 2) + c);
+        }
+    }
     TcEpiQkv shifted(int m) const {
         TcEpiQkv o = *this;
         o.q_out += (size_t)m * q_cols;
@@ -126,35 +141,34 @@ struct TcEpiQkv {      // RoPE on q,k + K/V append (EpiQkv of the GEMV path)
         o.m_off += m;
         return o;
     }
-    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*) const {
+    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*,
+                                          const unsigned char* es) const {
         const bool odd = n & 1;
         const bool do_rope = rope && n < q_cols + kv_cols;
+        const bool to_cache = n >= q_cols;
         int slot[8], pos[8];
-        float c[8], sn[8];
+        if (to_cache) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {  // all loads first: they do not depend on one another
-            const int m = m0 + j < M ? m0 + j : (M > 0 ? M - 1 : 0);
-            if (row_slot) { slot[j] = __ldcg(row_slot + m); pos[j] = __ldcg(row_pos + m); }
-            else { slot[j] = (m + m_off) / rows_per_b; pos[j] = pos_base + (m + m_off) % rows_per_b; }
-        }
-        if (do_rope) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const __nv_bfloat162 f = *reinterpret_cast<const __nv_bfloat162*>(
-                    rope + ((size_t)pos[j] * HD + (n & (HD - 1))) * 2);
-                c[j] = __low2float(f);
-                sn[j] = __high2float(f);
+            for (int j = 0; j < 8; ++j) {  // loads first: they do not depend on one another
+                const int m = m0 + j < M ? m0 + j : (M > 0 ? M - 1 : 0);
+                if (row_slot) { slot[j] = __ldcg(row_slot + m); pos[j] = __ldcg(row_pos + m); }
+                else { slot[j] = (m + m_off) / rows_per_b; pos[j] = pos_base + (m + m_off) % rows_per_b; }
             }
         }
+        const __nv_bfloat162* rs = reinterpret_cast<const __nv_bfloat162*>(es);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int m = m0 + j;
             float t = rbf(v[j]);
             const float other = __shfl_xor_sync(0xffffffffu, t, 1);
             if (m >= M) continue;
-            if (do_rope) t = odd ? rbf(rbf(t * c[j]) + rbf(other * sn[j])) : rbf(rbf(t * c[j]) + rbf((-other) * sn[j]));
+            if (do_rope) {
+                const __nv_bfloat162 f = rs[m * 64 + (n & (HD - 1))];
+                const float c = __low2float(f), sn = __high2float(f);
+                t = odd ? rbf(rbf(t * c) + rbf(other * sn)) : rbf(rbf(t * c) + rbf((-other) * sn));
+            }
             const bf16 o = f2bf(t);
-            if (n < q_cols) q_out[(size_t)m * q_cols + n] = o;
+            if (!to_cache) q_out[(size_t)m * q_cols + n] = o;
             else if (n < q_cols + kv_cols) k_cache[((size_t)slot[j] * max_seq + pos[j]) * kv_cols + (n - q_cols)] = o;
             else v_cache[((size_t)slot[j] * max_seq + pos[j]) * kv_cols + (n - q_cols - kv_cols)] = o;
         }
@@ -164,23 +178,30 @@ struct TcEpiQkv {      // RoPE on q,k + K/V append (EpiQkv of the GEMV path)
 struct TcEpiResidual {  // x += bf16(acc)
     bf16* x; int N; bf16* tap;
     static constexpr bool PAIRED = false;
+    static constexpr bool STAGED = true;
+    // While the MMAs run: this tile's slice of the residual stream, x[m][tile*128 .. +128) -> es[m][128].
+    __device__ __forceinline__ void stage(unsigned char* es, int tile, int M, int tid) const {
+        uint4* dst = reinterpret_cast<uint4*>(es);
+        for (int i = tid; i < M * 16; i += TC_THREADS) {
+            const int m = i >> 4, c = i & 15;
+            dst[i] = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * N + tile * TC_TILE_N) + c);
+        }
+    }
     TcEpiResidual shifted(int m) const {
         TcEpiResidual o = *this;
         o.x += (size_t)m * N;
         if (tap) o.tap += (size_t)m * N;
         return o;
     }
-    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*) const {
-        unsigned short xb[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)  // the 8 residual values are fetched together, then added and stored
-            xb[j] = (m0 + j < M) ? __ldcg(reinterpret_cast<const unsigned short*>(x) + (size_t)(m0 + j) * N + n) : 0;
+    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*,
+                                          const unsigned char* es) const {
+        const bf16* xs = reinterpret_cast<const bf16*>(es);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int m = m0 + j;
             if (m >= M) continue;
             const size_t idx = (size_t)m * N + n;
-            const bf16 o = f2bf(bf2f(__ushort_as_bfloat16(xb[j])) + rbf(v[j]));
+            const bf16 o = f2bf(bf2f(xs[m * TC_TILE_N + (n & (TC_TILE_N - 1))]) + rbf(v[j]));
             x[idx] = o;
             if (tap) tap[idx] = o;
         }
@@ -190,40 +211,38 @@ struct TcEpiResidual {  // x += bf16(acc)
 struct TcEpiSwiGLU {    // tile rows 0..63 = w1 rows, 64..127 = w3 rows of the same hidden units
     bf16* act; int F;  // hidden unit of tile row r (< 64) is tile*64 + r
     static constexpr bool PAIRED = true;
+    static constexpr bool STAGED = false;
     TcEpiSwiGLU shifted(int m) const {
         TcEpiSwiGLU o = *this;
         o.act += (size_t)m * F;
         return o;
     }
-    __device__ __forceinline__ void apply(int n_global_unit, int r_local, int m0, int M, const float (&v)[8],
-                                          float* xchg /* [128][8] */) const {
+    // a1 = the unit's w1 sums, a3 = its w3 sums, for activation rows m0..m0+7
+    __device__ __forceinline__ void apply_pair(int unit, int m0, int M, const float (&a1)[8],
+                                               const float (&a3)[8]) const {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) xchg[r_local * 8 + j] = v[j];
-        __syncthreads();
-        if (r_local < 64) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int m = m0 + j;
-                if (m >= M) continue;
-                const float a = rbf(v[j]), g = rbf(xchg[(r_local + 64) * 8 + j]);
-                const float s = rbf(a / (1.0f + expf(-a)));
-                act[(size_t)m * F + n_global_unit] = f2bf(s * g);
-            }
+        for (int j = 0; j < 8; ++j) {
+            const int m = m0 + j;
+            if (m >= M) continue;
+            const float a = rbf(a1[j]), g = rbf(a3[j]);
+            const float sl = rbf(a / (1.0f + expf(-a)));
+            act[(size_t)m * F + unit] = f2bf(sl * g);
         }
-        __syncthreads();
     }
 };
 
 struct TcEpiLogits {    // plain bf16 rows (+ optional second copy with its own stride)
     bf16* out; int N; bf16* tap; int tap_stride;
     static constexpr bool PAIRED = false;
+    static constexpr bool STAGED = false;
     TcEpiLogits shifted(int m) const {
         TcEpiLogits o = *this;
         o.out += (size_t)m * N;
         if (tap) o.tap += (size_t)m * tap_stride;
         return o;
     }
-    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*) const {
+    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*,
+                                          const unsigned char*) const {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int m = m0 + j;
@@ -238,12 +257,14 @@ struct TcEpiLogits {    // plain bf16 rows (+ optional second copy with its own 
 struct TcEpiProjPos {   // depth position 0: bf16(acc) + pos_emb[0], written to row m*row_mul
     const bf16* pos_emb; bf16* out; int rd, row_mul;
     static constexpr bool PAIRED = false;
+    static constexpr bool STAGED = false;
     TcEpiProjPos shifted(int m) const {
         TcEpiProjPos o = *this;
         o.out += (size_t)m * row_mul * rd;
         return o;
     }
-    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*) const {
+    __device__ __forceinline__ void apply(int n, int m0, int M, const float (&v)[8], float*,
+                                          const unsigned char*) const {
         const float pe = bf2f(pos_emb[n]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -258,12 +279,23 @@ struct TcArgs {
     int N;            // weight rows, a multiple of 128 (PAIRED: hidden units, a multiple of 64)
     int row_off;      // first weight row of tile 0 inside the mapped matrix (stacked depth heads)
     int M, Mpad;      // activation rows, padded to a multiple of 16 (<= 256)
-    int chunks;       // K chunks of 64 handled by one CTA
-    int splits;       // gridDim.y
+    int chunks;       // K chunks of 64 in all; split s handles chunks [s*chunks/splits, (s+1)*chunks/splits)
+    int stages;       // TMA ring depth (<= TC_MAX_STAGES, <= chunks)
+    int splits;       // gridDim.x: 1, 2, 4, 8 or 16 (PAIRED: not 2)
     float* partial;   // (tiles, splits, 128, Mpad) fp32 scratch (splits > 1)
-    int32_t* counters;  // (tiles) zero between launches
+    int32_t* counters;  // (2, tiles) arrivals / departures, zero between launches
+    int tiles;
     int32_t* flag;
+    unsigned long long* dbg;  // optional: device-clock stamps of CTA (0,0) (profiling aid)
 };
+
+__device__ __forceinline__ void tc_stamp(const TcArgs& a, int i) {
+    if (a.dbg && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        a.dbg[i] = t;
+    }
+}
 
 template <class Epi>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -272,12 +304,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
     extern __shared__ unsigned char smem_dyn[];
     __shared__ uint64_t bar_full[TC_MAX_STAGES], bar_empty[TC_MAX_STAGES], bar_done;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_last, s_bad;
+    __shared__ int s_bad;
     __shared__ float xchg[Epi::PAIRED ? 128 * 8 : 1];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, split = blockIdx.y;
-    const int stages = a.chunks < TC_MAX_STAGES ? a.chunks : TC_MAX_STAGES;
+    const int split = blockIdx.x, tile = blockIdx.y;  // the CTAs of one tile are neighbours in launch order
+    tc_stamp(a, 0);
+    const int stages = a.stages;  // <= smallest chunk count of any split
     const uint32_t a_bytes = TC_TILE_N * TC_KCHUNK * 2, b_bytes = (uint32_t)a.Mpad * TC_KCHUNK * 2;
     const uint32_t stage_bytes = a_bytes + ((b_bytes + 1023u) & ~1023u);
     unsigned char* base = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -300,16 +333,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
+    tc_stamp(a, 1);
     // Only now may the next kernel's CTAs become resident: every CTA of this grid already owns its
     // tensor-memory columns, so early dependents can never starve it of them.
     pdl_trigger();
 
-    const int k_first = split * a.chunks;  // in chunks
+    const int k_first = (int)((long long)split * a.chunks / a.splits);  // in chunks
+    const int n_chunks = (int)((long long)(split + 1) * a.chunks / a.splits) - k_first;
     // weight rows of this tile: PAIRED -> 64 rows of each matrix at unit offset tile*64
     const int rowA0 = a.row_off + (Epi::PAIRED ? tile * 64 : tile * TC_TILE_N);
     const int rowA1 = a.row_off + (Epi::PAIRED ? tile * 64 : tile * TC_TILE_N + 64);
 
-    if (warp == 0 && lane == 0) {
+    // Roles are per warp: the 31 idle lanes of a role's warp park at __syncwarp(), not in an
+    // mbarrier wait, so they cannot hold back the lane that feeds the pipeline.
+    if (warp == 0) {
+      if (lane == 0) {
         // ---- TMA producer.  Weights for the first ring pass go out before the dependency wait.
         for (int c = 0; c < stages; ++c) {
             unsigned char* st = base + (size_t)c * stage_bytes;
@@ -320,7 +358,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
         pdl_wait();
         for (int c = 0; c < stages; ++c)
             tma_load_2d(base + (size_t)c * stage_bytes + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, 0, &bar_full[c]);
-        for (int c = stages; c < a.chunks; ++c) {
+        for (int c = stages; c < n_chunks; ++c) {
             const int s = c % stages;
             if (!mbar_wait(&bar_empty[s], ((c / stages) & 1) ^ 1)) { s_bad = 1; break; }
             unsigned char* st = base + (size_t)s * stage_bytes;
@@ -329,12 +367,20 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
             tma_load_2d(st + a_bytes / 2, &mapA1, (k_first + c) * TC_KCHUNK, rowA1, &bar_full[s]);
             tma_load_2d(st + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, 0, &bar_full[s]);
         }
-    } else if (warp == 1 && lane == 0) {
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      if (lane == 0) {
         // ---- MMA issuer
         const uint32_t idesc = umma_idesc_bf16(a.Mpad);
-        for (int c = 0; c < a.chunks; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
             const int s = c % stages;
             if (!mbar_wait(&bar_full[s], (c / stages) & 1)) { s_bad = 1; break; }
+            if (a.dbg && split == 0 && tile == 0 && c < 8) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                a.dbg[8 + c] = t;  // when chunk c (< 8) became available to the MMA thread
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             unsigned char* st = base + (size_t)s * stage_bytes;
             const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + a_bytes);
@@ -344,24 +390,39 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
             umma_commit(&bar_empty[s]);
         }
         umma_commit(&bar_done);
+      }
+      __syncwarp();
     }
-    if (warp != 0 || lane != 0) pdl_wait();
+    pdl_wait();
+    tc_stamp(a, 2);
+    unsigned char* es = base + (size_t)stages * stage_bytes;  // epilogue staging, filled while the MMAs run
+    if constexpr (Epi::STAGED) ep.stage(es, tile, a.M, tid);
     // ---- everyone: wait for the accumulator
     const bool done_ok = mbar_wait(&bar_done, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     if ((!done_ok || s_bad) && tid == 0) atomicOr(a.flag, FLAG_TC_TIMEOUT);
+    tc_stamp(a, 3);
 
-    const int r_local = tid;                                   // tile row = TMEM lane
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-    const int n_global = Epi::PAIRED ? tile * 64 + (r_local & 63) : tile * TC_TILE_N + r_local;
-
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);  // thread tid reads tile row tid (TMEM lane)
     if (a.splits == 1) {
         for (int m0 = 0; m0 < a.Mpad; m0 += 8) {
             float v[8];
             tmem_ld8(trow + m0, v);
-            if constexpr (Epi::PAIRED) ep.apply(n_global, r_local, m0, a.M, v, xchg);
-            else ep.apply(n_global, m0, a.M, v, xchg);
+            if constexpr (Epi::PAIRED) {  // rows r and r+64 are the w1 / w3 sums of hidden unit tile*64 + r
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xchg[tid * 8 + j] = v[j];
+                __syncthreads();
+                if (tid < 64) {
+                    float g[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) g[j] = xchg[(tid + 64) * 8 + j];
+                    ep.apply_pair(tile * 64 + tid, m0, a.M, v, g);
+                }
+                __syncthreads();
+            } else {
+                ep.apply(tile * TC_TILE_N + tid, m0, a.M, v, xchg, es);
+            }
         }
     } else {
         // partial tile to scratch as [m][n]: the 128 threads of a CTA write 512 contiguous bytes per m
@@ -370,44 +431,76 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
             float v[8];
             tmem_ld8(trow + m0, v);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) mine[(size_t)(m0 + j) * TC_TILE_N + r_local] = v[j];
+            for (int j = 0; j < 8; ++j) mine[(size_t)(m0 + j) * TC_TILE_N + tid] = v[j];
         }
+        tc_stamp(a, 4);
         __threadfence();
         __syncthreads();
         if (tid == 0) {
-            const int old = atomicAdd(a.counters + tile, 1);
-            s_last = (old == a.splits - 1);
+            // arrive, then wait (bounded) until every split of this tile has published its partial
+            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(a.counters + tile) : "memory");
+            int v = 0;
+            unsigned spins = 0;
+            for (;;) {
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.counters + tile) : "memory");
+                if (v >= a.splits) break;
+                if (++spins > (1u << 22)) { atomicOr(a.flag, FLAG_TC_TIMEOUT); break; }
+            }
         }
         __syncthreads();
-        if (s_last) {
-            __threadfence();
-            // The last CTA of the tile adds the splits in index order.  Thread n keeps its row: for
-            // every (split, m) the 128 threads read 512 contiguous bytes; 8 rows x up to 8 splits of
-            // loads are in flight before the first add.
-            const float* all = a.partial + (size_t)tile * a.splits * a.Mpad * TC_TILE_N + r_local;
-            const size_t split_stride = (size_t)a.Mpad * TC_TILE_N;
-            for (int m0 = 0; m0 < a.Mpad; m0 += 8) {
-                float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                for (int s0 = 0; s0 < a.splits; s0 += 8) {
-                    float p[8][8];
+        tc_stamp(a, 5);
+        // This CTA finishes 128/splits rows of the tile: thread = (row j of the slice, column group mg).
+        const int rpc = TC_TILE_N / a.splits;       // rows per CTA
+        const int j_row = tid % rpc, mg = tid / rpc;  // mg in [0, splits)
+        int row;                                      // row inside the tile
+        if constexpr (Epi::PAIRED) {
+            const int half = rpc / 2;                 // w1 rows, then the matching w3 rows (same warp)
+            row = j_row < half ? split * half + j_row : 64 + split * half + (j_row - half);
+        } else {
+            row = split * rpc + j_row;
+        }
+        const float* all = a.partial + (size_t)tile * a.splits * a.Mpad * TC_TILE_N + row;
+        const size_t split_stride = (size_t)a.Mpad * TC_TILE_N;
+        const int n_mchunks = a.Mpad / 8;
+        for (int chunk0 = 0; chunk0 < n_mchunks; chunk0 += a.splits) {  // uniform trip count: the
+            const bool active = chunk0 + mg < n_mchunks;                // epilogues shuffle within a warp
+            const int m0 = (active ? chunk0 + mg : n_mchunks - 1) * 8;
+            const int Meff = active ? a.M : 0;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int s0 = 0; s0 < a.splits; s0 += 8) {  // up to 64 loads in flight, summed in split order
+                float p[8][8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
+                for (int u = 0; u < 8; ++u)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            p[u][j] = (s0 + u < a.splits)
-                                          ? __ldcg(all + (size_t)(s0 + u) * split_stride + (size_t)(m0 + j) * TC_TILE_N)
-                                          : 0.f;
+                    for (int j = 0; j < 8; ++j)
+                        p[u][j] = (s0 + u < a.splits)
+                                      ? __ldcg(all + (size_t)(s0 + u) * split_stride + (size_t)(m0 + j) * TC_TILE_N)
+                                      : 0.f;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
+                for (int u = 0; u < 8; ++u)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] += p[u][j];
-                }
-                if constexpr (Epi::PAIRED) ep.apply(n_global, r_local, m0, a.M, v, xchg);
-                else ep.apply(n_global, m0, a.M, v, xchg);
+                    for (int j = 0; j < 8; ++j) v[j] += p[u][j];
             }
-            if (tid == 0) a.counters[tile] = 0;
+            if constexpr (Epi::PAIRED) {
+                const int half = rpc / 2;
+                float g[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[j] = __shfl_xor_sync(0xffffffffu, v[j], half);
+                if (j_row < half) ep.apply_pair(tile * 64 + row, m0, Meff, v, g);
+            } else {
+                ep.apply(tile * TC_TILE_N + row, m0, Meff, v, xchg, es);
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {  // the last CTA to leave re-arms both counters for the next launch
+            const int old = atomicAdd(a.counters + a.tiles + tile, 1);
+            if (old == a.splits - 1) {
+                a.counters[tile] = 0;
+                a.counters[a.tiles + tile] = 0;
+            }
         }
     }
+    tc_stamp(a, 6);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <unordered_set>
 
 #include "decode_kernels.cuh"
 #include "frame_kernel.cuh"
@@ -107,8 +108,8 @@ static void make_layout(VuibEngine* e) {
     L.xn = take(R * (size_t)(c.ffn > c.d_model ? c.ffn : c.d_model) * 2);
     L.rq_xn = take(2 * RB * rd * 2);
     L.rq_attn = take(2 * RB * rd * 2);
-    L.tc_partial = take((size_t)TC_PARTIAL_TILES * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
-    L.tc_counters = take(256 * 4);
+    L.tc_partial = take((size_t)(TC_PARTIAL_TILES + 80) * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
+    L.tc_counters = take(2 * 256 * 4);
     L.total = off;
 }
 
@@ -128,9 +129,22 @@ static bool pdl_enabled() {
     return v == 1;
 }
 
+// Every kernel of a frame asks for the same (largest) shared-memory carve-out.  The tensor-core
+// GEMM needs ~100-200 KB of shared memory and the small kernels between two GEMMs need almost
+// none; left to their own preferences the SMs would re-partition L1/shared memory at every
+// switch, which drains them and blocks the overlap of consecutive launches.
+static void prefer_max_smem(const void* kern) {
+    static std::mutex mu;
+    static std::unordered_set<const void*> done;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.insert(kern).second)
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 template <class... KArgs, class... Args>
 static cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
                           Args... args) {
+    prefer_max_smem(reinterpret_cast<const void*>(kern));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -424,16 +438,22 @@ static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& 
     const WsLayout& L = e->lay;
     const int tiles = Epi::PAIRED ? units / 64 : units / TC_TILE_N;
     const int chunks_total = K / TC_KCHUNK;
-    int splits = chunks_total;
-    for (int d = 1; d <= chunks_total; ++d)  // enough CTAs to keep HBM busy, few enough partial tiles to add up
-        if (chunks_total % d == 0 && tiles * d >= 64) { splits = d; break; }
-    while (tiles * splits > TC_PARTIAL_TILES && splits > 1) {  // stay inside the partial scratch
-        int d = splits - 1;
-        while (d > 1 && chunks_total % d) --d;
+    // Split K over enough CTAs to occupy the SMs (one MMA of this shape takes ~96 ns whatever the
+    // batch, so the tensor pipe of ONE SM consumes weights at only ~42 GB/s).  The CTAs of a tile
+    // meet on a counter, so the grid must be resident at once: at most two CTAs per SM.
+    if (e->num_sms == 0) {
+        int dev = 0;
+        CK(cudaGetDevice(&dev));
+        CK(cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    int splits = 1;
+    for (int d = 2; d <= 16; d *= 2) {
+        if (d > chunks_total || tiles * d > e->num_sms + e->num_sms / 2) break;
+        if (Epi::PAIRED && d == 2) continue;
         splits = d;
     }
     static bool attr_set = false;
-    const int max_smem = TC_MAX_STAGES * (TC_TILE_N * TC_KCHUNK * 2 + 256 * TC_KCHUNK * 2) + 1024;
+    const int max_smem = 202 * 1024;
     if (!attr_set) {
         CK(cudaFuncSetAttribute(k_gemm_tc<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         attr_set = true;
@@ -448,15 +468,24 @@ static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& 
         ta.row_off = row_off;
         ta.M = Mb;
         ta.Mpad = Mpad;
-        ta.chunks = chunks_total / splits;
+        ta.chunks = chunks_total;
         ta.splits = splits;
+        ta.tiles = tiles;
         ta.partial = wsp<float>(e, L.tc_partial);
         ta.counters = wsp<int32_t>(e, L.tc_counters);
         ta.flag = wsp<int32_t>(e, L.flag);
-        const int stages = ta.chunks < TC_MAX_STAGES ? ta.chunks : TC_MAX_STAGES;
-        size_t smem = (size_t)stages * (TC_TILE_N * TC_KCHUNK * 2 + ((Mpad * TC_KCHUNK * 2 + 1023) & ~1023));
-        smem += 1024;
-        CK(launch(k_gemm_tc<Epi>, dim3(tiles, splits), TC_THREADS, smem, s, a0, a1, mx, ta, ep.shifted(m0)));
+        ta.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) + 1 + 2 * TRACE_MAX : nullptr;
+        const int min_chunks = chunks_total / splits;  // the shortest split
+        const size_t stage_bytes = TC_TILE_N * TC_KCHUNK * 2 + ((Mpad * TC_KCHUNK * 2 + 1023) & ~1023);
+        const size_t epi_bytes = Epi::STAGED ? (size_t)Mpad * TC_EPI_BYTES_PER_M : 0;
+        // two CTAs per SM when split (all CTAs of the grid must be resident), the whole SM otherwise
+        const size_t budget = (splits > 1 ? 100 : 200) * 1024;
+        int stages = epi_bytes + stage_bytes <= budget ? (int)((budget - epi_bytes) / stage_bytes) : 1;
+        if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+        if (stages > min_chunks) stages = min_chunks;
+        ta.stages = stages;
+        const size_t smem = (size_t)stages * stage_bytes + epi_bytes + 1024;
+        CK(launch(k_gemm_tc<Epi>, dim3(splits, tiles), TC_THREADS, smem, s, a0, a1, mx, ta, ep.shifted(m0)));
         e->launches++;
     }
     return VUIB_OK;
@@ -1063,7 +1092,7 @@ extern "C" int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t ma
     if (n > (unsigned long long)TRACE_MAX) n = TRACE_MAX;
     if ((long long)n > max_entries) n = max_entries;
     if (n) CK(cudaMemcpy(out_host, e->ws + e->lay.trace + 8, n * 16, cudaMemcpyDeviceToHost));
-    CK(cudaMemcpy(out_host + 2 * (size_t)max_entries, e->ws + e->lay.trace + 8 + (size_t)2 * TRACE_MAX * 8, 8 * 8,
+    CK(cudaMemcpy(out_host + 2 * (size_t)max_entries, e->ws + e->lay.trace + 8 + (size_t)2 * TRACE_MAX * 8, 16 * 8,
                   cudaMemcpyDeviceToHost));
     *n_out = (int32_t)n;
     return VUIB_OK;
