@@ -111,6 +111,23 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
     for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive accumulator columns of this thread's TMEM lane in one instruction.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // ---------------------------------------------------------------------------
 // Epilogue functors.  A thread owns weight row n (0..127 of the tile) and is handed
 // 8 consecutive activation rows m0..m0+7 at a time (the whole CTA calls together).
@@ -427,15 +444,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
     } else {
         // partial tile to scratch as [m][n]: the 128 threads of a CTA write 512 contiguous bytes per m
         float* mine = a.partial + ((size_t)tile * a.splits + split) * a.Mpad * TC_TILE_N;
-        for (int m0 = 0; m0 < a.Mpad; m0 += 8) {
+        int m0 = 0;
+        for (; m0 + 32 <= a.Mpad; m0 += 32) {
+            float v[32];
+            tmem_ld32(trow + m0, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mine[(size_t)(m0 + j) * TC_TILE_N + tid] = v[j];
+        }
+        for (; m0 < a.Mpad; m0 += 8) {
             float v[8];
             tmem_ld8(trow + m0, v);
 #pragma unroll
             for (int j = 0; j < 8; ++j) mine[(size_t)(m0 + j) * TC_TILE_N + tid] = v[j];
         }
         tc_stamp(a, 4);
-        __threadfence();
-        __syncthreads();
+        __syncthreads();  // orders every thread's partial stores before thread 0's release below
         if (tid == 0) {
             // arrive, then wait (bounded) until every split of this tile has published its partial
             asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(a.counters + tile) : "memory");
