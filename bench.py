@@ -145,48 +145,41 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def run_b200(args):
+def measure(model, dev, rank, world, B, K, W, prompt_len, ragged, sample, max_seq_arg, phases=True):
+    """Prefill B streams, then time K frames device-resident and K frames end to end."""
     import torch
     import torch.distributed as dist
 
-    rank, local_rank, world = _dist_env()
-    if world > 1:
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    dev = torch.device("cuda", local_rank if world > 1 else 0)
-    torch.cuda.set_device(dev)
+    from vui_b200 import Engine, GenConfig
 
-    from vui_b200 import Engine, GenConfig, VuiB200, VuiShape
-
-    B, K, W = args.streams, args.steps, args.warmup
-    ceiling = VuiShape().max_seq_len
+    shape = model.shape
+    ceiling = shape.max_seq_len
     K = min(K, (ceiling - 513 - 2 * W - 40) // 2)  # both timed loops must fit the trained context
-    plen = 512 if args.ragged else args.prompt_len
-    max_seq = args.max_seq or 64 * ((plen + 2 * (K + W) + 16 + 63) // 64 + 1)
+    plen = 512 if ragged else prompt_len
+    max_seq = max_seq_arg or 64 * ((plen + 2 * (K + W) + 16 + 63) // 64 + 1)
     max_seq = max(max_seq, 1024) if B == 1 else max_seq
-    shape = VuiShape()
-    model = VuiB200.random_init(shape, seed=0, device=dev)
     eng = Engine(model=model, max_rows=B, max_seq=min(max_seq, model.decoder.max_seqlen), seed=1234 + rank)
     gen = torch.Generator().manual_seed(100 + rank)
-    if args.ragged:
+    if ragged:
         lens = torch.randint(64, 513, (B,), generator=torch.Generator().manual_seed(1)).tolist()
     else:
-        lens = [args.prompt_len] * B
+        lens = [prompt_len] * B
     rows = [eng.new_row() for _ in range(B)]
     embs = [(r, model.token_emb(torch.randint(0, shape.vocab_size, (1, n), generator=gen))) for r, n in zip(rows, lens)]
+    torch.cuda.synchronize(dev)
     t_pref0 = time.perf_counter()
     hs = eng._prefill_many(embs)
     torch.cuda.synchronize(dev)
     prefill_s = time.perf_counter() - t_pref0
     hidden = torch.stack([h[-1] for h in hs])
     cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.0)
-    greedy = not args.sample
+    greedy = not sample
     eng._apply_cfg(cfg, greedy=greedy)
     eng._g_slot_idx[:B] = torch.tensor([r.idx for r in rows], device=dev, dtype=torch.int32)
     eng._g_seq_inc[:B].fill_(1)
     eng._g_codes_in[:B] = eng._first_frames(rows, hidden)
     launches0 = eng.launch_count()
-    graph = eng._frame_graph(eng._buckets[-1] if B == eng.max_rows else B)
+    graph = eng._frame_graph(B)
     launches_per_frame = (eng.launch_count() - launches0) // 2  # one warm-up + one captured call
 
     def barrier():
@@ -200,7 +193,7 @@ def run_b200(args):
         graph.replay()
     seq_after_warm = eng.seq_lens.clone()
     codes_after_warm = eng._g_codes_in.clone()
-    sampler = ClockSampler(local_rank if world > 1 else 0)
+    sampler = ClockSampler(dev.index or 0)
     barrier()
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -235,10 +228,10 @@ def run_b200(args):
     # ---- phase split (eager, events): backbone step vs depth step ---------------
     eng.seq_lens.copy_(seq_after_warm)
     phase = {}
-    if rank == 0:
+    if rank == 0 and phases:
         P = lambda t: __import__("ctypes").c_void_p(t.data_ptr())  # noqa: E731
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        reps = 20
+        reps = 10
         tb = td = 0.0
         for _ in range(reps):
             e0.record()
@@ -255,16 +248,47 @@ def run_b200(args):
             td += e1.elapsed_time(e2)
         phase = {"backbone_ms_eager": tb / reps, "depth_ms_eager": td / reps}
 
-    # ---- aggregate over ranks ----------------------------------------------------
     from vui_b200.replicas import aggregate_rate
 
     fps, ms_max = aggregate_rate(B * K, ms, dev)
     e2e_fps, _ = aggregate_rate(B * K, e2e_s * 1e3, dev)
+    w_bytes = model.weight_bytes_per_step()
+    step_bytes = w_bytes + B * (GATHER_BYTES_PER_STREAM + KV_BYTES_PER_POS * (mean_T + 1))
+    res = {
+        "B": B, "K": K, "fps": fps, "e2e_fps": e2e_fps, "ms_per_step": ms_max / K, "lat": lat, "lens": lens,
+        "mean_T": mean_T, "max_seq": eng.max_seq, "prefill_s": prefill_s, "prefill_tokens": int(sum(lens)),
+        "launches_per_frame": launches_per_frame, "step_bytes": step_bytes, "phase": phase, "clocks": clocks,
+        "greedy": greedy,
+    }
+    del graph, eng
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, local_rank, world = _dist_env()
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank if world > 1 else 0)
+    torch.cuda.set_device(dev)
+
+    from vui_b200 import VuiB200, VuiShape
+
+    model = VuiB200.random_init(VuiShape(), seed=0, device=dev)
+    B, W = args.streams, args.warmup
+    m = measure(model, dev, rank, world, B, args.steps, W, args.prompt_len, args.ragged, args.sample, args.max_seq)
+    extra = None
+    if B == 1 and not args.no_batched:
+        # BASELINE config 3's shape beside the headline: 64 streams, prompts U[64,512], T=0.8 top-k 50
+        extra = measure(model, dev, rank, world, 64, min(args.steps, 100), W, 0, True, True, 0, phases=False)
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
-        w_bytes = model.weight_bytes_per_step()
-        step_bytes = w_bytes + B * (GATHER_BYTES_PER_STREAM + KV_BYTES_PER_POS * (mean_T + 1))
-        achieved = step_bytes / (ms_max / K * 1e-3) / 1e9
+        K, lat = m["K"], m["lat"]
+        achieved = m["step_bytes"] / (m["ms_per_step"] * 1e-3) / 1e9
         traffic = ncu_traffic().get(f"B{B}")
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
@@ -274,30 +298,42 @@ def run_b200(args):
                    "sample": "20 greedy frames after a 64-token prefill (BASELINE config 1 shape), "
                              "oracle/vui_oracle.py fp32 on torch CPU"}
         line = {
-            "metric": "codec frames/s", "value": fps, "unit": "frames/s", "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak",
+            "metric": "codec frames/s", "value": m["fps"], "unit": "frames/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "x_realtime": fps / FRAME_RATE,
+            "x_realtime": m["fps"] / FRAME_RATE,
             "config": {
-                "workload": (f"cfg2: B=1, {args.prompt_len} random text ids, greedy, KV<=1024" if B == 1 and greedy
+                "workload": (f"cfg2: B=1, {args.prompt_len} random text ids, greedy, KV<=1024" if B == 1 and m["greedy"]
                              else f"{B} streams/GPU, prompts {'U[64,512]' if args.ragged else args.prompt_len}, "
-                                  f"{'greedy' if greedy else 'T=0.8 top-k 50'}"),
-                "streams_per_gpu": B, "max_seq": eng.max_seq, "mean_kv_len": mean_T,
+                                  f"{'greedy' if m['greedy'] else 'T=0.8 top-k 50'}"),
+                "streams_per_gpu": B, "max_seq": m["max_seq"], "mean_kv_len": m["mean_T"],
                 "l2": "inputs larger than L2: 666 MB of weights are streamed every step",
-                "replicas": world, "prefill_s": prefill_s,
+                "replicas": world, "prefill_s": m["prefill_s"],
+                "prefill_tokens_per_s": m["prefill_tokens"] / m["prefill_s"],
             },
-            "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": B * 16 * 8,
+            "e2e": {"value": m["e2e_fps"], "unit": "frames/s", "h2d_bytes_per_step": B * 16 * 8,
                     "d2h_bytes_per_step": B * 16 * 8 + B * 4,
                     "p50_frame_latency_ms": 1e3 * lat[len(lat) // 2], "p95_frame_latency_ms": 1e3 * lat[int(len(lat) * 0.95)]},
-            "gpu_launches": launches_per_frame * K,
-            "launches_per_frame": launches_per_frame,
+            "gpu_launches": m["launches_per_frame"] * K,
+            "launches_per_frame": m["launches_per_frame"],
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
-                         "kernel": f"frame graph ({launches_per_frame} launches)",
-                         "bytes_per_step": step_bytes, **phase},
+                         "kernel": f"frame graph ({m['launches_per_frame']} launches)",
+                         "bytes_per_step": m["step_bytes"], **m["phase"]},
             "cpu_baseline": cpu,
-            "clocks": clocks,
+            "clocks": m["clocks"],
         }
+        if extra is not None:
+            ach = extra["step_bytes"] / (extra["ms_per_step"] * 1e-3) / 1e9
+            line["streams64"] = {
+                "workload": "cfg3: 64 streams/GPU, prompts U[64,512], T=0.8 top-k 50 (tcgen05 GEMM path)",
+                "value": extra["fps"], "unit": "frames/s (aggregate)", "x_realtime": extra["fps"] / FRAME_RATE,
+                "ms_per_step": extra["ms_per_step"], "steps": extra["K"], "e2e": extra["e2e_fps"],
+                "p50_frame_latency_ms": 1e3 * extra["lat"][len(extra["lat"]) // 2],
+                "launches_per_frame": extra["launches_per_frame"], "mean_kv_len": extra["mean_T"],
+                "prefill_tokens_per_s": extra["prefill_tokens"] / extra["prefill_s"],
+                "roofline_frac": ach / peak, "bytes_per_step": extra["step_bytes"],
+            }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -316,6 +352,7 @@ def main():
     ap.add_argument("--ragged", action="store_true", help="prompt lengths U[64,512] (config 3)")
     ap.add_argument("--sample", action="store_true", help="T=0.8 top-k 50 instead of greedy")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-batched", action="store_true", help="skip the extra 64-stream measurement")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
