@@ -306,6 +306,42 @@ def test_persistent_kernel_equals_per_phase_kernels(eng8):
             assert torch.equal(a, b), (lens, greedy)
 
 
+def test_cluster_depth_kernel_equals_per_phase_kernels(eng8):
+    """The depth step as one kernel on a 16-CTA cluster (activations exchanged through distributed
+    shared memory) gives, bit for bit, the codes and depth logits of the per-phase kernels:
+    greedy and sampled, B = 1 and ragged B = 3, and with fewer codebooks."""
+    from vui_b200 import GenConfig
+
+    eng = eng8
+    tap = torch.zeros(8, 15, 2048, device="cuda", dtype=torch.bfloat16)
+    cases = [([33], True, 0), ([40, 150, 77], True, 0), ([64, 200, 31, 90], False, 0), ([50, 60], True, 10)]
+    for lens, greedy, ncb in cases:
+        cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4, n_codebooks=ncb)
+        outs = []
+        for on in ("1", ""):
+            os.environ["VUIB_CLUSTER"] = on
+            eng._set_taps(None, tap)
+            tap.zero_()
+            eng.reset()
+            eng._ws_reset_counters()
+            rows = [eng.new_row() for _ in lens]
+            hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 70 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
+            h = torch.stack([x[-1] for x in hs])
+            codes = eng.generate_frames(rows, h, 5, cfg, greedy=greedy).cpu()
+            torch.cuda.synchronize()
+            outs.append((codes, tap[: len(lens)].clone(), eng._g_eos_prob[: len(lens)].clone(),
+                         eng._g_hidden_out[: len(lens)].clone()))  # rows past len(lens) are bucket padding
+            eng.check_device()
+            for r in rows:
+                r.close()
+        os.environ["VUIB_CLUSTER"] = ""
+        eng._set_taps(None, None)
+        for a, b in zip(outs[0], outs[1]):
+            assert torch.equal(a, b), (lens, greedy, ncb)
+        if ncb:
+            assert (outs[0][0][:, :, ncb:] == 0).all()
+
+
 def test_tensor_core_path_matches_gemv_path(nano_model, oracle_fp32):
     """More than 8 rows run on the tcgen05 GEMM (TMA-fed, accumulators in tensor memory); up to 8
     on the register-tile GEMV.  Same rounding points, different fp32 summation order: a 40-token

@@ -19,6 +19,7 @@ HEADERS = [
     os.path.join(_HERE, "csrc", "decode_kernels.cuh"),
     os.path.join(_HERE, "csrc", "frame_kernel.cuh"),
     os.path.join(_HERE, "csrc", "tc_gemm.cuh"),
+    os.path.join(_HERE, "csrc", "depth_cluster.cuh"),
     os.path.join(_ROOT, "include", "vuib200.h"),
 ]
 NVCC_FLAGS = [

@@ -14,6 +14,7 @@
 #include "decode_kernels.cuh"
 #include "frame_kernel.cuh"
 #include "tc_gemm.cuh"
+#include "depth_cluster.cuh"
 
 using namespace vuib;
 
@@ -951,6 +952,82 @@ static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const in
     return VUIB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Depth step on one 16-CTA cluster (depth_cluster.cuh): one launch for B <= 4.
+// ---------------------------------------------------------------------------
+// Opt-in (VUIB_CLUSTER=1): bit-identical to the per-phase kernels but not faster.  On 16 SMs the
+// step is bound by instruction issue (~100 warp instructions per 512-long dot product, 23.5 k
+// dot products per codebook), 86 us per codebook against 53 us for the launch-bound graph.
+static bool cluster_ok(VuibEngine* e, int B) {
+    const VuibConfig& c = e->cfg;
+    return B <= 4 && c.d_model == 1024 && c.rq_d_model == 512 && c.rq_n_heads == 8 &&
+           (c.rq_ffn == 1408 || c.rq_ffn == 1536) && c.codebook_size == 2048 && env_off("VUIB_CLUSTER");
+}
+
+typedef void (*DepthKernel)(DepthArgs);
+
+static int32_t launch_depth_cluster(VuibEngine* e, int B, const int32_t* slots, const bf16* hidden,
+                                    const bf16* cb0, const bf16* eos, int first_frame, int64_t* codes_out,
+                                    float* eos_prob, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    DepthArgs da;
+    memset(&da, 0, sizeof(da));
+    da.m = wsp<DevModel>(e, L.devmodel);
+    FrameBufs& b = da.b;
+    b.rq_k = wsp<bf16>(e, L.rq_k);
+    b.rq_v = wsp<bf16>(e, L.rq_v);
+    b.rq_logits = wsp<bf16>(e, L.rq_logits);
+    b.code_cur = wsp<int32_t>(e, L.code_cur);
+    b.ctl = wsp<SamplingCtl>(e, L.ctl);
+    b.frame_ctr = wsp<int32_t>(e, L.frame_ctr);
+    b.rep_counts = wsp<float>(e, L.rep_counts);
+    b.rep_hist = wsp<int32_t>(e, L.rep_hist);
+    b.rep_head = wsp<int32_t>(e, L.rep_head);
+    b.rep_filled = wsp<int32_t>(e, L.rep_filled);
+    b.flag = wsp<int32_t>(e, L.flag);
+    da.B = B;
+    da.slots = slots;
+    da.hidden = hidden;
+    da.cb0_logits = cb0;
+    da.eos_logit = eos;
+    da.eos_prob = eos_prob;
+    da.codes_out = codes_out;
+    da.tap_rq = e->tap_rq;
+    da.Q = c.n_quantizers;
+    da.CS = c.codebook_size;
+    da.rq_n_layers = c.rq_n_layers;
+    da.rq_n_heads = c.rq_n_heads;
+    da.max_rows = c.max_rows;
+    da.rq_norm_eps = c.rq_norm_eps;
+    da.n_codebooks = e->samp.n_codebooks > 0 ? e->samp.n_codebooks : c.n_quantizers;
+    da.first_frame = first_frame;
+    da.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) + 1 + 2 * TRACE_MAX : nullptr;
+    const int rt = B <= 1 ? 1 : B <= 2 ? 2 : 4;
+    DepthKernel kern;
+    if (c.rq_ffn == 1408) kern = rt == 1 ? k_depth_cluster<1, 1408> : rt == 2 ? k_depth_cluster<2, 1408> : k_depth_cluster<4, 1408>;
+    else kern = rt == 1 ? k_depth_cluster<1, 1536> : rt == 2 ? k_depth_cluster<2, 1536> : k_depth_cluster<4, 1536>;
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    prefer_max_smem(reinterpret_cast<const void*>(kern));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(DC_CTAS);
+    cfg.blockDim = dim3(DC_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = DC_CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    CK(cudaLaunchKernelEx(&cfg, kern, da));
+    e->launches++;
+    return VUIB_OK;
+}
+
 extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
                                    const void* hidden_dev, const void* cb0_logits_dev,
                                    const void* eos_logit_dev, int32_t first_frame,
@@ -960,6 +1037,10 @@ extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slot
     if (!slots_dev || !hidden_dev || !cb0_logits_dev || !codes_out_dev) return VUIB_ERR_NULL;
     if (B < 1 || B > e->cfg.max_rows)
         return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    if (!persistent_ok(e, B) && cluster_ok(e, B))
+        return launch_depth_cluster(e, B, slots_dev, static_cast<const bf16*>(hidden_dev),
+                                    static_cast<const bf16*>(cb0_logits_dev), static_cast<const bf16*>(eos_logit_dev),
+                                    first_frame, codes_out_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
     if (persistent_ok(e, B))
         return launch_frame(e, B, slots_dev, nullptr, codes_out_dev,
                             const_cast<bf16*>(static_cast<const bf16*>(hidden_dev)),
@@ -987,6 +1068,10 @@ extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* sl
     rc = vuib_backbone_step(e, B, slots_dev, seq_inc_dev, codes_io_dev, hidden_out_dev,
                             cb0_out_dev, eos_out_dev, stream);
     if (rc) return rc;
+    if (cluster_ok(e, B))
+        return launch_depth_cluster(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
+                                    static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
+                                    codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
     return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
                      static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
                      codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
