@@ -702,26 +702,43 @@ __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, in
         }
     }
     attn_stamp(a, tid, 4);
-    __threadfence();
-    bar_named(bar_id, ATT_THREADS);
+    bar_named(bar_id, ATT_THREADS);  // every thread's partial stores precede thread 0's release below
     attn_stamp(a, tid, 5);
     if (tid == 0) {
-        const int old = atomicAdd(a.counters + r * a.Hkv + kvh, 1);
+        int old;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.counters + r * a.Hkv + kvh) : "memory");
         s_last = (old == nsplit - 1);
     }
     bar_named(bar_id, ATT_THREADS);
     attn_stamp(a, tid, 6);
     if (!s_last) return;
-    __threadfence();
     if (head_ok) {
+        // merge the splits in index order; 16 splits' worth of loads are in flight at a time
         const float* pb = a.part + ((size_t)r * a.Hq + hq) * a.S * PART_STRIDE;
-        float Mx = NEG_BIG;
-        for (int i = 0; i < nsplit; ++i) Mx = fmaxf(Mx, __ldcg(pb + i * PART_STRIDE + HD));
-        float Ls = 0.f, Os = 0.f;
-        for (int i = 0; i < nsplit; ++i) {
-            const float c = __expf(__ldcg(pb + i * PART_STRIDE + HD) - Mx);
-            Ls += __ldcg(pb + i * PART_STRIDE + HD + 1) * c;
-            Os += __ldcg(pb + i * PART_STRIDE + dim) * c;
+        float Mx = NEG_BIG, Ls = 0.f, Os = 0.f;
+        for (int i0 = 0; i0 < nsplit; i0 += 16) {
+            float ms[16], ls[16], os[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const bool ok = i0 + u < nsplit;
+                const float* q = pb + (size_t)(ok ? i0 + u : i0) * PART_STRIDE;
+                ms[u] = ok ? __ldcg(q + HD) : NEG_BIG;
+                ls[u] = ok ? __ldcg(q + HD + 1) : 0.f;
+                os[u] = ok ? __ldcg(q + dim) : 0.f;
+            }
+            float Mn = Mx;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) Mn = fmaxf(Mn, ms[u]);
+            const float c0 = __expf(Mx - Mn);
+            Ls *= c0;
+            Os *= c0;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const float c = __expf(ms[u] - Mn);
+                Ls += ls[u] * c;
+                Os += os[u] * c;
+            }
+            Mx = Mn;
         }
         a.out[(size_t)r * a.Hq * HD + hq * HD + dim] = f2bf(Os / Ls);
     }
@@ -846,6 +863,13 @@ struct SampleArgs {
     float* eos_prob;          // (B)
     int bump_frame;           // last sampler of the frame advances frame_ctr
     int zero_from;            // >0: also zero codes_out[r, zero_from..Q)
+    // optional: also build the depth token the next codebook consumes,
+    // emb_out[r*emb_row_mul + emb_row_add] = code_emb[(emb_p-1)*CS + code] + pos_emb[emb_p]
+    // (model.py:922-925, 967-969)
+    bf16* emb_out;
+    const bf16* code_emb;
+    const bf16* pos_emb;
+    int emb_p, emb_rd, emb_row_mul, emb_row_add;
 };
 
 struct SampleSmem {
@@ -1033,6 +1057,19 @@ __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, S
             }
         }
         if (a.bump_frame) a.frame_ctr[slot] += 1;
+    }
+    if (a.emb_out) {
+        const bf16* e = a.code_emb + ((size_t)(a.emb_p - 1) * CS + choice) * a.emb_rd;
+        const bf16* pe = a.pos_emb + (size_t)a.emb_p * a.emb_rd;
+        bf16* o = a.emb_out + ((size_t)r * a.emb_row_mul + a.emb_row_add) * a.emb_rd;
+        for (int k = tid * 8; k < a.emb_rd; k += SAMPLE_THREADS * 8) {
+            float x[8], c[8], sum[8];
+            unpack8(__ldg(reinterpret_cast<const uint4*>(e + k)), x);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(pe + k)), c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] = x[j] + c[j];
+            *reinterpret_cast<uint4*>(o + k) = pack8(sum);
+        }
     }
     return choice;
 }

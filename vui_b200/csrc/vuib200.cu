@@ -772,6 +772,14 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     sa.eos_prob = eos_prob;
     sa.bump_frame = 0;
     sa.zero_from = Qn < Q ? Qn : 0;
+    // the sampler also builds depth position 1 from the code it drew (rows 2b+1)
+    sa.emb_out = wsp<bf16>(e, L.rq_x2);
+    sa.code_emb = static_cast<const bf16*>(e->w.rq_code_emb);
+    sa.pos_emb = static_cast<const bf16*>(e->w.rq_pos_emb);
+    sa.emb_p = 1;
+    sa.emb_rd = rd;
+    sa.emb_row_mul = 2;
+    sa.emb_row_add = 1;
     CK(launch(k_sample, B, SAMPLE_THREADS, 0, s, sa));
     e->launches++;
     CK(cudaGetLastError());
@@ -795,9 +803,6 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
         EpiProjPos ep{static_cast<const bf16*>(e->w.rq_backbone_proj), c.d_model, pos_emb, x2, rd, 2};
         CK(VUIB_GEMV(c.d_model, e, sc, ep, B, rd, s));
     }
-    CK(launch(k_rq_embed, B, 64, 0, s, code_cur, code_emb, pos_emb, x2, rd, CS, 1, 2, 1));
-    e->launches++;
-    CK(cudaGetLastError());
     rc = tc ? rq_layers_tc(e, 2 * B, x2, 2, 0, s) : rq_layers(e, 2 * B, x2, 2, 0, s);
     if (rc) return rc;
 
@@ -805,9 +810,6 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     const bf16* head = static_cast<const bf16*>(e->w.rq_head);
     for (int i = 0; i < Qn - 1; ++i) {
         if (i > 0) {
-            CK(launch(k_rq_embed, B, 64, 0, s, code_cur, code_emb, pos_emb, x1, rd, CS, i + 1, 1, 0));
-            e->launches++;
-            CK(cudaGetLastError());
             rc = tc ? rq_layers_tc(e, B, x1, 1, i + 1, s) : rq_layers(e, B, x1, 1, i + 1, s);
             if (rc) return rc;
         }
@@ -829,6 +831,10 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
         sa.codebook = i + 1;
         sa.out_col = i + 1;
         sa.bump_frame = (i == Qn - 2);
+        sa.emb_out = (i + 1 < Qn - 1) ? x1 : nullptr;  // token of depth position i+2 for the next codebook
+        sa.emb_p = i + 2;
+        sa.emb_row_mul = 1;
+        sa.emb_row_add = 0;
         CK(launch(k_sample, B, SAMPLE_THREADS, 0, s, sa));
         e->launches++;
         CK(cudaGetLastError());
