@@ -86,13 +86,13 @@ def measured_hbm_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+# DRAM bytes per frame (dram__bytes_read.sum + dram__bytes_write.sum over the launches of one frame)
+# from the ncu capture summarised in profiles/frame_graph_b1_dram_traffic.md.
+NCU_TRAFFIC_BYTES_PER_FRAME = {1: 943177216}
+
+
 def ncu_traffic():
-    """DRAM bytes per frame from the committed ncu summary, if one was recorded."""
-    p = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(p):
-        with open(p) as f:
-            return json.load(f)
-    return {}
+    return {f"B{b}": v for b, v in NCU_TRAFFIC_BYTES_PER_FRAME.items()}
 
 
 def cpu_oracle_frames_per_s(prompt_len: int, n_frames: int, threads: int):
