@@ -1,0 +1,113 @@
+"""The reference-facing Python API (Engine / Row / GenConfig / Segment / RenderRequest) end to
+end on the GPU with a stand-in tokenizer (the reference's downloads BPE files) and no codec:
+the calls of docs/python-api.md in the reference, checked for shapes, ranges, bookkeeping."""
+import zlib
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+class StubTok:
+    """Deterministic word-hash tokenizer with the attributes Engine reads."""
+
+    vocab_size = 151936
+
+    def __init__(self):
+        self.special_to_id = {"[SC]": 151900}
+
+    def encode(self, text: str):
+        ids = [zlib.crc32(w.encode()) % 151000 for w in text.split()]
+        return torch.tensor(ids or [1], dtype=torch.long)
+
+
+@pytest.fixture(scope="module")
+def model_tok(nano_sd):
+    from vui_b200 import VuiB200, VuiShape
+
+    return VuiB200(VuiShape(), nano_sd, device="cuda", tokenizer=StubTok())
+
+
+def _prompt_codes(n, seed):
+    return torch.randint(0, 2048, (n, 16), generator=torch.Generator().manual_seed(seed))
+
+
+def test_row_render_and_rewind(model_tok):
+    from vui_b200 import Engine, GenConfig, Segment
+
+    eng = Engine(model=model_tok, max_rows=1, max_seq=1024)
+    cfg = GenConfig(temperature=0.9, max_secs=4.0, min_secs=0.2, eos_threshold=0.99)
+    with eng.new_row() as row:
+        off = row.prefill([Segment("A short voice prompt, spoken calmly.", _prompt_codes(20, 1))])
+        # [SC] + 6 text tokens + 20 audio positions (no speaker projection in this checkpoint)
+        assert off == row.offset == 6 + 1 + 20
+        assert abs(row.prompt_wps - 6 / (20 / 12.5)) < 1e-6
+        codes, audio = row.render("Hello there, this is a test of the engine. It speaks two sentences.", cfg)
+        assert audio is None  # no codec attached
+        assert codes.dtype == torch.long and codes.shape[1] == 16 and 1 <= codes.shape[0] <= 50
+        assert codes.min() >= 0 and codes.max() < 2048
+        assert row.offset > off
+        assert row.rewind() == off and row.offset == off
+        again, _ = row.render("Hello there, this is a test of the engine. It speaks two sentences.", cfg)
+        assert again.shape[1] == 16
+        assert row.reset() == 0 and row.offset == 0
+    eng.check_device()
+    with pytest.raises(RuntimeError):
+        eng2 = Engine(model=model_tok, max_rows=1, max_seq=64)
+        r = eng2.new_row()
+        r.prefill([Segment("one two three", _prompt_codes(80, 2))])  # overflows max_seq
+
+
+def test_stream_codes_and_cancel(model_tok):
+    from vui_b200 import Engine, GenConfig
+
+    eng = Engine(model=model_tok, max_rows=1, max_seq=1024)
+    cfg = GenConfig(temperature=0.8, top_k=50, max_secs=3.0, eos_threshold=0.995, n_codebooks=8)
+    row = eng.new_row()
+    frames = list(eng._stream_codes(row, "Streaming works frame by frame, one chunk after another.", cfg))
+    assert 1 <= len(frames) <= int(3.0 * 12.5)
+    for f in frames:
+        assert f.shape == (16,) and f[:8].max() < 2048 and (f[8:] == 0).all()  # n_codebooks=8 zero-pads
+
+    class Cancel:
+        def __init__(self, after):
+            self.n, self.after = 0, after
+
+        def is_set(self):
+            self.n += 1
+            return self.n > self.after
+
+    row.reset()
+    few = list(eng._stream_codes(row, "Streaming works frame by frame, one chunk after another.", cfg, Cancel(3)))
+    assert len(few) < len(frames) or len(frames) <= 3
+    with pytest.raises(RuntimeError):
+        next(row.stream("needs a codec"))
+    row.close()
+    eng.check_device()
+
+
+def test_render_all_and_continuous_batching(model_tok):
+    from vui_b200 import Engine, GenConfig, RenderRequest, Segment
+
+    eng = Engine(model=model_tok, max_rows=3, max_seq=512)
+    cfg = GenConfig(temperature=0.9, max_secs=2.0, eos_threshold=0.99)
+    rows = [eng.new_row() for _ in range(3)]
+    for i, r in enumerate(rows):
+        r.prefill([Segment(f"prompt number {i} here", _prompt_codes(10 + i, 10 + i))])
+    res = eng._render_rows(rows, ["First row text here.", "Second row says something else entirely.", "Third."], cfg)
+    assert set(res) == {0, 1, 2}
+    for c in res.values():
+        assert c.shape[1] == 16 and 1 <= c.shape[0] <= 25 and c.max() < 2048
+    assert eng.render_all(rows, ["a b c.", "d e f.", "g h i."], cfg) == [None, None, None]  # no codec
+    for r in rows:
+        r.close()
+    # five requests over three slots, answered in input order
+    reqs = [RenderRequest(segments=[Segment(f"voice {i}", _prompt_codes(8, 30 + i))], text=f"Request {i} speaks now.")
+            for i in range(5)]
+    out = eng.render_continuous_codes(reqs, cfg)
+    assert len(out) == 5
+    for c in out:
+        assert c.ndim == 2 and c.shape[1] == 16 and 1 <= c.shape[0] <= 25 and c.min() >= 0 and c.max() < 2048
+    assert eng.render_continuous_codes([], cfg) == []
+    eng.check_device()
