@@ -5,7 +5,7 @@
 A step is one decode frame for every stream of the batch (backbone step, cb0
 sampling, 15 depth-transformer codebooks, gather-sum into the next frame's
 input), i.e. one replay of the captured frame graph.  Default workload is
-BASELINE config 2: one stream, 256 seeded text ids, greedy decode, KV up to 1024
+benchmark configuration 2: one stream, 256 seeded text ids, greedy decode, KV up to 1024
 positions; weights are seeded random-init (no checkpoint is available offline).
 
 Under torchrun (N > 1) every rank is an independent replica with its own streams
@@ -283,7 +283,7 @@ def run_b200(args):
     m = measure(model, dev, rank, world, B, args.steps, W, args.prompt_len, args.ragged, args.sample, args.max_seq)
     extra = None
     if B == 1 and not args.no_batched:
-        # BASELINE config 3's shape beside the headline: 64 streams, prompts U[64,512], T=0.8 top-k 50
+        # benchmark configuration 3's shape beside the headline: 64 streams, prompts U[64,512], T=0.8 top-k 50
         extra = measure(model, dev, rank, world, 64, min(args.steps, 100), W, 0, True, True, 0, phases=False)
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
@@ -295,7 +295,7 @@ def run_b200(args):
             threads = os.cpu_count() or 1
             ct = cpu_oracle_frames_per_s(64, 24, threads)[4:]
             cpu = {"value": len(ct) / sum(ct), "unit": "frames/s", "cores": threads, "kind": "port",
-                   "sample": "20 greedy frames after a 64-token prefill (BASELINE config 1 shape), "
+                   "sample": "20 greedy frames after a 64-token prefill (benchmark configuration 1 shape), "
                              "oracle/vui_oracle.py fp32 on torch CPU"}
         line = {
             "metric": "codec frames/s", "value": m["fps"], "unit": "frames/s", "n_gpus": world, "steps": K,

@@ -20,7 +20,7 @@ It restates, op by op, the algorithm of the reference PyTorch engine
 
 Two arithmetic modes:
 
-* ``dtype=torch.float32`` - the reference's CPU path (BASELINE config 1).
+* ``dtype=torch.float32`` - the reference's CPU path (benchmark configuration 1).
 * ``dtype=torch.bfloat16`` - the reference's inference precision: every tensor
   the reference materialises in bf16 is rounded to bf16 here at the same point
   (embedding sum, both RMSNorm roundings, each Linear output, the three RoPE

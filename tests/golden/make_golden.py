@@ -12,7 +12,7 @@ and stores what the reference computes:
 * ``ops_bf16.pt``   - per-op input/output pairs in bf16 (RMSNorm, RoPE,
   AudioEmbedding gather-sum, LlamaMLP, Wqkv, one RQ block, cb0 top-k
   probabilities) produced by the reference modules.
-* ``cfg1_fp32.pt``  - BASELINE config 1: 64 seeded text ids -> 50 greedy frames,
+* ``cfg1_fp32.pt``  - benchmark configuration 1: 64 seeded text ids -> 50 greedy frames,
   CPU fp32, through ``Decoder.forward`` + ``KVCache`` + causal mask and
   ``RQTransformer.generate(top_k=1)``; codes, and hidden / cb0 logits / RQ
   logits of a few frames.
@@ -184,7 +184,7 @@ def text_fixture(ref_root: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     ap.add_argument("--skip-full", action="store_true")
     args = ap.parse_args()
     torch.manual_seed(0)

@@ -344,7 +344,7 @@ def test_cluster_depth_kernel_equals_per_phase_kernels(eng8):
 
 
 def test_tensor_core_path_matches_gemv_path(nano_model, oracle_fp32):
-    """More than 8 rows run on the tcgen05 GEMM (TMA-fed, accumulators in tensor memory); up to 8
+    """Five rows and more run on the tcgen05 GEMM (TMA-fed, accumulators in tensor memory); up to 4
     on the register-tile GEMV.  Same rounding points, different fp32 summation order: a 40-token
     prefill must agree between the two and with the fp32 oracle within the bf16 tolerance, and a
     16-stream decode step must agree with the same streams decoded one by one."""

@@ -74,7 +74,7 @@ def test_cb0_topk_distribution(golden_dir):
 
 
 def test_cfg1_fp32_codes(golden_dir, nano_sd):
-    """BASELINE config 1 (CPU fp32, 64 ids -> greedy frames) against the reference's codes."""
+    """benchmark configuration 1 (CPU fp32, 64 ids -> greedy frames) against the reference's codes."""
     fx = _load(golden_dir, "cfg1_fp32.pt")
     n = 12  # the first frames; the full 50 take ~10 s more and add nothing new
     o = Oracle(OracleConfig(), nano_sd, max_seq=128, dtype=torch.float32)

@@ -366,7 +366,7 @@ extern "C" int32_t vuib_set_taps(VuibEngine* e, void* layer_hidden_dev, void* rq
 
 
 // ---------------------------------------------------------------------------
-// Tensor-core path (tc_gemm.cuh) for more than 8 rows: many streams, prefill.
+// Tensor-core path (tc_gemm.cuh) for five rows and more: many streams, prefill.
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
