@@ -307,6 +307,47 @@ def test_persistent_kernel_equals_per_phase_kernels(eng8):
             assert torch.equal(a, b), (lens, greedy)
 
 
+def test_tagged_persistent_frame_equals_per_phase_kernels(eng8):
+    """The barrier-free persistent frame kernel (activations handed on as self-validating tagged words)
+    runs the arithmetic of the per-phase kernels: identical codes, hidden states, cb0 logits, EOS
+    probabilities and depth logits; greedy and sampled, B = 1..4 with ragged lengths that cross the
+    128-key attention split, fewer codebooks, and shape changes from one launch to the next."""
+    from vui_b200 import GenConfig
+
+    eng = eng8
+    tap = torch.zeros(8, 15, 2048, device="cuda", dtype=torch.bfloat16)
+    cases = [([33], True, 0), ([40, 150, 77], True, 0), ([300], True, 0), ([64, 200, 31, 130], False, 0),
+             ([50, 60], True, 10), ([129], False, 2), ([33], True, 0)]
+    try:
+        for lens, greedy, ncb in cases:
+            cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4, n_codebooks=ncb)
+            outs = []
+            for on in ("1", ""):
+                os.environ["VUIB_LL"] = on
+                eng._graphs = {}
+                eng._set_taps(None, tap)
+                tap.zero_()
+                eng.reset()
+                eng._ws_reset_counters()
+                rows = [eng.new_row() for _ in lens]
+                hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 90 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
+                h = torch.stack([x[-1] for x in hs])
+                codes = eng.generate_frames(rows, h, 6, cfg, greedy=greedy).cpu()
+                torch.cuda.synchronize()
+                k0 = eng.model.decoder.flash_kv_caches[5].k_cache[rows[0].idx, : lens[0] + 5].clone()
+                outs.append((codes, eng._g_hidden_out[: len(lens)].clone(), eng._g_cb0_out[: len(lens)].clone(),
+                             eng._g_eos_prob[: len(lens)].clone(), tap[: len(lens)].clone(), k0))
+                eng.check_device()
+                for r in rows:
+                    r.close()
+            for j, (a, b) in enumerate(zip(outs[0], outs[1])):
+                assert torch.equal(a, b), (lens, greedy, ncb, j)
+    finally:
+        os.environ["VUIB_LL"] = ""
+        eng._graphs = {}
+        eng._set_taps(None, None)
+
+
 def test_cluster_depth_kernel_equals_per_phase_kernels(eng8):
     """The depth step as one kernel on a 16-CTA cluster (activations exchanged through distributed
     shared memory) gives, bit for bit, the codes and depth logits of the per-phase kernels:

@@ -14,17 +14,19 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libvuib200.so")
-SOURCES = [os.path.join(_HERE, "csrc", "vuib200.cu")]
-HEADERS = [
-    os.path.join(_HERE, "csrc", "decode_kernels.cuh"),
-    os.path.join(_HERE, "csrc", "frame_kernel.cuh"),
-    os.path.join(_HERE, "csrc", "tc_gemm.cuh"),
-    os.path.join(_HERE, "csrc", "depth_cluster.cuh"),
-    os.path.join(_ROOT, "include", "vuib200.h"),
-]
+_CSRC = os.path.join(_HERE, "csrc")
+_OBJ = os.path.join(_CSRC, "_obj")
+_API_H = os.path.join(_ROOT, "include", "vuib200.h")
+# translation unit -> the headers it includes (a unit is recompiled when one of them changes)
+UNITS = {
+    "vuib200.cu": ["decode_kernels.cuh", "frame_kernel.cuh", "tc_gemm.cuh", "depth_cluster.cuh", "frame_ll.h"],
+    "frame_ll.cu": ["decode_kernels.cuh", "frame_kernel.cuh", "frame_ll.h"],
+}
+SOURCES = [os.path.join(_CSRC, u) for u in UNITS]
+HEADERS = sorted({os.path.join(_CSRC, h) for hs in UNITS.values() for h in hs}) + [_API_H]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
 ]
 
 VUIB_MAX_LAYERS = 64
@@ -121,21 +123,59 @@ def _stale() -> bool:
         return f.read().strip() != _src_hash()
 
 
+def _unit_hash(unit: str) -> str:
+    import hashlib
+
+    h = hashlib.sha256()
+    for p in [os.path.join(_CSRC, unit)] + [os.path.join(_CSRC, x) for x in UNITS[unit]] + [_API_H]:
+        with open(p, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _compile_unit(nvcc: str, unit: str, verbose: bool) -> str:
+    """Compile one translation unit to an object file, unless an object of the same inputs exists."""
+    obj = os.path.join(_OBJ, unit + ".o")
+    stamp, want = obj + ".srchash", _unit_hash(unit)
+    if os.path.exists(obj) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == want:
+                return obj
+    cmd = [nvcc, *NVCC_FLAGS, "-c", "-o", obj, os.path.join(_CSRC, unit)]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {unit}:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print(res.stderr)
+    with open(stamp, "w") as f:
+        f.write(want)
+    return obj
+
+
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile csrc/*.cu for sm_100a into vui_b200/libvuib200.so (in-tree)."""
+    """Compile csrc/*.cu for sm_100a into vui_b200/libvuib200.so (in-tree): one object per
+    translation unit, compiled side by side, then one link."""
     if not force and not _stale():
         return LIB_PATH
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("libvuib200.so is missing or stale and nvcc was not found to build it")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *SOURCES]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    res = subprocess.run(cmd, capture_output=True, text=True)
+    os.makedirs(_OBJ, exist_ok=True)
+    if force:
+        for u in UNITS:
+            if os.path.exists(os.path.join(_OBJ, u + ".o.srchash")):
+                os.remove(os.path.join(_OBJ, u + ".o.srchash"))
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(max_workers=len(UNITS)) as pool:
+        objs = list(pool.map(lambda u: _compile_unit(nvcc, u, verbose), UNITS))
+    res = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "-shared",
+                          "-o", LIB_PATH, *objs], capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        print(res.stderr)
+        raise RuntimeError(f"nvcc link failed:\n{res.stdout}\n{res.stderr}")
     with open(LIB_PATH + ".srchash", "w") as f:
         f.write(_src_hash())
     return LIB_PATH

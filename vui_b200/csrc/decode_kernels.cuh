@@ -97,7 +97,7 @@ __device__ __forceinline__ float pick(const float (&a)[RT], int r) {
 // Embedding gather-sum for a decode step (AudioEmbedding.forward, model.py:559-563)
 // plus the per-row (slot, position) table every later kernel of the step reads.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) k_embed_codes(
+static __global__ void __launch_bounds__(128) k_embed_codes(
     const int64_t* __restrict__ codes, const int32_t* __restrict__ slots,
     const int32_t* __restrict__ seq_lens, const bf16* __restrict__ table, bf16* __restrict__ x,
     int32_t* __restrict__ row_slot, int32_t* __restrict__ row_pos, int d, int Q, int CS,
@@ -462,7 +462,7 @@ struct EpiProjPos {
 // and sweeps the M activation rows in tiles of RT staged in shared memory.
 // ---------------------------------------------------------------------------
 template <int K, int RT, class Stage, class Epi>
-__global__ void __launch_bounds__(GEMV_THREADS) k_gemv(Stage st, Epi ep, int M, int n_items) {
+__global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 ? 2 : 1)) k_gemv(Stage st, Epi ep, int M, int n_items) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Xs = reinterpret_cast<bf16*>(smem_raw);
     constexpr int NC = Epi::NC;
@@ -745,7 +745,7 @@ __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, in
     if (tid == 0) a.counters[r * a.Hkv + kvh] = 0;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
+static __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
     pdl_trigger();
     pdl_wait();
     __shared__ AttnSmem S_;
@@ -756,7 +756,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(AttnArgs a) {
 // Final RMSNorm of the backbone -> hidden_out, and seq_lens[slot] += inc.
 // (Decoder.forward_flash model.py:548-549; engine.py:449, 502.)
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) k_final_norm(const bf16* __restrict__ x,
+static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restrict__ x,
                                                     const bf16* __restrict__ w, float eps,
                                                     bf16* __restrict__ out, int d,
                                                     const int32_t* __restrict__ row_slot,
@@ -797,7 +797,7 @@ __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restrict__ x,
 // Depth-transformer token for position p >= 1: code_emb[(p-1)*CS + code] + pos_emb[p]
 // (model.py:922-925, 967-969).  Stage 0 writes it to row 2b+1, later stages to row b.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(64) k_rq_embed(const int32_t* __restrict__ code_cur,
+static __global__ void __launch_bounds__(64) k_rq_embed(const int32_t* __restrict__ code_cur,
                                                  const bf16* __restrict__ code_emb,
                                                  const bf16* __restrict__ pos_emb,
                                                  bf16* __restrict__ xout, int rd, int CS, int p,
@@ -1074,7 +1074,7 @@ __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, S
     return choice;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
+static __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
     pdl_trigger();
     pdl_wait();
     __shared__ SampleSmem S_;

@@ -15,6 +15,7 @@
 #include "frame_kernel.cuh"
 #include "tc_gemm.cuh"
 #include "depth_cluster.cuh"
+#include "frame_ll.h"
 
 using namespace vuib;
 
@@ -24,6 +25,7 @@ struct WsLayout {
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
     size_t bar, devmodel, trace;
     size_t xn, rq_xn, rq_attn, tc_partial, tc_counters;
+    size_t ll_state, ll_bufs;
     size_t total;
 };
 
@@ -111,6 +113,8 @@ static void make_layout(VuibEngine* e) {
     L.rq_attn = take(2 * RB * rd * 2);
     L.tc_partial = take((size_t)(TC_PARTIAL_TILES + 80) * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
     L.tc_counters = take(2 * 256 * 4);
+    L.ll_state = take(256);
+    L.ll_bufs = take(LLLayout::END * 4);
     L.total = off;
 }
 
@@ -873,16 +877,11 @@ static FrameKernel frame_kernel_for(int rt, int rqf) {
     }
 }
 
-static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc,
-                            int64_t* codes_io, bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob,
-                            int do_backbone, int first_frame, cudaStream_t s) {
+static FrameArgs fill_frame_args(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc,
+                                 int64_t* codes_io, bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob,
+                                 int do_backbone, int first_frame) {
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
-    if (e->num_sms == 0) {
-        int dev = 0;
-        CK(cudaGetDevice(&dev));
-        CK(cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, dev));
-    }
     FrameArgs fa;
     memset(&fa, 0, sizeof(fa));
     fa.m = wsp<DevModel>(e, L.devmodel);
@@ -938,7 +937,26 @@ static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const in
     fa.n_codebooks = e->samp.n_codebooks > 0 ? e->samp.n_codebooks : c.n_quantizers;
     fa.do_backbone = do_backbone;
     fa.first_frame = first_frame;
+    return fa;
+}
 
+static int32_t need_sm_count(VuibEngine* e) {
+    if (e->num_sms == 0) {
+        int dev = 0;
+        CK(cudaGetDevice(&dev));
+        CK(cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    return VUIB_OK;
+}
+
+static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc,
+                            int64_t* codes_io, bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob,
+                            int do_backbone, int first_frame, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    int32_t rc = need_sm_count(e);
+    if (rc) return rc;
+    FrameArgs fa = fill_frame_args(e, B, slots, seq_inc, codes_io, hidden, cb0, eos, eos_prob, do_backbone, first_frame);
     const int rt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
     FrameKernel kern = frame_kernel_for(rt, c.rq_ffn);
     const size_t smem = (size_t)rt * 3072 * sizeof(bf16);
@@ -955,6 +973,31 @@ static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const in
     cfg.attrs = attr;
     cfg.numAttrs = (e->coop && !env_off("VUIB_NO_COOP")) ? 1 : 0;
     CK(cudaLaunchKernelEx(&cfg, kern, fa));
+    e->launches++;
+    return VUIB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Barrier-free persistent frame (frame_ll.cu): one launch per frame for B <= 4, activations handed
+// from phase to phase as self-validating tagged words.  Needs a cooperative launch (every CTA
+// resident) and the one model shape its buffers are laid out for.
+// ---------------------------------------------------------------------------
+static bool ll_ok(VuibEngine* e, int B) {
+    const VuibConfig& c = e->cfg;
+    return B <= LL_MAXB && e->coop && c.d_model == 1024 && c.ffn == 3072 && c.n_heads == 16 && c.n_kv_heads == 8 &&
+           c.codebook_size == 2048 && c.rq_d_model == 512 && c.rq_n_heads == 8 && c.rq_n_layers <= 4 &&
+           c.n_quantizers == 16 && (c.rq_ffn == 1408 || c.rq_ffn == 1536) && env_off("VUIB_LL");
+}
+
+static int32_t launch_ll(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc, int64_t* codes_io,
+                         bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob, cudaStream_t s) {
+    int32_t rc = need_sm_count(e);
+    if (rc) return rc;
+    LLArgs la;
+    la.fa = fill_frame_args(e, B, slots, seq_inc, codes_io, hidden, cb0, eos, eos_prob, 1, 0);
+    la.bufs = wsp<uint32_t>(e, e->lay.ll_bufs);
+    la.state = wsp<uint32_t>(e, e->lay.ll_state);
+    CK((cudaError_t)launch_frame_ll(la, e->cfg.rq_ffn, e->num_sms, true, s));
     e->launches++;
     return VUIB_OK;
 }
@@ -1068,6 +1111,10 @@ extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* sl
     if (!slots_dev || !codes_io_dev || !hidden_out_dev || !cb0_out_dev || !eos_out_dev) return VUIB_ERR_NULL;
     if (B < 1 || B > e->cfg.max_rows)
         return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    if (ll_ok(e, B))
+        return launch_ll(e, B, slots_dev, seq_inc_dev, codes_io_dev, static_cast<bf16*>(hidden_out_dev),
+                         static_cast<bf16*>(cb0_out_dev), static_cast<bf16*>(eos_out_dev), eos_prob_out_dev,
+                         static_cast<cudaStream_t>(stream));
     if (persistent_ok(e, B))
         return launch_frame(e, B, slots_dev, seq_inc_dev, codes_io_dev, static_cast<bf16*>(hidden_out_dev),
                             static_cast<bf16*>(cb0_out_dev), static_cast<bf16*>(eos_out_dev), eos_prob_out_dev,
@@ -1173,6 +1220,7 @@ extern "C" int32_t vuib_reset_state(VuibEngine* e, void* stream) {
     CK(cudaMemsetAsync(e->ws + L.counters, 0, (size_t)e->R * c.n_kv_heads * 4, s));
     CK(cudaMemsetAsync(e->ws + L.frame_ctr, 0, (size_t)c.n_slots * 4, s));
     CK(cudaMemsetAsync(e->ws + L.bar, 0, 256, s));
+    CK(cudaMemsetAsync(e->ws + L.ll_state + 4, 0, 8, s));  // shape word: the next launch clears its exchange buffers
     return vuib_rep_reset(e, -1, stream);
 }
 
@@ -1216,7 +1264,7 @@ extern "C" int32_t vuib_check_device_flag(VuibEngine* e, void* stream) {
     CK(cudaStreamSynchronize(s));
     if (flag) {
         CK(cudaMemsetAsync(e->ws + e->lay.flag, 0, 4, s));
-        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code, 8 = grid barrier timed out, 16 = tensor-core pipeline wait timed out)", flag);
+        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code, 8 = grid barrier timed out, 16 = tensor-core pipeline wait timed out, 32 = tagged-word wait timed out)", flag);
     }
     return VUIB_OK;
 }
