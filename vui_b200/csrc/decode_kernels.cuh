@@ -794,32 +794,6 @@ static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restric
 }
 
 // ---------------------------------------------------------------------------
-// Depth-transformer token for position p >= 1: code_emb[(p-1)*CS + code] + pos_emb[p]
-// (model.py:922-925, 967-969).  Stage 0 writes it to row 2b+1, later stages to row b.
-// ---------------------------------------------------------------------------
-static __global__ void __launch_bounds__(64) k_rq_embed(const int32_t* __restrict__ code_cur,
-                                                 const bf16* __restrict__ code_emb,
-                                                 const bf16* __restrict__ pos_emb,
-                                                 bf16* __restrict__ xout, int rd, int CS, int p,
-                                                 int row_mul, int row_add) {
-    pdl_trigger();
-    pdl_wait();
-    const int b = blockIdx.x;
-    const int code = code_cur[b];
-    const bf16* e = code_emb + ((size_t)(p - 1) * CS + code) * rd;
-    const bf16* pe = pos_emb + (size_t)p * rd;
-    bf16* o = xout + ((size_t)b * row_mul + row_add) * rd;
-    for (int k = threadIdx.x * 8; k < rd; k += 64 * 8) {
-        float a[8], c[8], s[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(e + k)), a);
-        unpack8(__ldg(reinterpret_cast<const uint4*>(pe + k)), c);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s[j] = a[j] + c[j];
-        *reinterpret_cast<uint4*>(o + k) = pack8(s);
-    }
-}
-
-// ---------------------------------------------------------------------------
 // Sampler: one CTA per row over CS = 2048 logits.
 //   cb0 (engine.py:571-590, 855-863): optional repetition penalty, then greedy or
 //       softmax(l/T) restricted to the top-k, inverse-CDF draw.
