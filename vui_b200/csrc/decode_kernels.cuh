@@ -146,13 +146,37 @@ static __global__ void __launch_bounds__(128) k_embed_codes(
 // ---------------------------------------------------------------------------
 
 // RMSNorm (model.py:292-297): fp32 x*rsqrt(mean(x^2)+eps) -> bf16 -> * weight -> bf16.
+struct NoPre {};  // nothing to fetch ahead
+
+template <int K>
+struct NormW {  // this lane's norm weights
+    uint4 w[(K + 255) / 256];
+};
+
 struct StageNorm {
     const bf16* x;   // row r of the GEMV lives at x + (r*row_mul + row_add)*K
     const bf16* w;   // (K)
     float eps;
     int row_mul, row_add;
+    // The norm weights are constants: a kernel fetches them before it waits for its predecessor,
+    // so that their L2 round trip is not paid between the reduction and the scaling.
+    template <int K>
+    __device__ __forceinline__ NormW<K> preload() const {
+        NormW<K> nw;
+        const int lane = threadIdx.x & 31;
+#pragma unroll
+        for (int it = 0; it < (K + 255) / 256; ++it) {
+            const int k = it * 256 + lane * 8;
+            nw.w[it] = (k < K) ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0, 0, 0, 0);
+        }
+        return nw;
+    }
     template <int K>
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
+        stage<K>(Xs, r0, nr, preload<K>());
+    }
+    template <int K>
+    __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr, const NormW<K>& nw) const {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int rr = warp; rr < nr; rr += (int)(blockDim.x >> 5)) {
             const bf16* xr = x + ((size_t)(r0 + rr) * row_mul + row_add) * K;
@@ -176,7 +200,7 @@ struct StageNorm {
                 const int k = it * 256 + lane * 8;
                 if (k < K) {
                     float wf[8], o[8];
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+                    unpack8(nw.w[it], wf);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) o[j] = rbf(v[it][j] * rinv) * wf[j];
                     *reinterpret_cast<uint4*>(Xs + rr * K + k) = pack8(o);
@@ -188,6 +212,10 @@ struct StageNorm {
 
 struct StageCopy {
     const bf16* x;  // (M, K)
+    template <int K>
+    __device__ __forceinline__ NoPre preload() const { return NoPre{}; }
+    template <int K>
+    __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr, const NoPre&) const { stage<K>(Xs, r0, nr); }
     template <int K>
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
         const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r0 * K);
@@ -211,6 +239,10 @@ struct StageRqAttn {
     int rows_per_b;   // row r -> b = r / rows_per_b, pos = pos_base + r % rows_per_b
     int pos_base;
     template <int K>
+    __device__ __forceinline__ NoPre preload() const { return NoPre{}; }
+    template <int K>
+    __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr, const NoPre&) const { stage<K>(Xs, r0, nr); }
+    template <int K>
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int s = lane & 7, g = lane >> 3;
@@ -218,32 +250,51 @@ struct StageRqAttn {
             const int r = r0 + rr;
             const int b = r / rows_per_b, pos = pos_base + r % rows_per_b;
             for (int h = warp; h < H; h += (int)(blockDim.x >> 5)) {
+                // q and every key/value group of this lane (<= 16 positions = 4 groups) are requested
+                // together: one L2 round trip instead of one per group of four positions
+                const uint4 qraw = __ldcg(reinterpret_cast<const uint4*>(q + (size_t)r * K + h * HD + s * 8));
+                uint4 kraw[4], vraw[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int t = u * 4 + g;
+                    const bool ok = t <= pos;
+                    const size_t off = ((size_t)b * Qpos + (ok ? t : 0)) * K + h * HD + s * 8;
+                    if (u * 4 <= pos) {
+                        kraw[u] = __ldcg(reinterpret_cast<const uint4*>(kc + off));
+                        vraw[u] = __ldcg(reinterpret_cast<const uint4*>(vc + off));
+                    } else {
+                        kraw[u] = make_uint4(0, 0, 0, 0);
+                        vraw[u] = make_uint4(0, 0, 0, 0);
+                    }
+                }
                 float qf[8];
-                unpack8(__ldcg(reinterpret_cast<const uint4*>(q + (size_t)r * K + h * HD + s * 8)), qf);
+                unpack8(qraw, qf);
                 float m = NEG_BIG, l = 0.f, acc[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                for (int t0 = 0; t0 <= pos; t0 += 4) {
-                    const int t = t0 + g;
-                    const bool ok = t <= pos;
-                    const size_t off = ((size_t)b * Qpos + (ok ? t : 0)) * K + h * HD + s * 8;
-                    float kf[8], vf[8];
-                    unpack8(__ldcg(reinterpret_cast<const uint4*>(kc + off)), kf);
-                    unpack8(__ldcg(reinterpret_cast<const uint4*>(vc + off)), vf);
-                    float d = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) d = fmaf(qf[j], kf[j], d);
-                    d += __shfl_xor_sync(0xffffffffu, d, 1);
-                    d += __shfl_xor_sync(0xffffffffu, d, 2);
-                    d += __shfl_xor_sync(0xffffffffu, d, 4);
-                    if (ok) {
-                        const float sc = d * 0.125f;
-                        const float mn = fmaxf(m, sc);
-                        const float corr = __expf(m - mn), p = __expf(sc - mn);
-                        l = l * corr + p;
+                for (int u = 0; u < 4; ++u) {
+                    if (u * 4 <= pos) {  // the whole warp runs the same groups
+                        const int t = u * 4 + g;
+                        const bool ok = t <= pos;
+                        float kf[8], vf[8];
+                        unpack8(kraw[u], kf);
+                        unpack8(vraw[u], vf);
+                        float d = 0.f;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(p, vf[j], acc[j] * corr);
-                        m = mn;
+                        for (int j = 0; j < 8; ++j) d = fmaf(qf[j], kf[j], d);
+                        d += __shfl_xor_sync(0xffffffffu, d, 1);
+                        d += __shfl_xor_sync(0xffffffffu, d, 2);
+                        d += __shfl_xor_sync(0xffffffffu, d, 4);
+                        if (ok) {
+                            const float sc = d * 0.125f;
+                            const float mn = fmaxf(m, sc);
+                            const float corr = __expf(m - mn), p = __expf(sc - mn);
+                            l = l * corr + p;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[j] = fmaf(p, vf[j], acc[j] * corr);
+                            m = mn;
+                        }
                     }
                 }
 #pragma unroll
@@ -316,25 +367,49 @@ struct EpiQkv {
             }
         }
     }
+    // What lane r needs for row r besides the sums: requested before the dot products, so that the
+    // two dependent L2 round trips (position, then RoPE factors) are not paid after them.
+    struct Pre {
+        int slot, pos;
+        float c0, s0, c1, s1;
+    };
+    __device__ __forceinline__ Pre pre(int item, int r0, int nr, int lane) const {
+        Pre p{0, 0, 1.f, 0.f, 1.f, 0.f};
+        if (lane >= nr) return p;
+        const int r = r0 + lane;
+        const int n = 2 * item;
+        if (row_slot) {
+            p.slot = __ldcg(row_slot + r);
+            p.pos = __ldcg(row_pos + r);
+        } else {
+            p.slot = r / rows_per_b;
+            p.pos = pos_base + r % rows_per_b;
+        }
+        if (rope && n < q_cols + kv_cols) {
+            const int dd = n & (HD - 1);
+            const uint2 f = __ldg(reinterpret_cast<const uint2*>(rope + ((size_t)p.pos * HD + dd) * 2));
+            p.c0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x & 0xffffu)));
+            p.s0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x >> 16)));
+            p.c1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y & 0xffffu)));
+            p.s1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y >> 16)));
+        }
+        return p;
+    }
     template <int RT>
     __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
                                           const float (&acc)[2][RT]) const {
+        store<RT>(item, r0, nr, lane, acc, pre(item, r0, nr, lane));
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[2][RT], const Pre& pr_) const {
         if (lane >= nr) return;
         const int r = r0 + lane;
         const int n = 2 * item;
         float t0 = rbf(pick<RT>(acc[0], lane)), t1 = rbf(pick<RT>(acc[1], lane));
-        int slot, pos;
-        if (row_slot) {
-            slot = __ldcg(row_slot + r);
-            pos = __ldcg(row_pos + r);
-        } else {
-            slot = r / rows_per_b;
-            pos = pos_base + r % rows_per_b;
-        }
+        const int slot = pr_.slot, pos = pr_.pos;
         if (rope && n < q_cols + kv_cols) {
-            const int dd = n & (HD - 1);
-            const bf16* f = rope + ((size_t)pos * HD + dd) * 2;
-            const float c0 = bf2f(f[0]), s0 = bf2f(f[1]), c1 = bf2f(f[2]), s1 = bf2f(f[3]);
+            const float c0 = pr_.c0, s0 = pr_.s0, c1 = pr_.c1, s1 = pr_.s1;
             // t*cos + rotate_half(t)*sin, each product and the sum rounded to bf16
             const float o0 = rbf(rbf(t0 * c0) + rbf((-t1) * s0));
             const float o1 = rbf(rbf(t1 * c1) + rbf(t0 * s1));
@@ -366,12 +441,22 @@ struct EpiResidual {
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = W + (size_t)item * K;
     }
+    // The element this lane adds to: requested before the dot products hide its L2 round trip.
+    typedef unsigned short Pre;
+    __device__ __forceinline__ Pre pre(int item, int r0, int nr, int lane) const {
+        if (lane >= nr) return 0;
+        return __ldcg(reinterpret_cast<const unsigned short*>(x) + (size_t)(r0 + lane) * N + item);
+    }
     template <int RT>
     __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
                                           const float (&acc)[1][RT]) const {
+        store<RT>(item, r0, nr, lane, acc, pre(item, r0, nr, lane));
+    }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[1][RT], Pre xb) const {
         if (lane >= nr) return;
         const size_t idx = (size_t)(r0 + lane) * N + item;
-        const unsigned short xb = __ldcg(reinterpret_cast<const unsigned short*>(x) + idx);
         const bf16 o = f2bf(bf2f(__ushort_as_bfloat16(xb)) + rbf(pick<RT>(acc[0], lane)));
         x[idx] = o;
         if (tap) tap[idx] = o;
@@ -390,6 +475,13 @@ struct EpiSwiGLU {
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
         wr[0] = W1 + (size_t)item * K;
         wr[1] = W3 + (size_t)item * K;
+    }
+    typedef NoPre Pre;
+    __device__ __forceinline__ Pre pre(int, int, int, int) const { return NoPre{}; }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[2][RT], const NoPre&) const {
+        store<RT>(item, r0, nr, lane, acc);
     }
     template <int RT>
     __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
@@ -418,6 +510,13 @@ struct EpiLogits {
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = item < n_main ? W + (size_t)item * K : W_extra;
     }
+    typedef NoPre Pre;
+    __device__ __forceinline__ Pre pre(int, int, int, int) const { return NoPre{}; }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[1][RT], const NoPre&) const {
+        store<RT>(item, r0, nr, lane, acc);
+    }
     template <int RT>
     __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
                                           const float (&acc)[1][RT]) const {
@@ -445,6 +544,13 @@ struct EpiProjPos {
     __device__ __forceinline__ void hint(int) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = W + (size_t)item * K;
+    }
+    typedef NoPre Pre;
+    __device__ __forceinline__ Pre pre(int, int, int, int) const { return NoPre{}; }
+    template <int RT>
+    __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
+                                          const float (&acc)[1][RT], const NoPre&) const {
+        store<RT>(item, r0, nr, lane, acc);
     }
     template <int RT>
     __device__ __forceinline__ void store(int item, int r0, int nr, int lane,
@@ -484,12 +590,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 ? 2 : 1)) k_gemv(Stage 
                 w[c][it] = (k < K) ? ldg_stream(wr[c] + k) : make_uint4(0, 0, 0, 0);
             }
     }
+    const auto nw = st.template preload<K>();  // constants too
     pdl_wait();  // the weights above are constants; activations below come from the predecessor
     ep.hint(M);
     for (int r0 = 0; r0 < M; r0 += RT) {
         const int nr = min(RT, M - r0);
+        // what the epilogue needs from global memory is requested now and used after the dot products
+        typename Epi::Pre pre = live ? ep.pre(item, r0, nr, lane) : typename Epi::Pre{};
         if (r0) __syncthreads();
-        st.template stage<K>(Xs, r0, nr);
+        st.template stage<K>(Xs, r0, nr, nw);
         __syncthreads();
         if (live) {
             float acc[NC][RT];
@@ -522,7 +631,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 ? 2 : 1)) k_gemv(Stage 
             for (int c = 0; c < NC; ++c)
 #pragma unroll
                 for (int r = 0; r < RT; ++r) acc[c][r] = warp_sum(acc[c][r]);
-            ep.template store<RT>(item, r0, nr, lane, acc);
+            ep.template store<RT>(item, r0, nr, lane, acc, pre);
         }
     }
 }

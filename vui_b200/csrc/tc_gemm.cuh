@@ -540,10 +540,34 @@ __global__ void __launch_bounds__(128) k_rmsnorm_rows(const bf16* __restrict__ x
                                                       float eps, bf16* __restrict__ out, int K, int row_mul,
                                                       int row_add) {
     pdl_trigger();
-    pdl_wait();
     const int r = blockIdx.x;
     __shared__ float red[4];
     const bf16* xr = x + ((size_t)r * row_mul + row_add) * K;
+    if (K <= 128 * 8) {
+        // one 16-byte piece per thread: the row stays in registers between the two passes and the
+        // norm weights (constants) are fetched before the predecessor is waited for
+        const int k = threadIdx.x * 8;
+        const bool on = k < K;
+        const uint4 wv = on ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0, 0, 0, 0);
+        pdl_wait();
+        float f[8], wf[8], o[8];
+        unpack8(on ? __ldcg(reinterpret_cast<const uint4*>(xr + k)) : make_uint4(0, 0, 0, 0), f);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        const float rinv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)K + eps);
+        if (on) {
+            unpack8(wv, wf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = rbf(f[j] * rinv) * wf[j];
+            *reinterpret_cast<uint4*>(out + (size_t)r * K + k) = pack8(o);
+        }
+        return;
+    }
+    pdl_wait();
     float ss = 0.f;
     for (int k = threadIdx.x * 8; k < K; k += 128 * 8) {
         float f[8];

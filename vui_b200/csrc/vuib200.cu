@@ -239,7 +239,7 @@ extern "C" int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out) {
                     k_supported(c.d_model) && k_supported(c.ffn) && k_supported(c.rq_d_model) &&
                     k_supported(c.rq_ffn) && c.rq_d_model == c.rq_n_heads * HD &&
                     c.codebook_size == SAMPLE_THREADS * SAMPLE_EL && c.n_quantizers >= 2 &&
-                    c.n_quantizers <= 32 && c.n_layers >= 1 && c.n_layers <= VUIB_MAX_LAYERS &&
+                    c.n_quantizers <= 16 && c.n_layers >= 1 && c.n_layers <= VUIB_MAX_LAYERS &&
                     c.rq_n_layers >= 1 && c.rq_n_layers <= VUIB_MAX_LAYERS;
     if (!ok) return VUIB_ERR_SHAPE;
     if (c.n_slots < 1 || c.max_seq < 1 || c.max_rows < 1 || c.max_prefill_rows < 1)
@@ -797,7 +797,6 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     bf16* x2 = wsp<bf16>(e, L.rq_x2);
     bf16* x1 = wsp<bf16>(e, L.rq_x);
     const bf16* pos_emb = static_cast<const bf16*>(e->w.rq_pos_emb);
-    const bf16* code_emb = static_cast<const bf16*>(e->w.rq_code_emb);
     const bool tc = tc_ok(e, B);
     int32_t rc;
     if (tc) {
