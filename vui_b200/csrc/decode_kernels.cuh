@@ -351,13 +351,27 @@ struct EpiQkv {
     }
     // Warm L2 (and the TLB) with the K/V rows the attention kernel that follows will read: the
     // rows before each stream's current position do not change during the frame.  The whole
-    // grid shares the work, one 128-byte line per thread and step.
-    __device__ __forceinline__ void hint(int M) const {
+    // grid shares the work, one 128-byte line per thread and step.  Two steps, so that the
+    // round trip for (slot, position) is not paid in front of the staging loads: lane r asks
+    // for row r's pair first thing, the prefetches are issued once the tile is staged.
+    struct Hint {
+        int slot, pos;
+    };
+    __device__ __forceinline__ Hint hint_begin(int M) const {
+        Hint h{0, 0};
+        const int lane = threadIdx.x & 31;
+        if (row_slot && kv_hint && lane < M) {
+            h.slot = __ldcg(row_slot + lane);
+            h.pos = __ldcg(row_pos + lane);
+        }
+        return h;
+    }
+    __device__ __forceinline__ void hint_end(int M, const Hint& h) const {
         if (!row_slot || !kv_hint) return;
         const size_t row_bytes = (size_t)kv_cols * sizeof(bf16);
         const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
-        for (int r = 0; r < M; ++r) {
-            const int slot = __ldcg(row_slot + r), pos = __ldcg(row_pos + r);
+        for (int r = 0; r < M && r < 32; ++r) {
+            const int slot = __shfl_sync(0xffffffffu, h.slot, r), pos = __shfl_sync(0xffffffffu, h.pos, r);
             const size_t lines = (size_t)pos * row_bytes / 128;
             const char* kb = reinterpret_cast<const char*>(k_cache) + (size_t)slot * max_seq * row_bytes;
             const char* vb = reinterpret_cast<const char*>(v_cache) + (size_t)slot * max_seq * row_bytes;
@@ -437,7 +451,9 @@ struct EpiResidual {
     int N;
     bf16* tap;      // optional copy of the new x (M, N)
     static constexpr int NC = 1;
-    __device__ __forceinline__ void hint(int) const {}
+    typedef NoPre Hint;
+    __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
+    __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = W + (size_t)item * K;
     }
@@ -471,7 +487,9 @@ struct EpiSwiGLU {
     bf16* act;  // (M, F)
     int F;
     static constexpr int NC = 2;
-    __device__ __forceinline__ void hint(int) const {}
+    typedef NoPre Hint;
+    __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
+    __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
         wr[0] = W1 + (size_t)item * K;
         wr[1] = W3 + (size_t)item * K;
@@ -506,7 +524,9 @@ struct EpiLogits {
     bf16* tap;            // optional second copy of out with its own row stride
     int tap_stride;
     static constexpr int NC = 1;
-    __device__ __forceinline__ void hint(int) const {}
+    typedef NoPre Hint;
+    __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
+    __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = item < n_main ? W + (size_t)item * K : W_extra;
     }
@@ -541,7 +561,9 @@ struct EpiProjPos {
     bf16* out;        // (rows_out, rd); row of stream b is b*row_mul
     int rd, row_mul;
     static constexpr int NC = 1;
-    __device__ __forceinline__ void hint(int) const {}
+    typedef NoPre Hint;
+    __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
+    __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[1]) const {
         wr[0] = W + (size_t)item * K;
     }
@@ -592,7 +614,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 ? 2 : 1)) k_gemv(Stage 
     }
     const auto nw = st.template preload<K>();  // constants too
     pdl_wait();  // the weights above are constants; activations below come from the predecessor
-    ep.hint(M);
+    const typename Epi::Hint hint = ep.hint_begin(M);
     for (int r0 = 0; r0 < M; r0 += RT) {
         const int nr = min(RT, M - r0);
         // what the epilogue needs from global memory is requested now and used after the dot products
@@ -600,6 +622,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 ? 2 : 1)) k_gemv(Stage 
         if (r0) __syncthreads();
         st.template stage<K>(Xs, r0, nr, nw);
         __syncthreads();
+        if (r0 == 0) ep.hint_end(M, hint);  // its (slot, position) pair arrived while the tile was staged
         if (live) {
             float acc[NC][RT];
 #pragma unroll
@@ -689,10 +712,10 @@ struct AttnSmem {
 __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, int r, int tid,
                                           AttnSmem& S_, int bar_id) {
     attn_stamp(a, tid, 0);
+    const int slot = __ldcg(a.row_slot + r);  // both requests in flight before the first use
     const int len = __ldcg(a.row_pos + r) + 1;
     const int nsplit = (len + ATT_SPLIT - 1) / ATT_SPLIT;
     if (sp >= nsplit) return;
-    const int slot = __ldcg(a.row_slot + r);
     const int warp = tid >> 5, lane = tid & 31;
     const int s = lane & 7, g = lane >> 3;
     const int G = a.Hq / a.Hkv;  // q heads per kv head (2)
