@@ -345,7 +345,6 @@ struct EpiQkv {
     int rows_per_b, pos_base; // used when row_slot == NULL
     int kv_hint;              // 1: prefetch the K/V rows of the attention that follows into L2
     static constexpr int NC = 2;
-    static constexpr bool TWO_CTAS = false;  // ask for two resident CTAs per SM also below 4-row tiles
     __device__ __forceinline__ void rows(int item, const bf16* (&wr)[2]) const {
         wr[0] = W + (size_t)(2 * item) * K;
         wr[1] = wr[0] + K;
@@ -452,7 +451,6 @@ struct EpiResidual {
     int N;
     bf16* tap;      // optional copy of the new x (M, N)
     static constexpr int NC = 1;
-    static constexpr bool TWO_CTAS = false;  // ask for two resident CTAs per SM also below 4-row tiles
     typedef NoPre Hint;
     __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
     __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
@@ -489,7 +487,6 @@ struct EpiSwiGLU {
     bf16* act;  // (M, F)
     int F;
     static constexpr int NC = 2;
-    static constexpr bool TWO_CTAS = true;  // ask for two resident CTAs per SM also below 4-row tiles
     typedef NoPre Hint;
     __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
     __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
@@ -527,7 +524,6 @@ struct EpiLogits {
     bf16* tap;            // optional second copy of out with its own row stride
     int tap_stride;
     static constexpr int NC = 1;
-    static constexpr bool TWO_CTAS = false;  // ask for two resident CTAs per SM also below 4-row tiles
     typedef NoPre Hint;
     __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
     __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
@@ -565,7 +561,6 @@ struct EpiProjPos {
     bf16* out;        // (rows_out, rd); row of stream b is b*row_mul
     int rd, row_mul;
     static constexpr int NC = 1;
-    static constexpr bool TWO_CTAS = false;  // ask for two resident CTAs per SM also below 4-row tiles
     typedef NoPre Hint;
     __device__ __forceinline__ Hint hint_begin(int) const { return NoPre{}; }
     __device__ __forceinline__ void hint_end(int, const NoPre&) const {}
@@ -595,7 +590,7 @@ struct EpiProjPos {
 // and sweeps the M activation rows in tiles of RT staged in shared memory.
 // ---------------------------------------------------------------------------
 template <int K, int RT, class Stage, class Epi>
-__global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 || Epi::TWO_CTAS ? 2 : 1)) k_gemv(Stage st, Epi ep, int M, int n_items) {
+__global__ void __launch_bounds__(GEMV_THREADS, (RT >= 4 ? 2 : 1)) k_gemv(Stage st, Epi ep, int M, int n_items) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Xs = reinterpret_cast<bf16*>(smem_raw);
     constexpr int NC = Epi::NC;
