@@ -88,7 +88,7 @@ def measured_hbm_peak():
 
 # DRAM bytes per frame (dram__bytes_read.sum + dram__bytes_write.sum over the launches of one frame)
 # from the ncu capture summarised in profiles/frame_graph_b1_dram_traffic.md.
-NCU_TRAFFIC_BYTES_PER_FRAME = {1: 943177216}
+NCU_TRAFFIC_BYTES_PER_FRAME = {1: 945989120}
 
 
 def ncu_traffic():
