@@ -111,3 +111,29 @@ def test_render_all_and_continuous_batching(model_tok):
         assert c.ndim == 2 and c.shape[1] == 16 and 1 <= c.shape[0] <= 25 and c.min() >= 0 and c.max() < 2048
     assert eng.render_continuous_codes([], cfg) == []
     eng.check_device()
+
+
+def test_cut_short_chunk_is_retried_at_lower_temperature(model_tok):
+    """A chunk that ends with fewer than two frames per word is rewound and spoken again at 0.5,
+    then 0.3, then accepted (engine.py:953-983).  With an EOS threshold that every frame passes,
+    every chunk ends at min_frames, so each of the two chunks is retried exactly twice."""
+    from vui_b200 import Engine, GenConfig, Segment
+
+    eng = Engine(model=model_tok, max_rows=1, max_seq=512)
+    rewinds, temps = [], []
+    orig_rewind, orig_apply = eng._rewind_row, eng._apply_cfg
+    eng._rewind_row = lambda row, off: (rewinds.append(off), orig_rewind(row, off))[1]
+    eng._apply_cfg = lambda cfg, temperature=None, greedy=False: (temps.append(temperature),
+                                                                  orig_apply(cfg, temperature, greedy))[1]
+    cfg = GenConfig(temperature=0.9, max_secs=4.0, min_secs=0.16, eos_threshold=-1.0, sentence_only=True)
+    row = eng.new_row()
+    off0 = row.prefill([Segment("a calm voice prompt", _prompt_codes(12, 5))])
+    codes, _ = row.render("The first sentence has seven words here. The second sentence also has seven words.", cfg)
+    min_frames = int(0.16 * 12.5)
+    assert min_frames == 2
+    # two chunks, each accepted after two retries with min_frames + 1 frames kept (frame 0 + 2 steps - the EOS frame)
+    assert len(rewinds) == 4 and rewinds[0] == rewinds[1] and rewinds[2] == rewinds[3] and rewinds[0] >= off0
+    assert [t for t in temps if t is not None] == [0.5, 0.3, 0.5, 0.3]
+    assert codes.shape[1] == 16 and codes.shape[0] == 2 * min_frames
+    assert codes.min() >= 0 and codes.max() < 2048
+    eng.check_device()

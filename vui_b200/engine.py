@@ -29,6 +29,8 @@ from .model import VuiB200
 from .text import chunk_text, simple_clean
 
 FRAME_RATE = 12.5  # codec frames per second (src/vui/qwen_codec.py:27-29)
+MIN_FPW = 2.0              # frames per word below which a finished chunk counts as cut short (engine.py:909)
+RETRY_TEMPS = (0.5, 0.3)   # temperatures of the retries (engine.py:910)
 SAMPLE_RATE = 24000
 DEFAULT_WPS = 3.0
 RQ_TOP_K = 100  # the reference captures its depth graphs with top_k=100 (engine.py:395-397)
@@ -709,21 +711,52 @@ class Engine:
         B = len(rows)
         self._g_slot_idx[:B] = torch.tensor([r.idx for r in rows], device=self.device, dtype=torch.int32)
 
-        def advance(row: Row) -> bool:
+        chunk_start = {r.idx: r.offset for r in rows}  # KV length before the current chunk's text
+        retry_idx = {r.idx: 0 for r in rows}
+
+        def advance(row: Row, temp: float | None = None, flip: bool = True) -> bool:
             c = chunks[row.idx]
             if ci[row.idx] >= len(c):
                 return False
             ch = c[ci[row.idx]]
-            if ch["sc"] and row._spk_token_2 is not None:
+            if flip and ch["sc"] and row._spk_token_2 is not None:
                 row._active_speaker = 1 - row._active_speaker
             cap[row.idx] = cfg.max_turn_frames(len(ch["text"].split()), row.prompt_wps)
+            chunk_start[row.idx] = row.offset
             hidden = self._add_agent_text(row, ch["text"])
+            if temp is not None:  # a retry draws the chunk's first frame at the lower temperature
+                self._apply_cfg(cfg, temperature=temp)
             codes = self._first_frames([row], hidden[None])[0]
+            if temp is not None:
+                self._apply_cfg(cfg)
             self._set_codes_in(qi[row.idx], codes)
             frames[row.idx].append(codes.cpu())
             count[row.idx] += 1
             turn[row.idx] = 1
             return True
+
+        def retry_chunk(row: Row) -> bool:
+            """A chunk that ended after fewer than MIN_FPW frames per word was cut short: rewind
+            the KV to the chunk's start and speak it again at a lower temperature
+            (engine.py:953-983).  False when the chunk is long enough or the temperatures are used up."""
+            words = len(chunks[row.idx][ci[row.idx]]["text"].split())
+            fpw = turn[row.idx] / words if words > 0 else 999.0
+            ri = retry_idx[row.idx]
+            if fpw >= MIN_FPW or ri >= len(RETRY_TEMPS):
+                retry_idx[row.idx] = 0
+                return False
+            retry_idx[row.idx] = ri + 1
+            self._rewind_row(row, chunk_start[row.idx])
+            del frames[row.idx][len(frames[row.idx]) - turn[row.idx]:]
+            count[row.idx] -= turn[row.idx]
+            self._rep_reset(cfg.rep_penalty, cfg.rep_window)
+            return advance(row, temp=RETRY_TEMPS[ri], flip=False)
+
+        def next_chunk(row: Row) -> bool:
+            if retry_chunk(row):
+                return True
+            ci[row.idx] += 1
+            return advance(row)
 
         for r in rows:
             if not advance(r):
@@ -732,8 +765,7 @@ class Engine:
         while any(active.values()) and steps < max_frames:
             for r in rows:
                 if active[r.idx] and turn[r.idx] >= cap[r.idx]:
-                    ci[r.idx] += 1
-                    if not advance(r):
+                    if not next_chunk(r):
                         active[r.idx] = False
             if not any(active.values()):
                 break
@@ -750,8 +782,7 @@ class Engine:
                     active[r.idx] = False
                     continue
                 if turn[r.idx] >= min_frames and float(h_eos[qi[r.idx]]) > cfg.eos_threshold:
-                    ci[r.idx] += 1
-                    if not advance(r):
+                    if not next_chunk(r):
                         active[r.idx] = False
                     continue
                 frames[r.idx].append(h_codes[qi[r.idx]])
