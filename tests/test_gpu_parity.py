@@ -553,3 +553,36 @@ def test_host_side_errors(nano_model):
     eng2 = Engine(model=nano_model, max_rows=2, max_seq=128)
     with pytest.raises(RuntimeError):
         next(eng2.new_row().stream("hello"))
+
+
+def test_older_single_stream_api_decode_step(nano_model, oracle_fp32):
+    """`setup_decode_graph()` / `decode_step(codes, pos)` of the reference's older single-stream API
+    (model.py:1228-1300): four frames of codes fed at positions 0..3 give, bit for bit, what the
+    engine's own backbone step gives (that step is held to the oracle by the tests above; here the
+    fp32 oracle bounds it loosely, a single bf16 evaluation sits up to ~2.3e-2 from it), and stepping
+    back to a position overwrites it."""
+    from vui_b200 import Engine
+
+    m = nano_model
+    m.setup_decode_graph(max_seq=256)
+    eng = Engine(model=m, max_rows=1, max_seq=256)
+    eng.new_row()
+    g = torch.Generator().manual_seed(5)
+    frames = torch.randint(0, 2048, (4, 16), generator=g)
+    oracle_fp32.seq_lens = [0]
+    for pos in range(4):
+        hid, cb0, eos = m.decode_step(frames[pos].cuda(), pos)
+        assert hid.shape == (1, 1024) and cb0.shape == (1, 2048) and eos.shape == (1, 1)
+        eng._g_codes_in[0].copy_(frames[pos])
+        eh, ec, ee = eng._decode_step()
+        torch.cuda.synchronize()
+        assert torch.equal(hid, eh[:1]) and torch.equal(cb0, ec[:1]) and torch.equal(eos.reshape(-1), ee[:1].reshape(-1)), pos
+        rh, rc, re_ = oracle_fp32.backbone_step([0], frames[pos][None])
+        assert _rel(hid, rh) < 3e-2 and _cos(hid, rh) > COS_TOL, pos
+        assert _rel(cb0, rc) < 3e-2 and _cos(cb0, rc) > COS_TOL, pos
+        assert abs(float(eos) - float(re_)) < 3e-2 * max(1.0, float(rc.abs().max())), pos
+    first = m.decode_step(frames[3].cuda(), 3)[0].clone()
+    again = m.decode_step(frames[3].cuda(), 3)[0]
+    assert torch.equal(first, again)  # same position, same history: bit-identical
+    with pytest.raises(RuntimeError):
+        type(m).decode_step(type(m).__new__(type(m)), frames[0], 0)

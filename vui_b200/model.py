@@ -220,6 +220,38 @@ class VuiB200(torch.nn.Module):
             raise RuntimeError("this checkpoint has no spk_proj")
         return F.linear(spk_emb.to(self.device_, torch.bfloat16), self.sd["spk_proj.weight"]).reshape(1, 1, -1)
 
+    # ---- the reference's older single-stream API (Vui.setup_decode_graph / decode_step,
+    #      model.py:1228-1300; used by demo/cli.py and inference.py) --------------------------
+    def setup_decode_graph(self, pool=None, max_seq: int | None = None) -> None:
+        """One slot, static I/O buffers and one captured backbone step.  ``pool`` is accepted
+        for signature compatibility (the library works in a caller-provided workspace)."""
+        from .engine import Engine  # the engine owns the native handle; imported late to avoid a cycle
+
+        self._decode_engine = Engine(model=self, max_rows=1, max_seq=max_seq)
+        self._decode_row = self._decode_engine.new_row()
+        self._decode_graph = None
+
+    @torch.inference_mode()
+    def decode_step(self, codes: Tensor, pos: int) -> tuple[Tensor, Tensor, Tensor]:
+        """Feed one frame of codes (Q,) at position ``pos``: returns the static buffers
+        (hidden (1, d), codec logits (1, CS), eos logit (1, 1)); the KV length becomes pos + 1."""
+        eng = getattr(self, "_decode_engine", None)
+        if eng is None:
+            raise RuntimeError("call setup_decode_graph() first")
+        eng._g_codes_in[0].copy_(codes.to(eng.device))
+        eng._rewind_row(self._decode_row, int(pos))
+        if self._decode_graph is None:
+            eng._decode_step()  # warm-up outside capture (it advances the position: put it back)
+            eng._rewind_row(self._decode_row, int(pos))
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                eng._decode_step()
+            eng._rewind_row(self._decode_row, int(pos))
+            self._decode_graph = g
+        self._decode_graph.replay()
+        return eng._g_hidden_out[:1], eng._g_cb0_out[:1], eng._g_eos_out[:1].reshape(1, 1)
+
     def weight_bytes_per_step(self) -> int:
         """Distinct weight bytes one decode step reads: every backbone, head and
         depth-transformer matrix once (embedding tables are gathered, not streamed)."""
