@@ -129,6 +129,14 @@ int32_t vuib_bind_rope(VuibEngine* e, const void* freqs_cis_dev);
 /* Copies *s to the device-side control block (async on `stream`). */
 int32_t vuib_set_sampling(VuibEngine* e, const VuibSampling* s, void* stream);
 
+/* Optional per-row statistics of the cb0 draw (NULL disables): cb0_stats_dev is (max_rows, 2) fp32 on
+ * the device; every frame row r gets [2r] = entropy in nats and [2r+1] = largest probability of
+ * softmax(repetition-penalised cb0 logits / temperature) over the whole codebook.  Replaces
+ * _entropy_top1 of Engine._stream_row (engine.py:1369-1372), which the streaming gate averages over
+ * the first frames of a chunk (engine.py:1418-1424, 1455-1460, 1488-1516).  Set it before frames are
+ * captured in a graph; the per-frame kernels write it, the opt-in one-kernel paths do not. */
+int32_t vuib_set_stats(VuibEngine* e, float* cb0_stats_dev);
+
 /* Optional debug taps for the parity tests (NULL disables each):
  *  layer_hidden: (n_layers, max_rows, d) bf16 - residual stream after each block
  *  rq_logits:    (max_rows, Q-1, CS) bf16     - depth-head logits per codebook   */

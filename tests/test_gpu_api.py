@@ -137,3 +137,47 @@ def test_cut_short_chunk_is_retried_at_lower_temperature(model_tok):
     assert codes.shape[1] == 16 and codes.shape[0] == 2 * min_frames
     assert codes.min() >= 0 and codes.max() < 2048
     eng.check_device()
+
+
+def test_cb0_statistics_and_streaming_entropy_gate(model_tok):
+    """The sampler reports entropy and top probability of softmax(cb0 logits / T) (what the reference's
+    `_entropy_top1` computes, engine.py:1369-1372); the streaming gate (engine.py:1385-1533) holds the
+    first gate_frames frames back, retries the chunk at 0.5 and 0.3 while their mean entropy is above the
+    threshold, and otherwise only delays them: a gate that passes yields exactly the ungated frames."""
+    from vui_b200 import Engine, GenConfig
+
+    eng = Engine(model=model_tok, max_rows=1, max_seq=512)
+    text = "This sentence is long enough for a dozen frames of speech, at the very least."
+    base = dict(temperature=0.8, top_k=50, rep_penalty=1.0, max_secs=2.0, min_secs=0.4, eos_threshold=2.0,
+                sentence_only=True)
+
+    def stream(cfg):
+        eng.reset()
+        eng._ws_reset_counters()
+        row = eng.new_row()
+        out = [f.clone() for f in eng._stream_codes(row, text, cfg)]
+        row.close()
+        return torch.stack(out)
+
+    plain = stream(GenConfig(**base))
+    # statistics of the last frame's cb0 draw against torch on the logits the engine exposes
+    p = torch.softmax(eng._g_cb0_out[0].float() / 0.8, dim=-1)
+    ent = float(-(p * p.clamp_min(1e-9).log()).sum())
+    st = eng._g_cb0_stats[0].cpu()
+    assert abs(float(st[0]) - ent) < 2e-3 * max(1.0, ent) and abs(float(st[1]) - float(p.max())) < 1e-4
+    assert 0.0 < float(st[0]) <= 7.63  # ln 2048
+
+    passed = stream(GenConfig(**base, gate_frames=4, gate_entropy_max=100.0))
+    assert torch.equal(plain, passed)
+
+    rewinds, temps = [], []
+    orig_rewind, orig_apply = eng._rewind_row, eng._apply_cfg
+    eng._rewind_row = lambda row, off: (rewinds.append(off), orig_rewind(row, off))[1]
+    eng._apply_cfg = lambda cfg, temperature=None, greedy=False: (temps.append(temperature),
+                                                                  orig_apply(cfg, temperature, greedy))[1]
+    gated = stream(GenConfig(**base, gate_frames=4, gate_entropy_max=0.0, gate_retries=2))
+    eng._rewind_row, eng._apply_cfg = orig_rewind, orig_apply
+    assert len(rewinds) == 2 and rewinds[0] == rewinds[1]           # two retries from the chunk's start
+    assert [t for t in temps if t is not None] == [0.5, 0.3]
+    assert gated.shape == plain.shape and gated.min() >= 0 and gated.max() < 2048
+    eng.check_device()

@@ -82,6 +82,7 @@ SYMBOLS = {
     "vuib_bind_kv": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P), _P]),
     "vuib_bind_rope": (C.c_int32, [_P, _P]),
     "vuib_set_sampling": (C.c_int32, [_P, C.POINTER(VuibSampling), _P]),
+    "vuib_set_stats": (C.c_int32, [_P, _P]),
     "vuib_set_taps": (C.c_int32, [_P, _P, _P]),
     "vuib_prefill": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P]),
     "vuib_backbone_step": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P, _P, _P]),

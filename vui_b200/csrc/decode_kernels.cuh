@@ -976,6 +976,10 @@ struct SampleArgs {
     const bf16* code_emb;
     const bf16* pos_emb;
     int emb_p, emb_rd, emb_row_mul, emb_row_add;
+    // optional, cb0 only: stats_out[2r] = entropy (nats) and stats_out[2r+1] = largest probability of
+    // softmax(penalised logits / temperature) over the whole codebook - what the reference's streaming
+    // gate averages over the first frames of a chunk (engine.py:1369-1372, 1418-1424, 1455-1460)
+    float* stats_out;
 };
 
 struct SampleSmem {
@@ -1037,6 +1041,31 @@ __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, S
     for (int w = 1; w < 8; ++w)
         if (s_f[w] > bv || (s_f[w] == bv && s_i[w] < bi)) { bv = s_f[w]; bi = s_i[w]; }
     bar_named(bar_id, SAMPLE_THREADS);
+
+    if (is_cb0 && a.stats_out) {
+        // H = log Z - sum e_i x_i / Z with x_i = (v_i - max) / T, e_i = exp(x_i); p_max = 1 / Z
+        const float invT = 1.0f / ctl.temperature;
+        float z = 0.f, sx = 0.f;
+#pragma unroll
+        for (int j = 0; j < SAMPLE_EL; ++j) {
+            const float x = (v[j] - bv) * invT;
+            const float e = expf(x);
+            z += e;
+            sx = fmaf(e, x, sx);
+        }
+        z = warp_sum(z);
+        sx = warp_sum(sx);
+        float* scr = reinterpret_cast<float*>(hist);  // free until the k-th value search clears it
+        if (lane == 0) { scr[warp] = z; scr[8 + warp] = sx; }
+        bar_named(bar_id, SAMPLE_THREADS);
+        if (tid == 0) {
+            float Z = 0.f, SX = 0.f;
+            for (int w = 0; w < SAMPLE_THREADS / 32; ++w) { Z += scr[w]; SX += scr[8 + w]; }
+            a.stats_out[2 * r] = logf(Z) - SX / Z;
+            a.stats_out[2 * r + 1] = 1.0f / Z;
+        }
+        bar_named(bar_id, SAMPLE_THREADS);
+    }
 
     int choice = bi;
     if (top_k != 1) {

@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(DC_THREADS, 1) k_depth_cluster(DepthArgs a) {
     sa.codes_out = a.codes_out;
     sa.Q = a.Q;
     sa.emb_out = nullptr;
+    sa.stats_out = nullptr;
 
     // ---- cb0: CTA r draws for stream r and tells everyone ---------------------------------
     if ((int)c < B && tid < SAMPLE_THREADS) {

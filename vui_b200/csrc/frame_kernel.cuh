@@ -380,6 +380,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_frame(FrameArgs a) {
     sa.codes_out = a.codes_io;
     sa.Q = a.Q;
     sa.emb_out = nullptr;
+    sa.stats_out = nullptr;
     {
         EpiProjPos ep{static_cast<const bf16*>(m.w.rq_backbone_proj), D, pos_emb, b.rq_x2, RD, 2};
         WPref<D, EpiProjPos> wp;

@@ -980,6 +980,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_frame_ll(LLArgs la) {
     sa.codes_out = a.codes_io;
     sa.Q = a.Q;
     sa.emb_out = nullptr;
+    sa.stats_out = nullptr;
     uint32_t rx_tag = ll_tag(++g);  // depth positions 0 (projection of the hidden state) and 1 (cb0 token)
     {
         TEpiProjPos ep{static_cast<const bf16*>(m.w.rq_backbone_proj), D, pos_emb, TRX2, RD, 2, rx_tag};

@@ -59,6 +59,7 @@ struct VuibEngine {
     DevModel dm;        // host copy of what the persistent kernel reads from the workspace
     int num_sms;        // 0 until the first persistent launch asks the device
     int coop;           // launch the frame kernel cooperatively
+    float* cb0_stats;   // optional (max_rows, 2) fp32: entropy and top probability of each cb0 draw
     TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
     char err[256];
 };
@@ -358,6 +359,12 @@ extern "C" int32_t vuib_set_sampling(VuibEngine* e, const VuibSampling* s, void*
                        static_cast<cudaStream_t>(stream)));
     // the source is a stack object: make sure the copy has read it before returning
     CK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_set_stats(VuibEngine* e, float* cb0_stats_dev) {
+    if (!e) return VUIB_ERR_NULL;
+    e->cb0_stats = cb0_stats_dev;
     return VUIB_OK;
 }
 
@@ -777,6 +784,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     sa.eos_prob = eos_prob;
     sa.bump_frame = 0;
     sa.zero_from = Qn < Q ? Qn : 0;
+    sa.stats_out = e->cb0_stats;
     // the sampler also builds depth position 1 from the code it drew (rows 2b+1)
     sa.emb_out = wsp<bf16>(e, L.rq_x2);
     sa.code_emb = static_cast<const bf16*>(e->w.rq_code_emb);

@@ -31,6 +31,7 @@ from .text import chunk_text, simple_clean
 FRAME_RATE = 12.5  # codec frames per second (src/vui/qwen_codec.py:27-29)
 MIN_FPW = 2.0              # frames per word below which a finished chunk counts as cut short (engine.py:909)
 RETRY_TEMPS = (0.5, 0.3)   # temperatures of the retries (engine.py:910)
+GATE_RETRY_TEMPS = (0.5, 0.3)  # and of the streaming gate's retries (engine.py:1367)
 SAMPLE_RATE = 24000
 DEFAULT_WPS = 3.0
 RQ_TOP_K = 100  # the reference captures its depth graphs with top_k=100 (engine.py:395-397)
@@ -282,6 +283,8 @@ class Engine:
         self._g_cb0_out = torch.zeros(N, self.CS, device=dev, dtype=self.dtype)
         self._g_eos_out = torch.zeros(N, 1, device=dev, dtype=self.dtype)
         self._g_eos_prob = torch.zeros(N, device=dev, dtype=torch.float32)
+        self._g_cb0_stats = torch.zeros(N, 2, device=dev, dtype=torch.float32)  # entropy, top probability of the cb0 draw
+        self._ck(self._lib.vuib_set_stats(self._handle, C.c_void_p(self._g_cb0_stats.data_ptr())))
         self._g_slot_idx = torch.arange(N, device=dev, dtype=torch.int32)
         self._g_seq_inc = torch.ones(N, device=dev, dtype=torch.int32)
         self._buckets = _make_buckets(N)
@@ -900,8 +903,7 @@ class Engine:
     def _stream_codes(self, row: Row, text: str, cfg: GenConfig, cancel=None, *, reset_rep: bool = True,
                       final_turn: bool = False) -> Iterator[Tensor]:
         """Per-frame streaming for max_rows=1: yields (Q,) code tensors on the
-        host (engine.py:1308-1535 without the entropy gate, which only delays
-        the first frames of a chunk)."""
+        host (engine.py:1308-1535, entropy gate included)."""
         max_frames = int(cfg.max_secs * FRAME_RATE)
         min_frames = int(cfg.min_secs * FRAME_RATE)
         max_seq = self.max_seq - 10
@@ -929,22 +931,73 @@ class Engine:
             if ch["sc"] and row._spk_token_2 is not None:
                 row._active_speaker = 1 - row._active_speaker
             cap = cfg.max_turn_frames(len(ch["text"].split()), row.prompt_wps)
-            hidden = self._add_agent_text(row, ch["text"], final=(final_turn and ci == last))
-            codes = self._first_frames([row], hidden[None])[0]
-            self._set_codes_in(0, codes)
-            yield codes.cpu()
-            total += 1
-            offset = row.offset
-            for step in range(1, cap):
-                if total >= max_frames or offset >= max_seq or (cancel is not None and cancel.is_set()):
-                    return
-                self._frame_step(1)
-                offset += 1
-                h_codes, h_eos = self._read_frame(1)
-                if step >= min_frames and float(h_eos[0]) > cfg.eos_threshold:
-                    break
-                yield h_codes[0].clone()
-                total += 1
+            # Hallucination gate (engine.py:1385-1533): the first gate_frames frames of the first
+            # chunk are held back; if the mean entropy of their cb0 distributions is above
+            # gate_entropy_max the chunk is rewound and spoken again at 0.5, then 0.3.
+            use_gate = cfg.gate_frames > 0 and ci == 0 and reset_rep
+            chunk_start = row.offset
+            retry = 0
+            while True:
+                if retry > 0:
+                    self._apply_cfg(cfg, temperature=GATE_RETRY_TEMPS[min(retry - 1, len(GATE_RETRY_TEMPS) - 1)])
+                    self._rewind_row(row, chunk_start)
+                    self._rep_reset(cfg.rep_penalty, cfg.rep_window)
+                held: list[Tensor] = []
+                entropies: list[float] = []
+                hidden = self._add_agent_text(row, ch["text"], final=(final_turn and ci == last))
+                codes = self._first_frames([row], hidden[None])[0]
+                self._set_codes_in(0, codes)
+                if use_gate:
+                    entropies.append(float(self._g_cb0_stats[0, 0]))
+                    held.append(codes.cpu())
+                else:
+                    yield codes.cpu()
+                    total += 1
+                offset = row.offset
+                retry_triggered = False
+                for step in range(1, cap):
+                    if total >= max_frames or offset >= max_seq or (cancel is not None and cancel.is_set()):
+                        if cancel is None or not cancel.is_set():
+                            for hc in held:
+                                yield hc
+                                total += 1
+                        self._apply_cfg(cfg)
+                        return
+                    self._frame_step(1)
+                    offset += 1
+                    h_codes, h_eos = self._read_frame(1)
+                    gathering = use_gate and len(held) < cfg.gate_frames
+                    if gathering:
+                        entropies.append(float(self._g_cb0_stats[0, 0]))
+                    if step >= min_frames and float(h_eos[0]) > cfg.eos_threshold:
+                        for hc in held:  # a chunk shorter than the gate: flushed without a decision
+                            yield hc
+                            total += 1
+                        held = []
+                        break
+                    if gathering:
+                        held.append(h_codes[0].clone())
+                        if len(held) == cfg.gate_frames:
+                            if sum(entropies) / len(entropies) > cfg.gate_entropy_max and retry < cfg.gate_retries:
+                                retry_triggered = True
+                                break
+                            for hc in held:
+                                yield hc
+                                total += 1
+                            held = []
+                            use_gate = False
+                    else:
+                        yield h_codes[0].clone()
+                        total += 1
+                if retry_triggered:
+                    retry += 1
+                    continue
+                for hc in held:
+                    yield hc
+                    total += 1
+                break
+            if retry > 0:
+                self._apply_cfg(cfg)
 
     def _stream_row(self, row, text, cfg, cancel=None, *, reset_rep=True, final_turn=False):
         for codes in self._stream_codes(row, text, cfg, cancel, reset_rep=reset_rep, final_turn=final_turn):
