@@ -134,7 +134,7 @@ int32_t vuib_set_sampling(VuibEngine* e, const VuibSampling* s, void* stream);
  * softmax(repetition-penalised cb0 logits / temperature) over the whole codebook.  Replaces
  * _entropy_top1 of Engine._stream_row (engine.py:1369-1372), which the streaming gate averages over
  * the first frames of a chunk (engine.py:1418-1424, 1455-1460, 1488-1516).  Set it before frames are
- * captured in a graph; the per-frame kernels write it, the opt-in one-kernel paths do not. */
+ * captured in a graph. */
 int32_t vuib_set_stats(VuibEngine* e, float* cb0_stats_dev);
 
 /* Optional debug taps for the parity tests (NULL disables each):
@@ -148,7 +148,8 @@ int32_t vuib_set_taps(VuibEngine* e, void* layer_hidden_dev, void* rq_logits_dev
  *      slot must carry consecutive positions starting at that slot's length.
  *  emb: (n_rows, d) bf16;  hidden_out: (n_rows, d) bf16 final-norm output.
  * Does not touch seq_lens (the caller adds the segment lengths, as the reference
- * does on the host). */
+ * does on the host).  Slots and positions outside the cache are clamped and recorded in the
+ * device flag, so K/V are never written out of bounds. */
 int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* row_slot_dev,
                      const int32_t* row_pos_dev, const void* emb_dev, void* hidden_out_dev,
                      void* stream);
@@ -192,7 +193,9 @@ int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* slots_dev,
  * the QKV kernel has already done.  Row r attends keys [0, row_pos[r]] of slot row_slot[r];
  * GQA (n_heads / n_kv_heads query heads per KV head), scale 1/sqrt(head_dim), fp32 softmax.
  *  q, out: (n_rows, n_heads*head_dim) bf16, q with RoPE applied; n_rows <= max(max_rows,
- *  max_prefill_rows).  Uses the bound workspace for its split-KV partial results. */
+ *  max_prefill_rows).  Uses the bound workspace for its split-KV partial results.
+ *  A slot outside [0, n_slots) or a position outside [0, max_seq) is clamped into the cache and
+ *  recorded in the device flag (vuib_check_device_flag); nothing is read out of bounds. */
 int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, const void* q_dev,
                        const int32_t* row_slot_dev, const int32_t* row_pos_dev, void* out_dev,
                        void* stream);
@@ -208,6 +211,8 @@ int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, const void*
  *  head_dim 64.  Larger sizes return VUIB_ERR_RANGE with the reason in `err`.
  *  k_cache / v_cache: (slots, max_seq, n_kv_heads, 64) bf16 of ONE layer; q, out: (n_rows,
  *  n_heads*64) bf16; row r attends keys [0, row_pos[r]] of slot row_slot[r].
+ *  Positions outside [0, max_seq) are clamped on the device and negative slots read slot 0; the
+ *  number of slots is not known here, so a slot past the end of the caller's cache cannot be caught.
  *  The first call on a device looks up the array's device address (cudaGetSymbolAddress), so
  *  make that call before starting any stream capture.  All calls share the one array: it keeps
  *  the last call's contents (the call clears what it needs zeroed), and two calls that overlap
@@ -231,6 +236,20 @@ int32_t vuib_embed_codes(VuibEngine* e, int32_t n_rows, const int64_t* codes_dev
 int32_t vuib_sample_rows(VuibEngine* e, int32_t B, const int32_t* slots_dev, const void* logits_dev,
                          int32_t codebook, int64_t* codes_out_dev, void* stream);
 
+/* Single fused ops for parity tests.  With an identity matrix as w the product passes its staged
+ * input through exactly, so the outputs can be held bit for bit against the reference's modules:
+ *  vuib_debug_norm_linear: out (n_rows, n_out) = bf16(W . RMSNorm(x) * norm_w)   (RMSNorm.forward,
+ *      src/vui/model.py:292-297, as staged in front of Wqkv / w1 / w3); x (n_rows, d_model).
+ *  vuib_debug_linear_rope: out (n_rows, d_model) = RoPE(bf16(W . x)) at position row_pos[r], every
+ *      64 columns one head (apply_rotary_emb, src/vui/rope.py:23-57); W (d_model, d_model).
+ * tensor_cores = 0 runs the weight-streaming GEMV kernels, 1 the tcgen05 GEMM kernels
+ * (n_out a multiple of 128).  n_rows <= max(max_rows, max_prefill_rows). */
+int32_t vuib_debug_norm_linear(VuibEngine* e, int32_t n_rows, const void* x_dev, const void* norm_w_dev,
+                               const void* w_dev, int32_t n_out, void* out_dev, int32_t tensor_cores,
+                               void* stream);
+int32_t vuib_debug_linear_rope(VuibEngine* e, int32_t n_rows, const void* x_dev, const void* w_dev,
+                               const int32_t* row_pos_dev, void* out_dev, int32_t tensor_cores, void* stream);
+
 /* Clears the repetition-penalty state (counts + rolling history) of one slot, or
  * of every slot when slot == -1: Engine._rep_reset / _rep_reset_slot
  * (engine.py:555-569, 594-595).  Async on `stream`. */
@@ -241,14 +260,21 @@ int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream);
  * (The reference has no equivalent: its draws come from torch's global generator.) */
 int32_t vuib_reset_state(VuibEngine* e, void* stream);
 
-/* Profiling aid for the persistent frame kernel: when the environment variable VUIB_TRACE is
- * set, CTA 0 records the device clock (ns) when it arrives at and when it leaves each grid
- * barrier of the last launch.  Copies up to max_entries (arrive, leave) pairs to out_host
- * (2 uint64 each) and their count to *n_out, then 16 stamps taken inside one attention unit or
- * tensor-core GEMM CTA to out_host[2*max_entries .. 2*max_entries+16).  out_host holds
- * 2*max_entries+16 values.
- * Synchronous. */
-int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t max_entries, int32_t* n_out);
+/* Profiling aid: when the environment variable VUIB_TRACE is set, CTA (0,0) of a tensor-core GEMM
+ * launch records device-clock stamps (ns) at its pipeline stages.  Copies the first n_stamps (<= 32)
+ * stamps of the last such launch to out_host.  Synchronous. */
+int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t n_stamps);
+
+/* Every wait inside a kernel (the tile counter on which the K-splits of a tensor-core GEMM meet, its
+ * mbarrier pipeline) gives up after a bounded number of polls, records the device flag and lets the
+ * kernel finish; this sets that bound (default 2^22 polls, at least 16).  A frame that reported the
+ * flag is followed by vuib_reset_state before the handle is used again. */
+int32_t vuib_set_wait_limit(VuibEngine* e, uint32_t polls);
+
+/* Test hook for the bound above: presets the arrival counters so that the next tensor-core GEMM
+ * launch sees one arrival fewer than it waits for.  Its wait runs out, the flag is recorded, the
+ * kernel returns.  Nothing faults or hangs.  Synchronises `stream`. */
+int32_t vuib_debug_withhold_arrival(VuibEngine* e, void* stream);
 
 /* Position-only rewind / reset (engine.py:651-654).  Synchronous small copies. */
 int32_t vuib_set_seq_len(VuibEngine* e, int32_t slot, int32_t len);

@@ -74,6 +74,28 @@ def test_gather_sum_bit_exact(eng1, golden_dir):
     assert torch.equal(emb_k.float().cpu(), fx["emb_out"].float())
 
 
+@pytest.mark.parametrize("tensor_cores", [False, True])
+def test_rmsnorm_and_rope_bit_exact(eng8, golden_dir, tensor_cores):
+    """The RMSNorm staging and the RoPE epilogue of both kernel families against the reference
+    modules' bf16 outputs (RMSNorm.forward model.py:292-297; apply_rotary_emb rope.py:50), bit for
+    bit: an identity matrix as the Linear passes the staged row through unchanged."""
+    fx = torch.load(os.path.join(golden_dir, "ops_bf16.pt"))
+    eye = torch.eye(1024, dtype=torch.bfloat16)
+    y = eng8._debug_norm_linear(fx["norm_x"], fx["norm_w"], eye, tensor_cores).cpu()
+    assert torch.equal(y, fx["norm_y"])
+    q = fx["rope_q"].reshape(5, 1024)
+    out = eng8._debug_linear_rope(q, eye, fx["rope_pos"], tensor_cores).cpu()
+    assert torch.equal(out.view(5, 16, 64), fx["rope_out"])
+    # and with the real Wqkv of layer 0 behind the norm: the reference's Linear output within bf16 rounding
+    w = eng8.model.sd["decoder.blocks.0.attn.Wqkv.weight"]
+    ones = torch.ones(1024, dtype=torch.bfloat16)
+    got = eng8._debug_norm_linear(fx["mlp_x"], ones, w, tensor_cores).float().cpu()
+    h = fx["mlp_x"].float()
+    want = torch.nn.functional.linear((h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)).bfloat16().float(), w.float().cpu())
+    assert (got - want).abs().max().item() <= 2.0 ** -8 * want.abs().max().item() + 1e-6
+    eng8.check_device()
+
+
 def test_prefill_and_frame0_vs_oracle(eng1, oracle_gpu, oracle_fp32):
     """64-token prefill -> final hidden, cb0 logits, depth logits of frame 0."""
     eng, o = eng1, oracle_gpu
@@ -277,113 +299,6 @@ def test_batch_invariance_and_ragged(eng8, eng1):
         r.close()
 
 
-def test_persistent_kernel_equals_per_phase_kernels(eng8):
-    """The one-launch persistent frame kernel and the graph of per-phase kernels run the same
-    arithmetic: identical codes, hidden states and logits, greedy and sampled, B = 1 and ragged B = 3."""
-    from vui_b200 import GenConfig
-
-    eng = eng8
-    cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4)
-    for lens, greedy in (([33], True), ([40, 150, 77], True), ([64, 200, 31], False)):
-        outs = []
-        for on in ("1", ""):
-            os.environ["VUIB_PERSISTENT"] = on
-            eng._graphs = {}
-            eng.reset()
-            eng._ws_reset_counters()
-            rows = [eng.new_row() for _ in lens]
-            hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 50 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
-            h = torch.stack([x[-1] for x in hs])
-            codes = eng.generate_frames(rows, h, 5, cfg, greedy=greedy).cpu()
-            torch.cuda.synchronize()
-            outs.append((codes, eng._g_hidden_out[: len(lens)].clone(), eng._g_cb0_out[: len(lens)].clone(),
-                         eng._g_eos_prob[: len(lens)].clone()))
-            eng.check_device()
-            for r in rows:
-                r.close()
-        os.environ["VUIB_PERSISTENT"] = ""
-        eng._graphs = {}
-        for a, b in zip(outs[0], outs[1]):
-            assert torch.equal(a, b), (lens, greedy)
-
-
-def test_tagged_persistent_frame_equals_per_phase_kernels(eng8):
-    """The barrier-free persistent frame kernel (activations handed on as self-validating tagged words)
-    runs the arithmetic of the per-phase kernels: identical codes, hidden states, cb0 logits, EOS
-    probabilities and depth logits; greedy and sampled, B = 1..4 with ragged lengths that cross the
-    128-key attention split, fewer codebooks, and shape changes from one launch to the next."""
-    from vui_b200 import GenConfig
-
-    eng = eng8
-    tap = torch.zeros(8, 15, 2048, device="cuda", dtype=torch.bfloat16)
-    cases = [([33], True, 0), ([40, 150, 77], True, 0), ([300], True, 0), ([64, 200, 31, 130], False, 0),
-             ([50, 60], True, 10), ([129], False, 2), ([33], True, 0)]
-    try:
-        for lens, greedy, ncb in cases:
-            cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4, n_codebooks=ncb)
-            outs = []
-            for on in ("1", ""):
-                os.environ["VUIB_LL"] = on
-                eng._graphs = {}
-                eng._set_taps(None, tap)
-                tap.zero_()
-                eng.reset()
-                eng._ws_reset_counters()
-                rows = [eng.new_row() for _ in lens]
-                hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 90 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
-                h = torch.stack([x[-1] for x in hs])
-                codes = eng.generate_frames(rows, h, 6, cfg, greedy=greedy).cpu()
-                torch.cuda.synchronize()
-                k0 = eng.model.decoder.flash_kv_caches[5].k_cache[rows[0].idx, : lens[0] + 5].clone()
-                outs.append((codes, eng._g_hidden_out[: len(lens)].clone(), eng._g_cb0_out[: len(lens)].clone(),
-                             eng._g_eos_prob[: len(lens)].clone(), tap[: len(lens)].clone(), k0))
-                eng.check_device()
-                for r in rows:
-                    r.close()
-            for j, (a, b) in enumerate(zip(outs[0], outs[1])):
-                assert torch.equal(a, b), (lens, greedy, ncb, j)
-    finally:
-        os.environ["VUIB_LL"] = ""
-        eng._graphs = {}
-        eng._set_taps(None, None)
-
-
-def test_cluster_depth_kernel_equals_per_phase_kernels(eng8):
-    """The depth step as one kernel on a 16-CTA cluster (activations exchanged through distributed
-    shared memory) gives, bit for bit, the codes and depth logits of the per-phase kernels:
-    greedy and sampled, B = 1 and ragged B = 3, and with fewer codebooks."""
-    from vui_b200 import GenConfig
-
-    eng = eng8
-    tap = torch.zeros(8, 15, 2048, device="cuda", dtype=torch.bfloat16)
-    cases = [([33], True, 0), ([40, 150, 77], True, 0), ([64, 200, 31, 90], False, 0), ([50, 60], True, 10)]
-    for lens, greedy, ncb in cases:
-        cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.2, rep_window=4, n_codebooks=ncb)
-        outs = []
-        for on in ("1", ""):
-            os.environ["VUIB_CLUSTER"] = on
-            eng._set_taps(None, tap)
-            tap.zero_()
-            eng.reset()
-            eng._ws_reset_counters()
-            rows = [eng.new_row() for _ in lens]
-            hs = eng._prefill_many([(r, eng.model.token_emb(_ids(n, 70 + i)[None])) for i, (r, n) in enumerate(zip(rows, lens))])
-            h = torch.stack([x[-1] for x in hs])
-            codes = eng.generate_frames(rows, h, 5, cfg, greedy=greedy).cpu()
-            torch.cuda.synchronize()
-            outs.append((codes, tap[: len(lens)].clone(), eng._g_eos_prob[: len(lens)].clone(),
-                         eng._g_hidden_out[: len(lens)].clone()))  # rows past len(lens) are bucket padding
-            eng.check_device()
-            for r in rows:
-                r.close()
-        os.environ["VUIB_CLUSTER"] = ""
-        eng._set_taps(None, None)
-        for a, b in zip(outs[0], outs[1]):
-            assert torch.equal(a, b), (lens, greedy, ncb)
-        if ncb:
-            assert (outs[0][0][:, :, ncb:] == 0).all()
-
-
 def test_tensor_core_path_matches_gemv_path(nano_model, oracle_fp32):
     """Five rows and more run on the tcgen05 GEMM (TMA-fed, accumulators in tensor memory); up to 4
     on the register-tile GEMV.  Same rounding points, different fp32 summation order: a 40-token
@@ -476,26 +391,77 @@ def test_determinism_and_seeded_sampling(eng8):
     assert not torch.equal(outs[0][0], outs[0][1])
 
 
-def test_sampler_distribution(eng8, golden_dir):
-    """cb0 draws at T=0.8, top-k 50 against the reference's top-k distribution (chi-square on
-    the 50 kept entries; nothing outside the support)."""
-    import ctypes as C
+def _chi2(counts, probs, n):
+    exp = probs * n
+    return ((counts - exp) ** 2 / exp).sum().item()
 
+
+def test_sampler_distribution_cb0(eng8, golden_dir):
+    """cb0 draws at T=0.8, top-k 50 (Engine._sample_cb0, engine.py:855-863: softmax, top-k over the
+    probabilities, renormalise) against the distribution the reference computed for the same logits:
+    chi-square on the 50 kept entries, nothing outside the support."""
     fx = torch.load(os.path.join(golden_dir, "ops_bf16.pt"))
     eng = eng8
-    lg = fx["cb0_logits"][0].cuda()
-    probs = fx["cb0_probs_t0.8_k50"][0]
+    for row in (0, 1):
+        lg = fx["cb0_logits"][row].cuda()
+        probs = fx["cb0_probs_t0.8_k50"][row]
+        n = 4000
+        eng._ws_reset_counters()
+        eng._set_sampling(0.8, 50, 3, 1.0, 0, 0)  # the depth rule's k (3) must not leak into cb0
+        draws = eng._sample_rows(lg[None].expand(8, -1).contiguous(), n // 8, cb0=True)
+        counts = torch.bincount(draws.flatten(), minlength=2048).float()
+        support = probs > 0
+        assert int(support.sum()) == 50
+        assert counts[~support].sum() == 0
+        chi2 = _chi2(counts[support], probs[support], n)
+        assert chi2 < 100.0, chi2  # 49 dof: mean 49, p(chi2 > 100) ~ 2e-5
+
+
+def test_sampler_distribution_depth_rule(eng8, golden_dir):
+    """Depth codebooks (model.py:955-962): logits / T, keep entries >= the k-th value, softmax, draw."""
+    fx = torch.load(os.path.join(golden_dir, "ops_bf16.pt"))
+    eng = eng8
+    lg = fx["cb0_logits"][0]
+    sc = lg.float() / 0.8
+    kth = sc.topk(50).values[-1]
+    probs = torch.softmax(sc.masked_fill(sc < kth, float("-inf")), dim=-1)
     n = 4000
-    counts = torch.zeros(2048)
-    eng._set_sampling(0.8, 50, 50, 1.0, 0, 0)
-    draws = eng._sample_rows(lg[None].expand(8, -1).contiguous(), n // 8)
-    for c in draws.flatten().tolist():
-        counts[c] += 1
+    eng._ws_reset_counters()
+    eng._set_sampling(0.8, 3, 50, 1.0, 0, 0)
+    draws = eng._sample_rows(lg[None].expand(8, -1).contiguous().cuda(), n // 8)
+    counts = torch.bincount(draws.flatten(), minlength=2048).float()
     support = probs > 0
     assert counts[~support].sum() == 0
-    exp = probs[support] * n
-    chi2 = ((counts[support] - exp) ** 2 / exp).sum().item()
-    assert chi2 < 100.0, chi2  # 49 dof: mean 49, p(chi2 > 100) ~ 2e-5
+    assert _chi2(counts[support], probs[support], n) < 60.0 + 1.5 * int(support.sum())
+
+
+def test_first_frame_cb0_ignores_top_k(eng8, golden_dir):
+    """cb0 of a chunk's first frame is drawn from the WHOLE distribution even when top-k is set
+    (engine.py:936-937, 1416-1424): draws land outside the top-50 at the rate softmax(l/T) gives, and
+    32 equal-count bins of the codebook (sorted by probability) pass a chi-square test."""
+    fx = torch.load(os.path.join(golden_dir, "ops_bf16.pt"))
+    eng = eng8
+    lg = fx["cb0_logits"][0]
+    probs = torch.softmax(lg.float() / 0.8, dim=-1)
+    order = probs.argsort(descending=True)
+    n = 4000
+    eng._ws_reset_counters()
+    eng._set_sampling(0.8, 50, 1, 1.0, 0, 2)  # two codebooks: the depth loop after the draw stays short
+    draws = eng._sample_first_frame(lg[None].expand(8, -1).contiguous(), n // 8)
+    eng._set_sampling(1.0, 1, 1, 1.0, 0, 0)
+    counts = torch.bincount(draws.flatten(), minlength=2048).float()
+    p_out = probs[order[50:]].sum().item()
+    frac_out = counts[order[50:]].sum().item() / n
+    assert p_out > 0.5  # these logits are flat: most of the mass lies outside the top 50
+    assert abs(frac_out - p_out) < 5 * (p_out * (1 - p_out) / n) ** 0.5, (frac_out, p_out)
+    binned_c = counts[order].reshape(32, 64).sum(1)
+    binned_p = probs[order].reshape(32, 64).sum(1)
+    assert _chi2(binned_c, binned_p, n) < 80.0  # 31 dof
+    # greedy (top_k_cb0 == 1) stays greedy on the first frame
+    eng._set_sampling(1.0, 1, 1, 1.0, 0, 2)
+    g = eng._sample_first_frame(lg[None].expand(8, -1).contiguous(), 1)
+    assert g.flatten().tolist() == [int(torch.argmax(lg.float()))] * 8
+    eng._set_sampling(1.0, 1, 1, 1.0, 0, 0)
 
 
 def test_greedy_first_index_on_ties(eng8):
@@ -586,3 +552,78 @@ def test_older_single_stream_api_decode_step(nano_model, oracle_fp32):
     assert torch.equal(first, again)  # same position, same history: bit-identical
     with pytest.raises(RuntimeError):
         type(m).decode_step(type(m).__new__(type(m)), frames[0], 0)
+
+
+def test_bad_slot_and_position_are_clamped_and_flagged(eng8):
+    """Out-of-range slots / positions handed to the C ABI never index outside the cache: the kernels
+    clamp them and record the device flag (prefill rows, the attention entry point, the sampler)."""
+    import ctypes as C
+
+    from vui_b200._lib import VuibError
+
+    eng = eng8
+    eng.reset()
+    eng.check_device()
+    guard_k = eng._kv.clone()
+    P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    emb = torch.randn(3, 1024, generator=torch.Generator().manual_seed(1)).to("cuda", torch.bfloat16)
+    out = torch.empty_like(emb)
+    for slots, poss in (([0, 99, 1], [0, 0, 0]), ([0, -5, 1], [0, 0, 0]), ([0, 1, 2], [0, 10 ** 6, 0]), ([0, 1, 2], [0, -1, 0])):
+        slot = torch.tensor(slots, dtype=torch.int32, device="cuda")
+        pos = torch.tensor(poss, dtype=torch.int32, device="cuda")
+        eng._ck(eng._lib.vuib_prefill(eng._handle, 3, P(slot), P(pos), P(emb), P(out), eng._stream))
+        with pytest.raises(VuibError) as ei:
+            eng.check_device()
+        assert ei.value.code == -7
+        eng.check_device()  # cleared
+        assert torch.isfinite(out.float()).all()
+    # only slots 0..2, 8 (clamped high slot) and positions 0 / max_seq-1 of them may have been written
+    touched = (eng._kv != guard_k).any(dim=-1).any(dim=-1)  # (L, 2, slots, max_seq)
+    allowed = torch.zeros_like(touched)
+    allowed[:, :, :, 0] = True
+    allowed[:, :, :, eng.max_seq - 1] = True
+    assert not (touched & ~allowed).any()
+    # attention entry: bad position and slot
+    q = torch.randn(2, 1024, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    o = eng._attention(0, q, torch.tensor([0, 50]), torch.tensor([10 ** 6, 3]))
+    torch.cuda.synchronize()
+    assert torch.isfinite(o.float()).all()
+    with pytest.raises(VuibError):
+        eng.check_device()
+    # sampler: slot outside the per-slot state
+    lg = torch.zeros(2, 2048, device="cuda", dtype=torch.bfloat16)
+    codes = torch.zeros(2, device="cuda", dtype=torch.long)
+    bad = torch.tensor([0, 1000], dtype=torch.int32, device="cuda")
+    eng._ck(eng._lib.vuib_sample_rows(eng._handle, 2, P(bad), P(lg), 0, P(codes), eng._stream))
+    with pytest.raises(VuibError):
+        eng.check_device()
+    eng._ws_reset_counters()
+    eng.check_device()
+
+
+def test_bounded_wait_runs_out_and_reports(nano_model):
+    """A wait inside a kernel that cannot complete (one arrival of the tensor-core GEMM's tile counter
+    withheld by a test hook) gives up after the configured number of polls, records the device flag and
+    the kernel returns; after vuib_reset_state the same call is bit-identical to a clean run."""
+    from vui_b200 import Engine
+    from vui_b200._lib import VuibError
+
+    eng = Engine(model=nano_model, max_rows=1, max_seq=64, max_prefill_rows=16)
+    ids = _ids(8, 4)  # 8 rows: the tensor-core path, K split over several CTAs per tile
+    row = eng.new_row()
+    clean = eng.prefill_ids(row, ids).clone()
+    eng.check_device()
+    eng._rewind_row(row, 0)
+    eng._ck(eng._lib.vuib_set_wait_limit(eng._handle, 20000))
+    eng._ck(eng._lib.vuib_debug_withhold_arrival(eng._handle, eng._stream))
+    eng.prefill_ids(row, ids)
+    torch.cuda.synchronize()  # the kernels returned: nothing hangs
+    with pytest.raises(VuibError) as ei:
+        eng.check_device()
+    assert ei.value.code == -7 and "wait" in str(ei.value)
+    eng._ck(eng._lib.vuib_set_wait_limit(eng._handle, 1 << 22))
+    eng._ws_reset_counters()
+    eng._rewind_row(row, 0)
+    again = eng.prefill_ids(row, ids)
+    eng.check_device()
+    assert torch.equal(again, clean)

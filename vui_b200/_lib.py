@@ -19,8 +19,7 @@ _OBJ = os.path.join(_CSRC, "_obj")
 _API_H = os.path.join(_ROOT, "include", "vuib200.h")
 # translation unit -> the headers it includes (a unit is recompiled when one of them changes)
 UNITS = {
-    "vuib200.cu": ["decode_kernels.cuh", "frame_kernel.cuh", "tc_gemm.cuh", "depth_cluster.cuh", "frame_ll.h"],
-    "frame_ll.cu": ["decode_kernels.cuh", "frame_kernel.cuh", "frame_ll.h"],
+    "vuib200.cu": ["decode_kernels.cuh", "tc_gemm.cuh"],
 }
 SOURCES = [os.path.join(_CSRC, u) for u in UNITS]
 HEADERS = sorted({os.path.join(_CSRC, h) for hs in UNITS.values() for h in hs}) + [_API_H]
@@ -94,9 +93,13 @@ SYMBOLS = {
                                            C.c_char_p, C.c_size_t]),
     "vuib_embed_codes": (C.c_int32, [_P, C.c_int32, _P, _P, _P]),
     "vuib_sample_rows": (C.c_int32, [_P, C.c_int32, _P, _P, C.c_int32, _P, _P]),
+    "vuib_debug_norm_linear": (C.c_int32, [_P, C.c_int32, _P, _P, _P, C.c_int32, _P, C.c_int32, _P]),
+    "vuib_debug_linear_rope": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, C.c_int32, _P]),
     "vuib_rep_reset": (C.c_int32, [_P, C.c_int32, _P]),
     "vuib_reset_state": (C.c_int32, [_P, _P]),
-    "vuib_read_trace": (C.c_int32, [_P, C.POINTER(C.c_uint64), C.c_int32, C.POINTER(C.c_int32)]),
+    "vuib_read_trace": (C.c_int32, [_P, C.POINTER(C.c_uint64), C.c_int32]),
+    "vuib_set_wait_limit": (C.c_int32, [_P, C.c_uint32]),
+    "vuib_debug_withhold_arrival": (C.c_int32, [_P, _P]),
     "vuib_set_seq_len": (C.c_int32, [_P, C.c_int32, C.c_int32]),
     "vuib_get_seq_len": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_int32)]),
     "vuib_check_device_flag": (C.c_int32, [_P, _P]),

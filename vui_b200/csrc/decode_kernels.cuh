@@ -141,6 +141,29 @@ static __global__ void __launch_bounds__(128) k_embed_codes(
     }
 }
 
+// Copies the caller's per-row (slot, position) table of a prefill into the workspace, recording and
+// clamping anything outside the cache: every later kernel of the call indexes the KV cache with the
+// checked copy, so a bad value can neither read nor write out of bounds.
+static __global__ void __launch_bounds__(256) k_check_rows(
+    const int32_t* slot_in, const int32_t* pos_in, int32_t* row_slot, int32_t* row_pos, int n, int n_slots,
+    int max_seq, int32_t* flag) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int slot = slot_in[i], pos = pos_in[i];
+    if (slot < 0 || slot >= n_slots) {
+        atomicOr(flag, FLAG_BAD_SLOT);
+        slot = slot < 0 ? 0 : n_slots - 1;
+    }
+    if (pos < 0 || pos >= max_seq) {
+        atomicOr(flag, FLAG_BAD_POS);
+        pos = pos < 0 ? 0 : max_seq - 1;
+    }
+    row_slot[i] = slot;
+    row_pos[i] = pos;
+}
+
 // ---------------------------------------------------------------------------
 // Staging functors: fill the CTA's shared activation tile Xs[nr][K] (bf16).
 // ---------------------------------------------------------------------------
@@ -677,6 +700,8 @@ struct AttnArgs {
     bf16* out;            // (R, Hq*64)
     int Hq, Hkv, max_seq, S;
     unsigned long long* dbg;  // optional: 8 device-clock stamps of one unit (profiling aid)
+    int n_slots;              // slots in the cache; 0 = unknown (only negative slots can then be caught)
+    int32_t* flag;            // device error word (may be NULL)
 };
 
 __device__ __forceinline__ void attn_stamp(const AttnArgs& a, int tid, int i) {
@@ -712,8 +737,19 @@ struct AttnSmem {
 __device__ __forceinline__ void attn_unit(const AttnArgs& a, int sp, int kvh, int r, int tid,
                                           AttnSmem& S_, int bar_id) {
     attn_stamp(a, tid, 0);
-    const int slot = __ldcg(a.row_slot + r);  // both requests in flight before the first use
-    const int len = __ldcg(a.row_pos + r) + 1;
+    int slot = __ldcg(a.row_slot + r);  // both requests in flight before the first use
+    int pos = __ldcg(a.row_pos + r);
+    // A slot or position outside the cache is recorded and clamped, never followed: a position past
+    // max_seq would also ask for more splits than the grid has, and the merge would never run.
+    if (slot < 0 || (a.n_slots > 0 && slot >= a.n_slots)) {
+        if (a.flag && tid == 0 && sp == 0 && kvh == 0) atomicOr(a.flag, FLAG_BAD_SLOT);
+        slot = slot < 0 ? 0 : a.n_slots - 1;
+    }
+    if (pos < 0 || pos >= a.max_seq) {
+        if (a.flag && tid == 0 && sp == 0 && kvh == 0) atomicOr(a.flag, FLAG_BAD_POS);
+        pos = pos < 0 ? 0 : a.max_seq - 1;
+    }
+    const int len = pos + 1;
     const int nsplit = (len + ATT_SPLIT - 1) / ATT_SPLIT;
     if (sp >= nsplit) return;
     const int warp = tid >> 5, lane = tid & 31;
@@ -980,6 +1016,8 @@ struct SampleArgs {
     // softmax(penalised logits / temperature) over the whole codebook - what the reference's streaming
     // gate averages over the first frames of a chunk (engine.py:1369-1372, 1418-1424, 1455-1460)
     float* stats_out;
+    int n_slots;              // per-slot state has this many entries: a slot outside is recorded and clamped
+    int32_t* flag;
 };
 
 struct SampleSmem {
@@ -995,7 +1033,11 @@ struct SampleSmem {
 __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, SampleSmem& S_, int bar_id) {
     constexpr int CS = SAMPLE_THREADS * SAMPLE_EL;
     const int warp = tid >> 5, lane = tid & 31;
-    const int slot = __ldcg(a.slots + r);
+    int slot = __ldcg(a.slots + r);
+    if (slot < 0 || slot >= a.n_slots) {
+        if (a.flag && tid == 0) atomicOr(a.flag, FLAG_BAD_SLOT);
+        slot = slot < 0 ? 0 : a.n_slots - 1;
+    }
     const SamplingCtl ctl = *a.ctl;
     const bool is_cb0 = a.codebook == 0;
     float (&s_f)[8] = S_.s_f;

@@ -31,7 +31,7 @@ constexpr int TC_KCHUNK = 64;       // bf16 per row per stage = 128 bytes = one 
 constexpr int TC_MAX_STAGES = 12;     // ring depth is set per launch from the shared memory left
 constexpr int TC_EPI_BYTES_PER_M = 256;  // epilogue staging per activation row (128 bf16)
 constexpr int FLAG_TC_TIMEOUT = 16;
-constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
+constexpr unsigned TC_SPIN_LIMIT = 1u << 22;  // default bound of every wait below, in polls (TcArgs::spin_limit)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -46,10 +46,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
                  : "memory");
 }
 
-// Bounded wait on a phase parity; returns false after TC_SPIN_LIMIT probes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+// Bounded wait on a phase parity; returns false after `limit` probes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned limit) {
     const uint32_t a = smem_u32(bar);
-    for (unsigned spins = 0; spins < TC_SPIN_LIMIT; ++spins) {
+    for (unsigned spins = 0; spins < limit; ++spins) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -304,6 +304,7 @@ struct TcArgs {
     int tiles;
     int32_t* flag;
     unsigned long long* dbg;  // optional: device-clock stamps of CTA (0,0) (profiling aid)
+    unsigned spin_limit;      // polls after which a wait gives up and records FLAG_TC_TIMEOUT
 };
 
 __device__ __forceinline__ void tc_stamp(const TcArgs& a, int i) {
@@ -377,7 +378,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
             tma_load_2d(base + (size_t)c * stage_bytes + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, 0, &bar_full[c]);
         for (int c = stages; c < n_chunks; ++c) {
             const int s = c % stages;
-            if (!mbar_wait(&bar_empty[s], ((c / stages) & 1) ^ 1)) { s_bad = 1; break; }
+            if (!mbar_wait(&bar_empty[s], ((c / stages) & 1) ^ 1, 4 * a.spin_limit)) { s_bad = 1; break; }
             unsigned char* st = base + (size_t)s * stage_bytes;
             mbar_expect_tx(&bar_full[s], a_bytes + b_bytes);
             tma_load_2d(st, &mapA0, (k_first + c) * TC_KCHUNK, rowA0, &bar_full[s]);
@@ -392,7 +393,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
         const uint32_t idesc = umma_idesc_bf16(a.Mpad);
         for (int c = 0; c < n_chunks; ++c) {
             const int s = c % stages;
-            if (!mbar_wait(&bar_full[s], (c / stages) & 1)) { s_bad = 1; break; }
+            if (!mbar_wait(&bar_full[s], (c / stages) & 1, 4 * a.spin_limit)) { s_bad = 1; break; }
             if (a.dbg && split == 0 && tile == 0 && c < 8) {
                 unsigned long long t;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -415,7 +416,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
     unsigned char* es = base + (size_t)stages * stage_bytes;  // epilogue staging, filled while the MMAs run
     if constexpr (Epi::STAGED) ep.stage(es, tile, a.M, tid);
     // ---- everyone: wait for the accumulator
-    const bool done_ok = mbar_wait(&bar_done, 0);
+    const bool done_ok = mbar_wait(&bar_done, 0, 4 * a.spin_limit);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     if ((!done_ok || s_bad) && tid == 0) atomicOr(a.flag, FLAG_TC_TIMEOUT);
@@ -467,7 +468,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
             for (;;) {
                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.counters + tile) : "memory");
                 if (v >= a.splits) break;
-                if (++spins > (1u << 22)) { atomicOr(a.flag, FLAG_TC_TIMEOUT); break; }
+                if (++spins > a.spin_limit) { atomicOr(a.flag, FLAG_TC_TIMEOUT); break; }
             }
         }
         __syncthreads();

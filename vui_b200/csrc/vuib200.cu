@@ -12,10 +12,7 @@
 #include <unordered_set>
 
 #include "decode_kernels.cuh"
-#include "frame_kernel.cuh"
 #include "tc_gemm.cuh"
-#include "depth_cluster.cuh"
-#include "frame_ll.h"
 
 using namespace vuib;
 
@@ -23,13 +20,13 @@ struct WsLayout {
     size_t flag, ctl, row_slot, row_pos, x, q, attn, act, part, counters;
     size_t rq_x2, rq_x, rq_q, rq_act, rq_k, rq_v, rq_logits, code_cur;
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
-    size_t bar, devmodel, trace;
+    size_t trace;
     size_t xn, rq_xn, rq_attn, tc_partial, tc_counters;
-    size_t ll_state, ll_bufs;
     size_t total;
 };
 
 constexpr int TC_PARTIAL_TILES = 224;  // most (tile, split) pairs of one GEMM launch
+constexpr int TRACE_STAMPS = 32;        // device-clock stamps kept for vuib_read_trace
 
 // Tensor maps (TMA descriptors) of every weight matrix, built when the weights are bound.
 struct TcMaps {
@@ -56,9 +53,8 @@ struct VuibEngine {
     bf16* tap_layers;
     bf16* tap_rq;
     long long launches;
-    DevModel dm;        // host copy of what the persistent kernel reads from the workspace
-    int num_sms;        // 0 until the first persistent launch asks the device
-    int coop;           // launch the frame kernel cooperatively
+    int num_sms;        // 0 until a launch first asks the device
+    unsigned spin_limit;  // bound of the waits inside kernels, in polls (vuib_set_wait_limit)
     float* cb0_stats;   // optional (max_rows, 2) fp32: entropy and top probability of each cb0 draw
     TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
     char err[256];
@@ -106,16 +102,12 @@ static void make_layout(VuibEngine* e) {
     L.rep_hist = take((size_t)c.n_slots * REP_HIST_MAX * 4);
     L.rep_head = take((size_t)c.n_slots * 4);
     L.rep_filled = take((size_t)c.n_slots * 4);
-    L.bar = take(256);
-    L.devmodel = take(sizeof(DevModel));
-    L.trace = take((size_t)(1 + 2 * TRACE_MAX + 16) * 8);
+    L.trace = take((size_t)TRACE_STAMPS * 8);
     L.xn = take(R * (size_t)(c.ffn > c.d_model ? c.ffn : c.d_model) * 2);
     L.rq_xn = take(2 * RB * rd * 2);
     L.rq_attn = take(2 * RB * rd * 2);
     L.tc_partial = take((size_t)(TC_PARTIAL_TILES + 80) * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
     L.tc_counters = take(2 * 256 * 4);
-    L.ll_state = take(256);
-    L.ll_bufs = take(LLLayout::END * 4);
     L.total = off;
 }
 
@@ -168,25 +160,6 @@ template <class T>
 static T* wsp(VuibEngine* e, size_t off) { return reinterpret_cast<T*>(e->ws + off); }
 
 static void build_tc_maps(VuibEngine* e);
-
-// The persistent frame kernel reads the bound pointers from a copy in the workspace.
-static int32_t sync_devmodel(VuibEngine* e) {
-    if (!e->have_ws) return VUIB_OK;
-    e->dm.w = e->w;
-    for (int i = 0; i < VUIB_MAX_LAYERS; ++i) {
-        e->dm.k[i] = e->k[i];
-        e->dm.v[i] = e->v[i];
-    }
-    e->dm.rope = e->rope;
-    e->dm.seq_lens = e->seq_lens;
-    cudaError_t rc = cudaMemcpy(e->ws + e->lay.devmodel, &e->dm, sizeof(DevModel), cudaMemcpyHostToDevice);
-    if (rc != cudaSuccess) {
-        snprintf(e->err, sizeof(e->err), "copying the pointer table to the workspace failed: %s",
-                 cudaGetErrorString(rc));
-        return VUIB_ERR_CUDA;
-    }
-    return VUIB_OK;
-}
 
 // ---------------------------------------------------------------------------
 // GEMV launch: pick the row-tile size from M, K from the supported set.
@@ -255,7 +228,7 @@ extern "C" int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out) {
     e->samp.top_k_cb0 = 1;
     e->samp.top_k_rq = 1;
     e->samp.rep_penalty = 1.0f;
-    e->coop = 1;
+    e->spin_limit = TC_SPIN_LIMIT;
     make_layout(e);
     *out = e;
     return VUIB_OK;
@@ -289,7 +262,7 @@ extern "C" int32_t vuib_bind_workspace(VuibEngine* e, void* dev, size_t bytes) {
                     e->lay.total, bytes, dev);
     e->ws = static_cast<unsigned char*>(dev);
     e->have_ws = true;
-    return sync_devmodel(e);
+    return VUIB_OK;
 }
 
 extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
@@ -307,7 +280,7 @@ extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
     e->w = *w;
     e->have_w = true;
     build_tc_maps(e);
-    return sync_devmodel(e);
+    return VUIB_OK;
 }
 
 extern "C" int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* v_dev,
@@ -320,14 +293,14 @@ extern "C" int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* 
     }
     e->seq_lens = seq_lens_dev;
     e->have_kv = true;
-    return sync_devmodel(e);
+    return VUIB_OK;
 }
 
 extern "C" int32_t vuib_bind_rope(VuibEngine* e, const void* freqs_cis_dev) {
     if (!e || !freqs_cis_dev) return VUIB_ERR_NULL;
     e->rope = static_cast<const bf16*>(freqs_cis_dev);
     e->have_rope = true;
-    return sync_devmodel(e);
+    return VUIB_OK;
 }
 
 static int32_t ready(VuibEngine* e) {
@@ -465,11 +438,17 @@ static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& 
         if (Epi::PAIRED && d == 2) continue;
         splits = d;
     }
-    static bool attr_set = false;
     const int max_smem = 202 * 1024;
-    if (!attr_set) {
-        CK(cudaFuncSetAttribute(k_gemm_tc<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr_set = true;
+    {   // a function attribute belongs to one device's copy of the kernel: set it once per device
+        static std::mutex mu;
+        static bool attr_set[64];
+        int dev = 0;
+        CK(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            CK(cudaFuncSetAttribute(k_gemm_tc<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
     }
     for (int m0 = 0; m0 < M; m0 += 256) {
         const int Mb = M - m0 < 256 ? M - m0 : 256;
@@ -487,7 +466,8 @@ static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& 
         ta.partial = wsp<float>(e, L.tc_partial);
         ta.counters = wsp<int32_t>(e, L.tc_counters);
         ta.flag = wsp<int32_t>(e, L.flag);
-        ta.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) + 1 + 2 * TRACE_MAX : nullptr;
+        ta.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) : nullptr;
+        ta.spin_limit = e->spin_limit;
         const int min_chunks = chunks_total / splits;  // the shortest split
         const size_t stage_bytes = TC_TILE_N * TC_KCHUNK * 2 + ((Mpad * TC_KCHUNK * 2 + 1023) & ~1023);
         const size_t epi_bytes = Epi::STAGED ? (size_t)Mpad * TC_EPI_BYTES_PER_M : 0;
@@ -531,7 +511,7 @@ static int32_t run_layers_tc(VuibEngine* e, int M, cudaStream_t s) {
 
         AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
                     row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
-                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr};
+                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr, c.n_slots, wsp<int32_t>(e, L.flag)};
         CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
         e->launches++;
 
@@ -617,7 +597,7 @@ static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
 
         AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
                     row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
-                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr};
+                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr, c.n_slots, wsp<int32_t>(e, L.flag)};
         CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
         e->launches++;
         CK(cudaGetLastError());
@@ -663,8 +643,9 @@ extern "C" int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* ro
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const WsLayout& L = e->lay;
     const int d = e->cfg.d_model;
-    CK(cudaMemcpyAsync(e->ws + L.row_slot, row_slot_dev, (size_t)n_rows * 4, cudaMemcpyDeviceToDevice, s));
-    CK(cudaMemcpyAsync(e->ws + L.row_pos, row_pos_dev, (size_t)n_rows * 4, cudaMemcpyDeviceToDevice, s));
+    CK(launch(k_check_rows, (n_rows + 255) / 256, 256, 0, s, row_slot_dev, row_pos_dev, wsp<int32_t>(e, L.row_slot),
+              wsp<int32_t>(e, L.row_pos), n_rows, e->cfg.n_slots, e->cfg.max_seq, wsp<int32_t>(e, L.flag)));
+    e->launches++;
     CK(cudaMemcpyAsync(e->ws + L.x, emb_dev, (size_t)n_rows * d * 2, cudaMemcpyDeviceToDevice, s));
     rc = run_layers(e, n_rows, s);
     if (rc) return rc;
@@ -773,6 +754,8 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     sa.code_cur = code_cur;
     sa.codes_out = codes_out;
     sa.Q = Q;
+    sa.n_slots = c.n_slots;
+    sa.flag = wsp<int32_t>(e, L.flag);
 
     // cb0
     sa.logits = cb0_logits;
@@ -854,237 +837,6 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
     return VUIB_OK;
 }
 
-// ---------------------------------------------------------------------------
-// Persistent frame kernel (frame_kernel.cuh): one launch per frame for B <= 8.
-// ---------------------------------------------------------------------------
-
-static bool persistent_ok(VuibEngine* e, int B) {
-    const VuibConfig& c = e->cfg;
-    // opt-in: with one sync point per GEMV it is not faster than the graph of per-phase kernels
-    return B <= 8 && c.d_model == 1024 && c.ffn == 3072 && c.rq_d_model == 512 &&
-           (c.rq_ffn == 1408 || c.rq_ffn == 1536) && env_off("VUIB_PERSISTENT");
-}
-
-typedef void (*FrameKernel)(FrameArgs);
-
-static FrameKernel frame_kernel_for(int rt, int rqf) {
-    if (rqf == 1408) {
-        switch (rt) {
-            case 1: return k_frame<1, 1408>;
-            case 2: return k_frame<2, 1408>;
-            case 4: return k_frame<4, 1408>;
-            default: return k_frame<8, 1408>;
-        }
-    }
-    switch (rt) {
-        case 1: return k_frame<1, 1536>;
-        case 2: return k_frame<2, 1536>;
-        case 4: return k_frame<4, 1536>;
-        default: return k_frame<8, 1536>;
-    }
-}
-
-static FrameArgs fill_frame_args(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc,
-                                 int64_t* codes_io, bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob,
-                                 int do_backbone, int first_frame) {
-    const VuibConfig& c = e->cfg;
-    const WsLayout& L = e->lay;
-    FrameArgs fa;
-    memset(&fa, 0, sizeof(fa));
-    fa.m = wsp<DevModel>(e, L.devmodel);
-    FrameBufs& b = fa.b;
-    b.row_slot = wsp<int32_t>(e, L.row_slot);
-    b.row_pos = wsp<int32_t>(e, L.row_pos);
-    b.x = wsp<bf16>(e, L.x);
-    b.q = wsp<bf16>(e, L.q);
-    b.attn = wsp<bf16>(e, L.attn);
-    b.act = wsp<bf16>(e, L.act);
-    b.part = wsp<float>(e, L.part);
-    b.counters = wsp<int32_t>(e, L.counters);
-    b.rq_x2 = wsp<bf16>(e, L.rq_x2);
-    b.rq_x = wsp<bf16>(e, L.rq_x);
-    b.rq_q = wsp<bf16>(e, L.rq_q);
-    b.rq_act = wsp<bf16>(e, L.rq_act);
-    b.rq_k = wsp<bf16>(e, L.rq_k);
-    b.rq_v = wsp<bf16>(e, L.rq_v);
-    b.rq_logits = wsp<bf16>(e, L.rq_logits);
-    b.code_cur = wsp<int32_t>(e, L.code_cur);
-    b.ctl = wsp<SamplingCtl>(e, L.ctl);
-    b.frame_ctr = wsp<int32_t>(e, L.frame_ctr);
-    b.rep_counts = wsp<float>(e, L.rep_counts);
-    b.rep_hist = wsp<int32_t>(e, L.rep_hist);
-    b.rep_head = wsp<int32_t>(e, L.rep_head);
-    b.rep_filled = wsp<int32_t>(e, L.rep_filled);
-    b.flag = wsp<int32_t>(e, L.flag);
-    b.bar = wsp<unsigned>(e, L.bar);
-    b.trace = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) : nullptr;
-    fa.B = B;
-    fa.slots = slots;
-    fa.seq_inc = seq_inc;
-    fa.codes_io = codes_io;
-    fa.hidden_out = hidden;
-    fa.cb0_out = cb0;
-    fa.eos_out = eos;
-    fa.eos_prob = eos_prob;
-    fa.tap_layers = e->tap_layers;
-    fa.tap_rq = e->tap_rq;
-    fa.n_layers = c.n_layers;
-    fa.n_heads = c.n_heads;
-    fa.n_kv_heads = c.n_kv_heads;
-    fa.max_seq = c.max_seq;
-    fa.n_slots = c.n_slots;
-    fa.S = e->S;
-    fa.Q = c.n_quantizers;
-    fa.CS = c.codebook_size;
-    fa.rq_n_layers = c.rq_n_layers;
-    fa.rq_n_heads = c.rq_n_heads;
-    fa.max_rows = c.max_rows;
-    fa.norm_eps = c.norm_eps;
-    fa.rq_norm_eps = c.rq_norm_eps;
-    fa.n_codebooks = e->samp.n_codebooks > 0 ? e->samp.n_codebooks : c.n_quantizers;
-    fa.do_backbone = do_backbone;
-    fa.first_frame = first_frame;
-    return fa;
-}
-
-static int32_t need_sm_count(VuibEngine* e) {
-    if (e->num_sms == 0) {
-        int dev = 0;
-        CK(cudaGetDevice(&dev));
-        CK(cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, dev));
-    }
-    return VUIB_OK;
-}
-
-static int32_t launch_frame(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc,
-                            int64_t* codes_io, bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob,
-                            int do_backbone, int first_frame, cudaStream_t s) {
-    const VuibConfig& c = e->cfg;
-    const WsLayout& L = e->lay;
-    int32_t rc = need_sm_count(e);
-    if (rc) return rc;
-    FrameArgs fa = fill_frame_args(e, B, slots, seq_inc, codes_io, hidden, cb0, eos, eos_prob, do_backbone, first_frame);
-    const int rt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
-    FrameKernel kern = frame_kernel_for(rt, c.rq_ffn);
-    const size_t smem = (size_t)rt * 3072 * sizeof(bf16);
-    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CK(cudaMemsetAsync(e->ws + L.bar, 0, 4, s));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(e->num_sms);
-    cfg.blockDim = dim3(PF_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = (e->coop && !env_off("VUIB_NO_COOP")) ? 1 : 0;
-    CK(cudaLaunchKernelEx(&cfg, kern, fa));
-    e->launches++;
-    return VUIB_OK;
-}
-
-// ---------------------------------------------------------------------------
-// Barrier-free persistent frame (frame_ll.cu): one launch per frame for B <= 4, activations handed
-// from phase to phase as self-validating tagged words.  Needs a cooperative launch (every CTA
-// resident) and the one model shape its buffers are laid out for.
-// ---------------------------------------------------------------------------
-static bool ll_ok(VuibEngine* e, int B) {
-    const VuibConfig& c = e->cfg;
-    return B <= LL_MAXB && e->coop && c.d_model == 1024 && c.ffn == 3072 && c.n_heads == 16 && c.n_kv_heads == 8 &&
-           c.codebook_size == 2048 && c.rq_d_model == 512 && c.rq_n_heads == 8 && c.rq_n_layers <= 4 &&
-           c.n_quantizers == 16 && (c.rq_ffn == 1408 || c.rq_ffn == 1536) && env_off("VUIB_LL");
-}
-
-static int32_t launch_ll(VuibEngine* e, int B, const int32_t* slots, const int32_t* seq_inc, int64_t* codes_io,
-                         bf16* hidden, bf16* cb0, bf16* eos, float* eos_prob, cudaStream_t s) {
-    int32_t rc = need_sm_count(e);
-    if (rc) return rc;
-    LLArgs la;
-    la.fa = fill_frame_args(e, B, slots, seq_inc, codes_io, hidden, cb0, eos, eos_prob, 1, 0);
-    la.bufs = wsp<uint32_t>(e, e->lay.ll_bufs);
-    la.state = wsp<uint32_t>(e, e->lay.ll_state);
-    CK((cudaError_t)launch_frame_ll(la, e->cfg.rq_ffn, e->num_sms, true, s));
-    e->launches++;
-    return VUIB_OK;
-}
-
-// ---------------------------------------------------------------------------
-// Depth step on one 16-CTA cluster (depth_cluster.cuh): one launch for B <= 4.
-// ---------------------------------------------------------------------------
-// Opt-in (VUIB_CLUSTER=1): bit-identical to the per-phase kernels but not faster.  On 16 SMs the
-// step is bound by instruction issue (~100 warp instructions per 512-long dot product, 23.5 k
-// dot products per codebook), 86 us per codebook against 53 us for the launch-bound graph.
-static bool cluster_ok(VuibEngine* e, int B) {
-    const VuibConfig& c = e->cfg;
-    return B <= 4 && c.d_model == 1024 && c.rq_d_model == 512 && c.rq_n_heads == 8 &&
-           (c.rq_ffn == 1408 || c.rq_ffn == 1536) && c.codebook_size == 2048 && env_off("VUIB_CLUSTER");
-}
-
-typedef void (*DepthKernel)(DepthArgs);
-
-static int32_t launch_depth_cluster(VuibEngine* e, int B, const int32_t* slots, const bf16* hidden,
-                                    const bf16* cb0, const bf16* eos, int first_frame, int64_t* codes_out,
-                                    float* eos_prob, cudaStream_t s) {
-    const VuibConfig& c = e->cfg;
-    const WsLayout& L = e->lay;
-    DepthArgs da;
-    memset(&da, 0, sizeof(da));
-    da.m = wsp<DevModel>(e, L.devmodel);
-    FrameBufs& b = da.b;
-    b.rq_k = wsp<bf16>(e, L.rq_k);
-    b.rq_v = wsp<bf16>(e, L.rq_v);
-    b.rq_logits = wsp<bf16>(e, L.rq_logits);
-    b.code_cur = wsp<int32_t>(e, L.code_cur);
-    b.ctl = wsp<SamplingCtl>(e, L.ctl);
-    b.frame_ctr = wsp<int32_t>(e, L.frame_ctr);
-    b.rep_counts = wsp<float>(e, L.rep_counts);
-    b.rep_hist = wsp<int32_t>(e, L.rep_hist);
-    b.rep_head = wsp<int32_t>(e, L.rep_head);
-    b.rep_filled = wsp<int32_t>(e, L.rep_filled);
-    b.flag = wsp<int32_t>(e, L.flag);
-    da.B = B;
-    da.slots = slots;
-    da.hidden = hidden;
-    da.cb0_logits = cb0;
-    da.eos_logit = eos;
-    da.eos_prob = eos_prob;
-    da.codes_out = codes_out;
-    da.tap_rq = e->tap_rq;
-    da.Q = c.n_quantizers;
-    da.CS = c.codebook_size;
-    da.rq_n_layers = c.rq_n_layers;
-    da.rq_n_heads = c.rq_n_heads;
-    da.max_rows = c.max_rows;
-    da.rq_norm_eps = c.rq_norm_eps;
-    da.n_codebooks = e->samp.n_codebooks > 0 ? e->samp.n_codebooks : c.n_quantizers;
-    da.first_frame = first_frame;
-    da.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) + 1 + 2 * TRACE_MAX : nullptr;
-    const int rt = B <= 1 ? 1 : B <= 2 ? 2 : 4;
-    DepthKernel kern;
-    if (c.rq_ffn == 1408) kern = rt == 1 ? k_depth_cluster<1, 1408> : rt == 2 ? k_depth_cluster<2, 1408> : k_depth_cluster<4, 1408>;
-    else kern = rt == 1 ? k_depth_cluster<1, 1536> : rt == 2 ? k_depth_cluster<2, 1536> : k_depth_cluster<4, 1536>;
-    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    prefer_max_smem(reinterpret_cast<const void*>(kern));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(DC_CTAS);
-    cfg.blockDim = dim3(DC_THREADS);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = DC_CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    CK(cudaLaunchKernelEx(&cfg, kern, da));
-    e->launches++;
-    return VUIB_OK;
-}
-
 extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slots_dev,
                                    const void* hidden_dev, const void* cb0_logits_dev,
                                    const void* eos_logit_dev, int32_t first_frame,
@@ -1094,16 +846,6 @@ extern "C" int32_t vuib_depth_step(VuibEngine* e, int32_t B, const int32_t* slot
     if (!slots_dev || !hidden_dev || !cb0_logits_dev || !codes_out_dev) return VUIB_ERR_NULL;
     if (B < 1 || B > e->cfg.max_rows)
         return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
-    if (!persistent_ok(e, B) && cluster_ok(e, B))
-        return launch_depth_cluster(e, B, slots_dev, static_cast<const bf16*>(hidden_dev),
-                                    static_cast<const bf16*>(cb0_logits_dev), static_cast<const bf16*>(eos_logit_dev),
-                                    first_frame, codes_out_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
-    if (persistent_ok(e, B))
-        return launch_frame(e, B, slots_dev, nullptr, codes_out_dev,
-                            const_cast<bf16*>(static_cast<const bf16*>(hidden_dev)),
-                            const_cast<bf16*>(static_cast<const bf16*>(cb0_logits_dev)),
-                            const_cast<bf16*>(static_cast<const bf16*>(eos_logit_dev)), eos_prob_out_dev, 0,
-                            first_frame, static_cast<cudaStream_t>(stream));
     return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_dev),
                      static_cast<const bf16*>(cb0_logits_dev), static_cast<const bf16*>(eos_logit_dev),
                      first_frame, codes_out_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
@@ -1118,21 +860,9 @@ extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* sl
     if (!slots_dev || !codes_io_dev || !hidden_out_dev || !cb0_out_dev || !eos_out_dev) return VUIB_ERR_NULL;
     if (B < 1 || B > e->cfg.max_rows)
         return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
-    if (ll_ok(e, B))
-        return launch_ll(e, B, slots_dev, seq_inc_dev, codes_io_dev, static_cast<bf16*>(hidden_out_dev),
-                         static_cast<bf16*>(cb0_out_dev), static_cast<bf16*>(eos_out_dev), eos_prob_out_dev,
-                         static_cast<cudaStream_t>(stream));
-    if (persistent_ok(e, B))
-        return launch_frame(e, B, slots_dev, seq_inc_dev, codes_io_dev, static_cast<bf16*>(hidden_out_dev),
-                            static_cast<bf16*>(cb0_out_dev), static_cast<bf16*>(eos_out_dev), eos_prob_out_dev,
-                            1, 0, static_cast<cudaStream_t>(stream));
     rc = vuib_backbone_step(e, B, slots_dev, seq_inc_dev, codes_io_dev, hidden_out_dev,
                             cb0_out_dev, eos_out_dev, stream);
     if (rc) return rc;
-    if (cluster_ok(e, B))
-        return launch_depth_cluster(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
-                                    static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
-                                    codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
     return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
                      static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
                      codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
@@ -1149,7 +879,7 @@ extern "C" int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, 
     AttnArgs aa{static_cast<const bf16*>(q_dev), static_cast<const bf16*>(e->k[layer]),
                 static_cast<const bf16*>(e->v[layer]), row_slot_dev, row_pos_dev,
                 wsp<float>(e, e->lay.part), wsp<int32_t>(e, e->lay.counters), static_cast<bf16*>(out_dev),
-                c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr};
+                c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr, c.n_slots, wsp<int32_t>(e, e->lay.flag)};
     CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, n_rows), ATT_THREADS, 0, static_cast<cudaStream_t>(stream), aa));
     e->launches++;
     CK(cudaGetLastError());
@@ -1196,9 +926,73 @@ extern "C" int32_t vuib_sample_rows(VuibEngine* e, int32_t B, const int32_t* slo
     sa.Q = 1;
     sa.out_col = 0;
     sa.bump_frame = 1;
+    sa.n_slots = e->cfg.n_slots;
+    sa.flag = wsp<int32_t>(e, L.flag);
     CK(launch(k_sample, B, SAMPLE_THREADS, 0, static_cast<cudaStream_t>(stream), sa));
     e->launches++;
     CK(cudaGetLastError());
+    return VUIB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Single fused ops on caller-supplied rows, for the parity tests: with an identity
+// matrix as W the GEMV passes its staged input through exactly, so the RMSNorm
+// staging and the RoPE epilogue can be held bit for bit against the reference's
+// own module outputs.
+// ---------------------------------------------------------------------------
+extern "C" int32_t vuib_debug_norm_linear(VuibEngine* e, int32_t n_rows, const void* x_dev,
+                                          const void* norm_w_dev, const void* w_dev, int32_t n_out,
+                                          void* out_dev, int32_t tensor_cores, void* stream) {
+    if (!e || !x_dev || !norm_w_dev || !w_dev || !out_dev) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    const VuibConfig& c = e->cfg;
+    if (n_rows < 1 || n_rows > e->R || n_out < 1) return fail(e, VUIB_ERR_RANGE, "n_rows %d / n_out %d out of range", n_rows, n_out);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bf16* x = static_cast<const bf16*>(x_dev);
+    const int d = c.d_model;
+    if (tensor_cores) {
+        if (n_out % TC_TILE_N) return fail(e, VUIB_ERR_RANGE, "n_out must be a multiple of %d on the tensor-core path", TC_TILE_N);
+        CUtensorMap mw;
+        if (!make_map(&mw, w_dev, n_out, d, 64)) return fail(e, VUIB_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+        bf16* xn = wsp<bf16>(e, e->lay.xn);
+        int32_t rc = norm_rows(e, x, norm_w_dev, c.norm_eps, xn, n_rows, d, 1, 0, s);
+        if (rc) return rc;
+        TcEpiLogits el{static_cast<bf16*>(out_dev), n_out, nullptr, 0};
+        return tc_gemm(e, mw, mw, xn, n_rows, d, n_out, 0, el, s);
+    }
+    StageNorm sn{x, static_cast<const bf16*>(norm_w_dev), c.norm_eps, 1, 0};
+    EpiLogits el{static_cast<const bf16*>(w_dev), d, n_out, static_cast<bf16*>(out_dev), nullptr, nullptr, nullptr,
+                 nullptr, 0};
+    CK(VUIB_GEMV(d, e, sn, el, n_rows, n_out, s));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_debug_linear_rope(VuibEngine* e, int32_t n_rows, const void* x_dev, const void* w_dev,
+                                          const int32_t* row_pos_dev, void* out_dev, int32_t tensor_cores,
+                                          void* stream) {
+    if (!e || !x_dev || !w_dev || !row_pos_dev || !out_dev) return VUIB_ERR_NULL;
+    if (!e->have_ws || !e->have_rope) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace and the rope table first");
+    const VuibConfig& c = e->cfg;
+    if (n_rows < 1 || n_rows > e->R) return fail(e, VUIB_ERR_RANGE, "n_rows %d outside [1, %d]", n_rows, e->R);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int d = c.d_model;
+    // every output column is a "q" column: rotated at row_pos[r], nothing goes to a cache
+    int32_t* row_slot = wsp<int32_t>(e, e->lay.row_slot);
+    int32_t* row_pos = wsp<int32_t>(e, e->lay.row_pos);
+    CK(cudaMemsetAsync(row_slot, 0, (size_t)n_rows * 4, s));
+    CK(launch(k_check_rows, (n_rows + 255) / 256, 256, 0, s, static_cast<const int32_t*>(row_slot), row_pos_dev, row_slot,
+              row_pos, n_rows, c.n_slots, c.max_seq, wsp<int32_t>(e, e->lay.flag)));
+    e->launches++;
+    if (tensor_cores) {
+        CUtensorMap mw;
+        if (!make_map(&mw, w_dev, d, d, 64)) return fail(e, VUIB_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+        TcEpiQkv eq{static_cast<bf16*>(out_dev), d, 0, nullptr, nullptr, row_slot, row_pos, c.max_seq, e->rope, 1, 0, 0};
+        return tc_gemm(e, mw, mw, static_cast<const bf16*>(x_dev), n_rows, d, d, 0, eq, s);
+    }
+    StageCopy sc{static_cast<const bf16*>(x_dev)};
+    EpiQkv eq{static_cast<const bf16*>(w_dev), d, static_cast<bf16*>(out_dev), d, 0, nullptr, nullptr,
+              row_slot, row_pos, c.max_seq, e->rope, 1, 0, 0};
+    CK(VUIB_GEMV(d, e, sc, eq, n_rows, d / 2, s));
     return VUIB_OK;
 }
 
@@ -1226,22 +1020,33 @@ extern "C" int32_t vuib_reset_state(VuibEngine* e, void* stream) {
     CK(cudaMemsetAsync(e->ws + L.flag, 0, 256, s));
     CK(cudaMemsetAsync(e->ws + L.counters, 0, (size_t)e->R * c.n_kv_heads * 4, s));
     CK(cudaMemsetAsync(e->ws + L.frame_ctr, 0, (size_t)c.n_slots * 4, s));
-    CK(cudaMemsetAsync(e->ws + L.bar, 0, 256, s));
-    CK(cudaMemsetAsync(e->ws + L.ll_state + 4, 0, 8, s));  // shape word: the next launch clears its exchange buffers
+    CK(cudaMemsetAsync(e->ws + L.tc_counters, 0, 2 * 256 * 4, s));
     return vuib_rep_reset(e, -1, stream);
 }
 
-extern "C" int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t max_entries, int32_t* n_out) {
-    if (!e || !out_host || !n_out) return VUIB_ERR_NULL;
+extern "C" int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t n_stamps) {
+    if (!e || !out_host) return VUIB_ERR_NULL;
     if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
-    unsigned long long n = 0;
-    CK(cudaMemcpy(&n, e->ws + e->lay.trace, 8, cudaMemcpyDeviceToHost));
-    if (n > (unsigned long long)TRACE_MAX) n = TRACE_MAX;
-    if ((long long)n > max_entries) n = max_entries;
-    if (n) CK(cudaMemcpy(out_host, e->ws + e->lay.trace + 8, n * 16, cudaMemcpyDeviceToHost));
-    CK(cudaMemcpy(out_host + 2 * (size_t)max_entries, e->ws + e->lay.trace + 8 + (size_t)2 * TRACE_MAX * 8, 16 * 8,
-                  cudaMemcpyDeviceToHost));
-    *n_out = (int32_t)n;
+    if (n_stamps < 1 || n_stamps > TRACE_STAMPS) return fail(e, VUIB_ERR_RANGE, "n_stamps outside [1, %d]", TRACE_STAMPS);
+    CK(cudaMemcpy(out_host, e->ws + e->lay.trace, (size_t)n_stamps * 8, cudaMemcpyDeviceToHost));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_set_wait_limit(VuibEngine* e, uint32_t polls) {
+    if (!e) return VUIB_ERR_NULL;
+    if (polls < 16) return fail(e, VUIB_ERR_RANGE, "wait limit %u below 16 polls", polls);
+    e->spin_limit = polls;
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_debug_withhold_arrival(VuibEngine* e, void* stream) {
+    if (!e) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    int32_t minus_one[256];
+    for (int i = 0; i < 256; ++i) minus_one[i] = -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CK(cudaMemcpyAsync(e->ws + e->lay.tc_counters, minus_one, sizeof(minus_one), cudaMemcpyHostToDevice, s));
+    CK(cudaStreamSynchronize(s));  // the source is a stack array
     return VUIB_OK;
 }
 
@@ -1271,7 +1076,10 @@ extern "C" int32_t vuib_check_device_flag(VuibEngine* e, void* stream) {
     CK(cudaStreamSynchronize(s));
     if (flag) {
         CK(cudaMemsetAsync(e->ws + e->lay.flag, 0, 4, s));
-        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = bad slot, 2 = position past max_seq, 4 = bad code, 8 = grid barrier timed out, 16 = tensor-core pipeline wait timed out, 32 = tagged-word wait timed out)", flag);
+        // a wait that gave up may have left arrival counters half way: re-arm them with the flag
+        CK(cudaMemsetAsync(e->ws + e->lay.tc_counters, 0, 2 * 256 * 4, s));
+        CK(cudaMemsetAsync(e->ws + e->lay.counters, 0, (size_t)e->R * e->cfg.n_kv_heads * 4, s));
+        return fail(e, VUIB_ERR_DEVICE_FLAG, "device flag 0x%x (1 = slot outside the cache, 2 = position outside [0, max_seq), 4 = code outside the codebook, 16 = a bounded wait inside a kernel ran out)", flag);
     }
     return VUIB_OK;
 }
@@ -1361,7 +1169,7 @@ extern "C" int32_t vuib_attention_noalloc(int32_t n_heads, int32_t n_kv_heads, i
     AttnArgs aa{static_cast<const bf16*>(q_dev), static_cast<const bf16*>(k_cache_dev),
                 static_cast<const bf16*>(v_cache_dev), row_slot_dev, row_pos_dev,
                 reinterpret_cast<float*>(b), reinterpret_cast<int32_t*>(b + NA_PART_BYTES),
-                static_cast<bf16*>(out_dev), n_heads, n_kv_heads, max_seq, S, nullptr};
+                static_cast<bf16*>(out_dev), n_heads, n_kv_heads, max_seq, S, nullptr, 0, nullptr};
     k_attn_decode<<<dim3(S, n_kv_heads, n_rows), ATT_THREADS, 0, s>>>(aa);
     rc = cudaGetLastError();
     if (rc != cudaSuccess)

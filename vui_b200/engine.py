@@ -581,6 +581,41 @@ class Engine:
                                                 C.c_void_p(out[i].data_ptr()), self._stream))
         return out.cpu()
 
+    def _debug_norm_linear(self, x: Tensor, norm_w: Tensor, w: Tensor, tensor_cores: bool = False) -> Tensor:
+        """bf16(W . RMSNorm(x) * norm_w) through the GEMV (or tcgen05) kernels: x (n, d), W (n_out, d)."""
+        x, norm_w, w = (t.to(self.device, self.dtype).contiguous() for t in (x, norm_w, w))
+        out = torch.empty(x.shape[0], w.shape[0], device=self.device, dtype=self.dtype)
+        P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        self._ck(self._lib.vuib_debug_norm_linear(self._handle, x.shape[0], P(x), P(norm_w), P(w), w.shape[0], P(out),
+                                                  int(tensor_cores), self._stream))
+        return out
+
+    def _debug_linear_rope(self, x: Tensor, w: Tensor, pos: Tensor, tensor_cores: bool = False) -> Tensor:
+        """RoPE(bf16(W . x)) at positions pos (n,), every 64 columns one head: x (n, d), W (d, d)."""
+        x, w = (t.to(self.device, self.dtype).contiguous() for t in (x, w))
+        pos = pos.to(self.device, torch.int32).contiguous()
+        out = torch.empty(x.shape[0], w.shape[0], device=self.device, dtype=self.dtype)
+        P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        self._ck(self._lib.vuib_debug_linear_rope(self._handle, x.shape[0], P(x), P(w), P(pos), P(out),
+                                                  int(tensor_cores), self._stream))
+        return out
+
+    def _sample_first_frame(self, cb0_logits: Tensor, n_draws: int) -> Tensor:
+        """cb0 draws of a chunk's first frame (no top-k, engine.py:936-937) for rows of logits (B, CS),
+        through the depth step the frame-0 path uses; returns (n_draws, B) on the host."""
+        B = cb0_logits.shape[0]
+        lg = cb0_logits.to(self.device, self.dtype).contiguous()
+        hid = torch.zeros(B, self.D, device=self.device, dtype=self.dtype)
+        slots = torch.arange(B, device=self.device, dtype=torch.int32)
+        codes = torch.zeros(B, self.Q, device=self.device, dtype=torch.long)
+        out = torch.zeros(n_draws, B, dtype=torch.long, device=self.device)
+        P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        for i in range(n_draws):
+            self._ck(self._lib.vuib_depth_step(self._handle, B, P(slots), P(hid), P(lg), None, 1, P(codes), None,
+                                               self._stream))
+            out[i] = codes[:, 0]
+        return out.cpu()
+
     def _ws_reset_counters(self) -> None:
         """Zero the sampler state (draw counters, penalty state, error flag)."""
         self._ck(self._lib.vuib_reset_state(self._handle, self._stream))
