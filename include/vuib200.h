@@ -261,7 +261,7 @@ int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream);
 int32_t vuib_reset_state(VuibEngine* e, void* stream);
 
 /* Profiling aid: when the environment variable VUIB_TRACE is set, CTA (0,0) of a tensor-core GEMM
- * launch records device-clock stamps (ns) at its pipeline stages.  Copies the first n_stamps (<= 32)
+ * launch records device-clock stamps (ns) at its pipeline stages.  Copies the first n_stamps (<= 64)
  * stamps of the last such launch to out_host.  Synchronous. */
 int32_t vuib_read_trace(VuibEngine* e, uint64_t* out_host, int32_t n_stamps);
 

@@ -75,25 +75,25 @@ def test_gather_sum_bit_exact(eng1, golden_dir):
 
 
 @pytest.mark.parametrize("tensor_cores", [False, True])
-def test_rmsnorm_and_rope_bit_exact(eng8, golden_dir, tensor_cores):
+def test_rmsnorm_and_rope_bit_exact(eng1, golden_dir, tensor_cores):
     """The RMSNorm staging and the RoPE epilogue of both kernel families against the reference
     modules' bf16 outputs (RMSNorm.forward model.py:292-297; apply_rotary_emb rope.py:50), bit for
     bit: an identity matrix as the Linear passes the staged row through unchanged."""
     fx = torch.load(os.path.join(golden_dir, "ops_bf16.pt"))
     eye = torch.eye(1024, dtype=torch.bfloat16)
-    y = eng8._debug_norm_linear(fx["norm_x"], fx["norm_w"], eye, tensor_cores).cpu()
+    y = eng1._debug_norm_linear(fx["norm_x"], fx["norm_w"], eye, tensor_cores).cpu()
     assert torch.equal(y, fx["norm_y"])
     q = fx["rope_q"].reshape(5, 1024)
-    out = eng8._debug_linear_rope(q, eye, fx["rope_pos"], tensor_cores).cpu()
+    out = eng1._debug_linear_rope(q, eye, fx["rope_pos"], tensor_cores).cpu()
     assert torch.equal(out.view(5, 16, 64), fx["rope_out"])
     # and with the real Wqkv of layer 0 behind the norm: the reference's Linear output within bf16 rounding
-    w = eng8.model.sd["decoder.blocks.0.attn.Wqkv.weight"]
+    w = eng1.model.sd["decoder.blocks.0.attn.Wqkv.weight"]
     ones = torch.ones(1024, dtype=torch.bfloat16)
-    got = eng8._debug_norm_linear(fx["mlp_x"], ones, w, tensor_cores).float().cpu()
+    got = eng1._debug_norm_linear(fx["mlp_x"], ones, w, tensor_cores).float().cpu()
     h = fx["mlp_x"].float()
     want = torch.nn.functional.linear((h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)).bfloat16().float(), w.float().cpu())
     assert (got - want).abs().max().item() <= 2.0 ** -8 * want.abs().max().item() + 1e-6
-    eng8.check_device()
+    eng1.check_device()
 
 
 def test_prefill_and_frame0_vs_oracle(eng1, oracle_gpu, oracle_fp32):
@@ -254,27 +254,39 @@ def test_teacher_forced_32_frames(eng1, oracle_gpu):
     eng._apply_cfg(None, greedy=True)
     eng._g_slot_idx[0] = row.idx
     eng._g_seq_inc[0] = 1
-    mism, total = 0, 0
+    mism, wide, total = 0, 0, 0
+    rq_tap = torch.zeros(1, 15, 2048, device="cuda", dtype=torch.bfloat16)
+    eng._set_taps(None, rq_tap)
     c0 = eng._first_frames([row], h[None])[0].cpu()
-    frames = [c0]
+    frames, mine_logits = [c0], [[eng._last_first[1][0].float().cpu()] + list(rq_tap[0].float().cpu())]
     for f in range(1, 32):
         eng._g_codes_in[0] = ref[f - 1].cuda()
         eng._frame_step(1)
         frames.append(eng._g_codes_in[0].cpu())
+        mine_logits.append([eng._g_cb0_out[0].float().cpu()] + list(rq_tap[0].float().cpu()))
         assert _rel(eng._g_hidden_out[0], tr.hidden[f]) < REL_TOL_BF16
         assert _rel(eng._g_cb0_out[0], tr.cb0[f]) < REL_TOL_BF16
-    # the depth loop is autoregressive inside a frame: compare up to its first internal divergence
+    eng._set_taps(None, None)
+    # the depth loop is autoregressive inside a frame: compare up to its first internal divergence.  An argmax
+    # may differ only where the oracle's top-2 margin is within two bf16 steps, or within twice the largest
+    # difference between the two logit vectors themselves (each of the two candidates moves by at most that)
     for f in range(32):
         for q in range(16):
             total += 1
             if frames[f][q] != ref[f][q]:
                 lg = tr.cb0[f] if q == 0 else tr.rq_logits[f][q - 1]
                 top2 = lg.topk(2).values
-                assert (top2[0] - top2[1]).item() <= 2 * BF16_ULP_AT_1 * max(1.0, abs(top2[0].item())), (f, q)
+                margin = (top2[0] - top2[1]).item()
+                two_steps = 2 * BF16_ULP_AT_1 * max(1.0, abs(top2[0].item()))
+                delta = (mine_logits[f][q] - lg).abs().max().item()
+                assert delta <= REL_TOL_BF16 * lg.abs().max().item(), (f, q, delta)
+                assert margin <= max(two_steps, 2 * delta), (f, q, margin, delta)
+                wide += margin > two_steps
                 mism += 1
                 break
     print(f"\n[teacher-forced] frames whose first differing argmax is a near-tie: {mism}/32 "
-          f"(every other argmax identical)")
+          f"({wide} of them wider than two bf16 steps but within twice the logit difference; every other argmax identical)")
+    assert wide <= 2
     row.close()
 
 
@@ -284,7 +296,15 @@ def test_batch_invariance_and_ragged(eng8, eng1):
     on the GEMV path, more go to the tensor cores, which sum in another order)."""
     lens = [64, 17, 130, 255]
     idss = [_ids(n, 10 + i) for i, n in enumerate(lens)]
-    solo = [_greedy_engine(eng1, ids, 6) for ids in idss]
+    # a lone row normally takes the two-kernel fused layers, which sum out_proj / w2 in another order:
+    # switch them off here so that one row and four rows run the same kernels
+    os.environ["VUIB_NO_FUSED"] = "1"
+    eng1._graphs = {}
+    try:
+        solo = [_greedy_engine(eng1, ids, 6) for ids in idss]
+    finally:
+        os.environ["VUIB_NO_FUSED"] = ""
+        eng1._graphs = {}
     eng = eng8
     eng.reset()
     rows = [eng.new_row() for _ in lens]
@@ -297,6 +317,66 @@ def test_batch_invariance_and_ragged(eng8, eng1):
     eng.check_device()
     for r in rows:
         r.close()
+
+
+def test_fused_layers_match_per_phase_kernels(eng1, oracle_fp32):
+    """A lone row runs each layer as two cluster kernels (attention block, MLP block; partial sums of
+    out_proj and w2 exchanged as fp32 rows), several rows as five kernels per layer.  Same rounding
+    points, another fp32 summation order: after a prefill + decode steps the residual stream after every
+    block, the final hidden, the cb0 and depth logits and the K/V rows written agree closely, both are
+    equally close to the fp32 oracle, and the greedy codes agree except at near-ties."""
+    eng = eng1
+    ids = _ids(200, 77)
+    res = {}
+    for off in ("1", ""):
+        os.environ["VUIB_NO_FUSED"] = off
+        eng._graphs = {}
+        eng.reset()
+        row = eng.new_row()
+        h = eng.prefill_ids(row, ids)
+        taps = torch.zeros(24, 1, 1024, device="cuda", dtype=torch.bfloat16)
+        rq_tap = torch.zeros(1, 15, 2048, device="cuda", dtype=torch.bfloat16)
+        eng._set_taps(taps, rq_tap)
+        eng._apply_cfg(None, greedy=True)
+        eng._g_slot_idx[0] = row.idx
+        eng._g_seq_inc[0] = 1
+        codes_in = torch.randint(0, 2048, (16,), generator=torch.Generator().manual_seed(8)).cuda()
+        frames = []
+        for f in range(3):  # teacher-forced on fixed input codes: both runs see the same history
+            eng._g_codes_in[0] = (codes_in + f) % 2048
+            eng._frame_call(1)
+            frames.append(eng._g_codes_in[0].clone())
+        torch.cuda.synchronize()
+        eng.check_device()
+        res[off] = dict(taps=taps.clone(), rq=rq_tap.clone(), hidden=eng._g_hidden_out.clone(), cb0=eng._g_cb0_out.clone(),
+                        eos=eng._g_eos_out.clone(), codes=torch.stack(frames).cpu(),
+                        k=torch.stack([eng._kv[li, 0, row.idx, 200:203].clone() for li in (0, 11, 23)]),
+                        v=torch.stack([eng._kv[li, 1, row.idx, 200:203].clone() for li in (0, 11, 23)]), off=row.offset)
+        eng._set_taps(None, None)
+        row.close()
+    os.environ["VUIB_NO_FUSED"] = ""
+    eng._graphs = {}
+    a, b = res[""], res["1"]  # fused, per-phase
+    assert a["off"] == b["off"] == 203 and a["k"].float().abs().max() > 0
+    worst = max(_rel(a["taps"][li], b["taps"][li]) for li in range(24))
+    print(f"\n[fused vs per-phase] worst per-layer hidden {worst:.5f}, final hidden {_rel(a['hidden'], b['hidden']):.5f}, "
+          f"cb0 {_rel(a['cb0'], b['cb0']):.5f}, depth logits {_rel(a['rq'], b['rq']):.5f}, K {_rel(a['k'], b['k']):.5f}")
+    # two bf16 evaluations that round at different summation orders: the bound the oracle tests use
+    assert worst < REL_TOL_BF16 and all(_cos(a["taps"][li], b["taps"][li]) > COS_TOL for li in range(24))
+    assert _rel(a["hidden"], b["hidden"]) < REL_TOL_BF16 and _cos(a["hidden"], b["hidden"]) > COS_TOL
+    assert _rel(a["cb0"], b["cb0"]) < REL_TOL_BF16 and _rel(a["k"], b["k"]) < REL_TOL_BF16 and _rel(a["v"], b["v"]) < REL_TOL_BF16
+    assert abs(a["eos"].float().item() - b["eos"].float().item()) < 3e-2
+    assert _cos(a["rq"], b["rq"]) > COS_TOL
+    # and the fused path is as close to the fp32 evaluation as the per-phase path is
+    o32 = oracle_fp32
+    o32.seq_lens = [0]
+    o32.prefill_text(0, ids)
+    codes_in = torch.randint(0, 2048, (16,), generator=torch.Generator().manual_seed(8))
+    for f in range(3):
+        h32, cb32, _ = o32.backbone_step([0], ((codes_in + f) % 2048)[None])
+    ea, eb = _rel(a["hidden"], h32[0]), _rel(b["hidden"], h32[0])
+    print(f"[fused vs per-phase] final hidden vs fp32: fused {ea:.4f}, per-phase {eb:.4f}")
+    assert ea < REL_TOL + 5e-3 and ea < 1.25 * eb + 2e-3
 
 
 def test_tensor_core_path_matches_gemv_path(nano_model, oracle_fp32):

@@ -181,6 +181,10 @@ struct StageNorm {
     const bf16* w;   // (K)
     float eps;
     int row_mul, row_add;
+    // single-row form only: the row is x + bf16(sum_p parts[p]), the partial rows (n_parts, K) fp32 that
+    // the fused two-kernel layers leave behind (fused_blocks.cuh), added in row order
+    const float* parts = nullptr;
+    int n_parts = 0;
     // The norm weights are constants: a kernel fetches them before it waits for its predecessor,
     // so that their L2 round trip is not paid between the reduction and the scaling.
     template <int K>
@@ -212,6 +216,17 @@ struct StageNorm {
                 if (k < K) {
                     uint4 u = __ldcg(reinterpret_cast<const uint4*>(xr + k));
                     unpack8(u, v[it]);
+                    if (n_parts > 0) {
+                        float sp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        for (int p = 0; p < n_parts; ++p) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * K + k));
+                            const float4 b = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * K + k + 4));
+                            sp[0] += a.x; sp[1] += a.y; sp[2] += a.z; sp[3] += a.w;
+                            sp[4] += b.x; sp[5] += b.y; sp[6] += b.z; sp[7] += b.w;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[it][j] = rbf(v[it][j] + rbf(sp[j]));
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) ss = fmaf(v[it][j], v[it][j], ss);
                 }
@@ -929,12 +944,35 @@ static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restric
                                                     bf16* __restrict__ out, int d,
                                                     const int32_t* __restrict__ row_slot,
                                                     const int32_t* __restrict__ seq_inc,
-                                                    int32_t* __restrict__ seq_lens, int bump) {
+                                                    int32_t* __restrict__ seq_lens, int bump,
+                                                    const float* __restrict__ parts, int n_parts,
+                                                    bf16* __restrict__ xsum_out) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x;
     __shared__ float red[4];
+    __shared__ __align__(16) bf16 xsum[1024];
     const bf16* xr = x + (size_t)r * d;
+    if (n_parts > 0) {
+        // single row, d <= 1024: x + bf16(sum of the fused layers' partial rows), kept for the second pass
+        for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
+            float f[8], sp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            unpack8(__ldcg(reinterpret_cast<const uint4*>(xr + k)), f);
+            for (int p = 0; p < n_parts; ++p) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * d + k));
+                const float4 b = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * d + k + 4));
+                sp[0] += a.x; sp[1] += a.y; sp[2] += a.z; sp[3] += a.w;
+                sp[4] += b.x; sp[5] += b.y; sp[6] += b.z; sp[7] += b.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = rbf(f[j] + rbf(sp[j]));
+            const uint4 u = pack8(f);
+            *reinterpret_cast<uint4*>(xsum + k) = u;
+            if (xsum_out) *reinterpret_cast<uint4*>(xsum_out + k) = u;
+        }
+        __syncthreads();
+        xr = xsum;
+    }
     float ss = 0.f;
     for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
         float f[8];

@@ -1,0 +1,750 @@
+// One transformer layer of a single-row decode step in TWO kernels instead of five.
+//
+// A chain of dependent launches costs ~3 us per hand-over whatever the bytes, so the number of
+// hand-overs is what a one-stream frame pays for.  Both kernels here run as thread-block clusters of
+// 8 CTAs (the portable size: this part's GPCs do not all hold 16 free SMs); what used to cross a kernel boundary (q/k/v -> attention -> out_proj; SwiGLU -> w2) now
+// crosses a hardware cluster barrier through distributed shared memory, and only the residual stream
+// crosses launches, as per-cluster partial rows that the consumer adds in a fixed order:
+//
+//   k_attn_block  (one cluster per kv head)   x = x_in + bf16(sum parts_in); h = RMSNorm(x);
+//       this head group's Wqkv rows (+RoPE, K/V append) -> cluster exchange -> attention over the
+//       cache, keys split over the 8 CTAs, partial softmax states exchanged and merged in CTA order
+//       -> this head group's K-slice of out_proj -> parts_out[kv head][d]      (fp32 partial rows)
+//   k_mlp_block   (11 or 12 clusters)         x = x_in + bf16(sum parts_in); h = RMSNorm(x);
+//       a slice of w1/w3 rows -> SiLU*gate -> cluster exchange -> the matching K-slice of w2
+//       -> parts_out[cluster][d]
+//
+// Rounding points are those of the five-kernel path (every tensor PyTorch materialises in bf16 is
+// rounded at the same place: src/vui/model.py:204-297, 359-375; src/vui/rope.py:50); out_proj and w2
+// sums are accumulated as per-cluster partials in fp32 and rounded once, so only the fp32 summation
+// order differs.
+//
+// Weights reach shared memory through bulk asynchronous copies (cp.async.bulk + mbarrier) issued
+// BEFORE the kernel waits for its predecessor (programmatic dependent launch): the copy engine keeps
+// HBM busy across the hand-over whenever both kernels fit on an SM together; each kernel also asks the
+// L2 for its successor's matrices, so that a successor that could not start early still finds them on
+// chip.  No copy here uses cluster multicast.  Every mbarrier wait is
+// bounded; cluster barriers are reached by every CTA unconditionally.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "tc_gemm.cuh"  // smem_u32, mbarrier helpers
+
+namespace vuib {
+
+namespace cg = cooperative_groups;
+
+constexpr int FB_THREADS = 256;  // attention block
+constexpr int FB_WARPS = 8;
+constexpr int FB_CL = 8;         // CTAs per cluster
+constexpr int FB_ATT_PRE = 4;    // key blocks (of 32 per CTA) whose loads are in flight before use
+constexpr int FB_MAX_PF = 3;     // matrices of the successor a kernel asks the L2 for
+
+// Regions of constant memory (the next kernel's matrices) to pull into L2, shared by the whole grid.
+struct PrefetchList {
+    const void* ptr[FB_MAX_PF];
+    unsigned long long bytes[FB_MAX_PF];
+};
+
+__device__ __forceinline__ void prefetch_l2(const PrefetchList& pf, int n_threads_cta) {
+    const size_t tid = (size_t)blockIdx.x * n_threads_cta + threadIdx.x, nth = (size_t)gridDim.x * n_threads_cta;
+#pragma unroll
+    for (int r = 0; r < FB_MAX_PF; ++r) {
+        if (!pf.ptr[r]) continue;
+        const char* base = static_cast<const char*>(pf.ptr[r]);
+        const size_t lines = (size_t)pf.bytes[r] / 128;
+        for (size_t i = tid; i < lines; i += nth) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + i * 128));
+    }
+}
+// Split cluster barrier: arrive when the CTA starts, wait right before the first access to a peer's
+// shared memory, which is only legal once every CTA of the cluster has started.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void fb_stamp(unsigned long long* dbg, int i) {
+    if (dbg && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        dbg[i] = t;
+    }
+}
+
+constexpr int FLAG_COPY_TIMEOUT = 16;  // same bit as the tensor-core pipeline: "a bounded wait ran out"
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Waits for this CTA's weight copies; on expiry records the flag and waits once more so that the
+// CTA does not retire with copies still landing in its shared memory.
+__device__ __forceinline__ void wait_weights(uint64_t* bar, unsigned limit, int32_t* flag) {
+    if (!mbar_wait(bar, 0, limit)) {
+        if (threadIdx.x == 0) atomicOr(flag, FLAG_COPY_TIMEOUT);
+        mbar_wait(bar, 0, limit);
+    }
+}
+
+// x[k] = x_in[k] + bf16(sum_p parts[p][k]) for this thread's EPT consecutive elements.  All rows (at
+// most FB_MAX_PARTS) are requested at once and added in row order.
+constexpr int FB_MAX_PARTS = 16;
+template <int K, int EPT>
+__device__ __forceinline__ void load_residual(const bf16* x_in, const float* parts, int n_parts, int k0,
+                                              float (&x)[EPT]) {
+    static_assert(EPT == 2 || EPT == 4, "2 or 4 elements per thread");
+    float s[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) s[j] = 0.f;
+    if constexpr (EPT == 4) {
+        const uint2 xr = __ldcg(reinterpret_cast<const uint2*>(x_in + k0));
+        float4 p[FB_MAX_PARTS];
+#pragma unroll
+        for (int u = 0; u < FB_MAX_PARTS; ++u)
+            p[u] = u < n_parts ? __ldcg(reinterpret_cast<const float4*>(parts + (size_t)u * K + k0))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < FB_MAX_PARTS; ++u) { s[0] += p[u].x; s[1] += p[u].y; s[2] += p[u].z; s[3] += p[u].w; }
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xr);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+    } else {
+        const unsigned xr = __ldcg(reinterpret_cast<const unsigned*>(x_in + k0));
+        float2 p[FB_MAX_PARTS];
+#pragma unroll
+        for (int u = 0; u < FB_MAX_PARTS; ++u)
+            p[u] = u < n_parts ? __ldcg(reinterpret_cast<const float2*>(parts + (size_t)u * K + k0)) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < FB_MAX_PARTS; ++u) { s[0] += p[u].x; s[1] += p[u].y; }
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr));
+        x[0] = a.x; x[1] = a.y;
+    }
+    if (n_parts > 0) {
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) x[j] = rbf(x[j] + rbf(s[j]));
+    }
+}
+
+template <int EPT>
+__device__ __forceinline__ void store_bf16(bf16* dst, const float (&x)[EPT]) {
+    if constexpr (EPT == 4) {
+        uint2 u;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+        h[0] = __floats2bfloat162_rn(x[0], x[1]);
+        h[1] = __floats2bfloat162_rn(x[2], x[3]);
+        *reinterpret_cast<uint2*>(dst) = u;
+    } else {
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(x[0], x[1]);
+    }
+}
+
+// RMSNorm of the CTA's copy of x (thread holds EPT elements) into shared memory as bf16.
+template <int K, int EPT, int NW>
+__device__ __forceinline__ void norm_to_smem(const float (&x)[EPT], const float (&w)[EPT], float eps, bf16* xs, int k0,
+                                             float* red) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) ss = fmaf(x[j], x[j], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NW; ++i) tot += red[i];
+    const float rinv = rsqrtf(tot / (float)K + eps);
+    float o[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) o[j] = rbf(x[j] * rinv) * w[j];
+    store_bf16<EPT>(xs + k0, o);
+}
+
+// This lane's share of the normed row: K / 256 sixteen-byte pieces, as floats.
+template <int K>
+__device__ __forceinline__ void load_h(const bf16* xs, float (&hf)[K / 32], int lane) {
+#pragma unroll
+    for (int it = 0; it < K / 256; ++it) {
+        float t[8];
+        unpack8(*reinterpret_cast<const uint4*>(xs + it * 256 + lane * 8), t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) hf[it * 8 + j] = t[j];
+    }
+}
+
+// NR dot products of weight rows in shared memory with the normed row, this lane's share of each.
+// Every load is issued before the first use and every row has two accumulators of its own, so the
+// dependent chains are short and many.
+template <int K, int NR>
+__device__ __forceinline__ void dot_rows(const bf16* const (&wrow)[NR], const float (&hf)[K / 32], int lane,
+                                         float (&acc)[NR]) {
+    constexpr int IT = K / 256;
+    uint4 w[NR][IT];
+#pragma unroll
+    for (int i = 0; i < NR; ++i)
+#pragma unroll
+        for (int it = 0; it < IT; ++it) w[i][it] = *reinterpret_cast<const uint4*>(wrow[i] + it * 256 + lane * 8);
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            float wf[8];
+            unpack8(w[i][it], wf);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                a0 = fmaf(wf[j], hf[it * 8 + j], a0);
+                a1 = fmaf(wf[4 + j], hf[it * 8 + 4 + j], a1);
+            }
+        }
+        acc[i] = a0 + a1;
+    }
+}
+
+// Sum NV values per lane over a group of lanes (xor offsets O, O/2, ..., 1) with the array halved at
+// every step while it has more than one entry: NV - 1 + (rounds left) shuffles instead of NV x rounds.
+// Afterwards a lane holds the total of ONE value: the halving round at offset o keeps the upper half of
+// the array in lanes whose bit o is set, so its index is made of those bits, most significant first.
+template <int NV, int O>
+struct GroupReduce {
+    static __device__ __forceinline__ float run(const float (&v)[NV], int lane) {
+        if constexpr (NV > 1) {
+            float k[NV / 2];
+            const bool up = (lane & O) != 0;
+#pragma unroll
+            for (int i = 0; i < NV / 2; ++i) {
+                const float keep = up ? v[i + NV / 2] : v[i];
+                const float send = up ? v[i] : v[i + NV / 2];
+                k[i] = keep + __shfl_xor_sync(0xffffffffu, send, O);
+            }
+            if constexpr (O > 1) return GroupReduce<NV / 2, O / 2>::run(k, lane);
+            else return k[0];
+        } else {
+            const float c[1] = {v[0] + __shfl_xor_sync(0xffffffffu, v[0], O)};
+            if constexpr (O > 1) return GroupReduce<1, O / 2>::run(c, lane);
+            else return c[0];
+        }
+    }
+    // index of the value this lane ends up with
+    static __device__ __forceinline__ int index(int lane) {
+        if constexpr (NV > 1) {
+            const int bit = (lane & O) ? NV / 2 : 0;
+            if constexpr (O > 1) return bit + GroupReduce<NV / 2, O / 2>::index(lane);
+            else return bit;
+        } else {
+            return 0;
+        }
+    }
+};
+
+// Rows of a small matrix in shared memory (row-major, C columns of bf16, C / 8 lanes per row) times a
+// vector in shared memory (fp32): the warp's RW rows at once, each lane accumulating NV rows before one
+// halving reduction; out[row] is written by the lanes that end up holding a row's total.
+template <int C, int RW>
+__device__ __forceinline__ void small_matvec(const bf16* mat, const float* vec, int row0, float* out, int lane) {
+    constexpr int LPR = (C / 8 < 32) ? C / 8 : 32;   // lanes per row
+    constexpr int CPL = C / 8 / LPR;                 // 16-byte pieces per lane and row
+    constexpr int RPP = 32 / LPR;                    // rows in flight per pass
+    constexpr int NV = RW / RPP;                     // rows accumulated per lane
+    static_assert(C % 8 == 0 && (C / 8) % LPR == 0 && RW % RPP == 0 && (NV & (NV - 1)) == 0 && NV <= LPR, "shape");
+    const int cl = lane % LPR, grp = lane / LPR;
+    float vf[CPL][8];
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) {
+        const float4 a0 = *reinterpret_cast<const float4*>(vec + (c * LPR + cl) * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(vec + (c * LPR + cl) * 8 + 4);
+        vf[c][0] = a0.x; vf[c][1] = a0.y; vf[c][2] = a0.z; vf[c][3] = a0.w;
+        vf[c][4] = a1.x; vf[c][5] = a1.y; vf[c][6] = a1.z; vf[c][7] = a1.w;
+    }
+    uint4 w[NV][CPL];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int c = 0; c < CPL; ++c)
+            w[i][c] = *reinterpret_cast<const uint4*>(mat + (size_t)(row0 + grp * NV + i) * C + (c * LPR + cl) * 8);
+    float s[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+            float wf[8];
+            unpack8(w[i][c], wf);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                a0 = fmaf(wf[j], vf[c][j], a0);
+                a1 = fmaf(wf[4 + j], vf[c][4 + j], a1);
+            }
+        }
+        s[i] = a0 + a1;
+    }
+    const float tot = GroupReduce<NV, LPR / 2>::run(s, lane);
+    constexpr int WRITERS_STRIDE = LPR / NV;  // lanes of a group that differ only in the low bits hold the same row
+    if (cl % WRITERS_STRIDE == 0) out[row0 + grp * NV + GroupReduce<NV, LPR / 2>::index(lane)] = tot;
+}
+
+// ---------------------------------------------------------------------------
+// Attention block
+// ---------------------------------------------------------------------------
+struct AttnBlockArgs {
+    const bf16* x_in;       // (K) residual stream before this layer (or the MLP block's input row)
+    const float* parts_in;  // (n_parts_in, K) partial rows of the previous block's last product
+    int n_parts_in;
+    bf16* x_out;            // (K) x as this block sees it (read by the MLP block that follows)
+    bf16* tap;              // optional second copy of x
+    const bf16* norm_w;
+    float eps;
+    const bf16* wqkv;       // ((Hq + 2 Hkv) * 64, K), rows q | k | v
+    const bf16* wo;         // (K, Hq * 64)
+    float* parts_out;       // (Hkv, K)
+    bf16* k_cache;          // (slots, max_seq, Hkv, 64) of this layer
+    bf16* v_cache;
+    const int32_t* row_slot;  // checked (slot, position) of the row; NULL -> fixed_slot / fixed_pos
+    const int32_t* row_pos;
+    int fixed_slot, fixed_pos;
+    int max_seq;
+    const bf16* rope;       // (max_seq, 64, 2) or NULL
+    int Hq, Hkv;
+    int32_t* flag;
+    unsigned spin_limit;
+    PrefetchList next;      // the following kernel's matrices
+    unsigned long long* dbg;  // optional: device-clock stamps of CTA 0 (profiling aid)
+};
+
+template <int K, int G>
+struct AttnBlockSmem {
+    static constexpr int QR = G * HD / FB_CL;  // q rows of this CTA (16 or 8)
+    static constexpr int KR = HD / FB_CL;      // k rows, and v rows (8)
+    static constexpr int NR = QR + 2 * KR;
+    static constexpr int NP = NR / 2;          // interleaved row pairs
+    static constexpr int PPW = (NP + FB_WARPS - 1) / FB_WARPS;  // pairs per warp
+    static constexpr int OR = K / FB_CL;       // out_proj rows of this CTA
+    static constexpr int OC = G * HD;          // out_proj columns (this head group's slice)
+    alignas(16) bf16 w[NR * K];
+    alignas(16) bf16 wo[OR * OC];
+    alignas(16) bf16 xs[K];
+    alignas(16) float qkv[G * HD + 2 * HD];    // q heads | new k | new v of the head group (bf16 values)
+    float part[FB_CL][G][HD + 2];              // per CTA: acc[64], m, l
+    float wpart[FB_WARPS][G][8][10];           // per warp: [s][acc8, m, l]
+    alignas(16) float attn[G * HD];
+    float s_new[G];
+    float red[FB_WARPS];
+    alignas(8) uint64_t bar;
+};
+
+template <int K, int G>
+__global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(AttnBlockArgs a) {
+    using S = AttnBlockSmem<K, G>;
+    constexpr int EPT = K / FB_THREADS;
+    constexpr int QR = S::QR, KR = S::KR, OR = S::OR, OC = S::OC, NP = S::NP;
+    static_assert(NP <= 2 * FB_WARPS, "at most two row pairs per warp");
+    extern __shared__ __align__(16) unsigned char fb_smem[];
+    S& sm = *reinterpret_cast<S*>(fb_smem);
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int kvh = blockIdx.x / FB_CL;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qcols = a.Hq * HD, kvcols = a.Hkv * HD;
+    fb_stamp(a.dbg, 0);
+    pdl_trigger();
+    cluster_arrive();
+
+    // ---- weights: bulk copies into shared memory, before the predecessor is waited for
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_init(&sm.bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&sm.bar, (uint32_t)(S::NR * K * 2 + OR * OC * 2));
+            bulk_g2s(sm.w, a.wqkv + (size_t)(kvh * G * HD + rank * QR) * K, QR * K * 2, &sm.bar);
+            bulk_g2s(sm.w + QR * K, a.wqkv + (size_t)(qcols + kvh * HD + rank * KR) * K, KR * K * 2, &sm.bar);
+            bulk_g2s(sm.w + (QR + KR) * K, a.wqkv + (size_t)(qcols + kvcols + kvh * HD + rank * KR) * K, KR * K * 2,
+                     &sm.bar);
+        }
+        __syncwarp();
+        for (int j = lane; j < OR; j += 32)
+            bulk_g2s(sm.wo + j * OC, a.wo + (size_t)(rank * OR + j) * qcols + kvh * OC, OC * 2, &sm.bar);
+    }
+    prefetch_l2(a.next, FB_THREADS);
+    const int k0 = tid * EPT;
+    float nw[EPT];
+    {
+        bf16 t[EPT];
+        if constexpr (EPT == 4) *reinterpret_cast<uint2*>(t) = __ldg(reinterpret_cast<const uint2*>(a.norm_w + k0));
+        else *reinterpret_cast<unsigned*>(t) = __ldg(reinterpret_cast<const unsigned*>(a.norm_w + k0));
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) nw[j] = bf2f(t[j]);
+    }
+    pdl_wait();
+    fb_stamp(a.dbg, 1);
+
+    // ---- row position first (the K/V requests depend on it), then the residual stream
+    int slot = a.fixed_slot, pos = a.fixed_pos;
+    if (a.row_slot) {
+        slot = __ldcg(a.row_slot);
+        pos = __ldcg(a.row_pos);
+    }
+    float x[EPT];
+    load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
+
+    // old keys [0, pos) split over the cluster's CTAs; this CTA's first FB_ATT_PRE blocks requested now
+    const int n_old = pos;
+    const int chunk = (n_old + FB_CL - 1) / FB_CL;
+    const int t_begin = rank * chunk, t_end = min(n_old, t_begin + chunk);
+    const int s8 = lane & 7, g4 = lane >> 3;
+    const size_t pos_stride = (size_t)kvcols;
+    const bf16* kb = a.k_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
+    const bf16* vb = a.v_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
+    uint4 kr[FB_ATT_PRE], vr[FB_ATT_PRE];
+#pragma unroll
+    for (int it = 0; it < FB_ATT_PRE; ++it) {
+        const int t = t_begin + it * 32 + warp * 4 + g4;
+        if (t < t_end) {
+            kr[it] = ldg_stream(kb + (size_t)t * pos_stride);
+            vr[it] = ldg_stream(vb + (size_t)t * pos_stride);
+        } else {
+            kr[it] = make_uint4(0, 0, 0, 0);
+            vr[it] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    // Each warp owns two interleaved row pairs (warp, warp + 8); after the reduction lanes 0-7 hold the
+    // first pair, lanes 16-23 the second.  RoPE factors of the lane's pair:
+    const int my_pair = warp + (lane >> 4) * FB_WARPS;
+    const bool pair_live = my_pair < NP;
+    const int prow = 2 * (pair_live ? my_pair : warp);  // first local row of the pair
+    const bool is_q = prow < QR, is_k = !is_q && prow < QR + KR;
+    const int sub = is_q ? prow : (is_k ? prow - QR : prow - QR - KR);
+    float c0 = 1.f, s0 = 0.f, c1 = 1.f, s1 = 0.f;
+    if (a.rope && (is_q || is_k)) {
+        const int dd = (is_q ? rank * QR + sub : rank * KR + sub) & (HD - 1);
+        const uint2 f = __ldg(reinterpret_cast<const uint2*>(a.rope + ((size_t)pos * HD + dd) * 2));
+        c0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x & 0xffffu)));
+        s0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x >> 16)));
+        c1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y & 0xffffu)));
+        s1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y >> 16)));
+    }
+    fb_stamp(a.dbg, 8);
+    if (blockIdx.x == 0) {
+        store_bf16<EPT>(a.x_out + k0, x);
+        if (a.tap) store_bf16<EPT>(a.tap + k0, x);
+    }
+    norm_to_smem<K, EPT, FB_WARPS>(x, nw, a.eps, sm.xs, k0, sm.red);
+    __syncthreads();
+    fb_stamp(a.dbg, 2);
+    wait_weights(&sm.bar, a.spin_limit, a.flag);
+    cluster_wait();
+    fb_stamp(a.dbg, 3);
+
+    // ---- q/k/v rows of this CTA: four rows per warp at once, results to every CTA of the cluster
+    {
+        float hf[K / 32];
+        load_h<K>(sm.xs, hf, lane);
+        const int p1 = warp + FB_WARPS < NP ? warp + FB_WARPS : warp;  // a warp without a second pair repeats its first
+        const bf16* rows[4] = {sm.w + (size_t)(2 * warp) * K, sm.w + (size_t)(2 * warp + 1) * K,
+                               sm.w + (size_t)(2 * p1) * K, sm.w + (size_t)(2 * p1 + 1) * K};
+        float acc[4];
+        dot_rows<K, 4>(rows, hf, lane, acc);
+        // lanes 0-7: row 0 of pair one, 8-15: row 1, 16-23: row 0 of pair two, 24-31: row 1
+        const float mine = rbf(GroupReduce<4, 16>::run(acc, lane));
+        const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+        if (pair_live && (lane & 8) == 0) {
+            float t0 = mine, t1 = other;
+            if (a.rope && (is_q || is_k)) {
+                // t*cos + rotate_half(t)*sin, each product and the sum rounded to bf16
+                const float o0 = rbf(rbf(t0 * c0) + rbf((-t1) * s0));
+                const float o1 = rbf(rbf(t1 * c1) + rbf(t0 * s1));
+                t0 = o0;
+                t1 = o1;
+            }
+            // place of the pair inside the head group's [q | k | v] vector; lane & 7 = the peer it goes to
+            const int idx = is_q ? rank * QR + sub : (is_k ? G * HD : G * HD + HD) + rank * KR + sub;
+            float* dst = cluster.map_shared_rank(sm.qkv, lane & 7);
+            *reinterpret_cast<float2*>(dst + idx) = make_float2(t0, t1);
+            if (!is_q && (lane & 7) == 0) {
+                bf16* cache = is_k ? a.k_cache : a.v_cache;
+                const int col = kvh * HD + rank * KR + sub;
+                *reinterpret_cast<__nv_bfloat162*>(cache + ((size_t)slot * a.max_seq + pos) * pos_stride + col) =
+                    __floats2bfloat162_rn(t0, t1);
+            }
+        }
+    }
+    __syncthreads();
+    fb_stamp(a.dbg, 9);
+    cluster.sync();
+    fb_stamp(a.dbg, 4);
+
+    // ---- attention: this CTA's share of the old keys
+    float qf[G][8];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        const float4 q0 = *reinterpret_cast<const float4*>(sm.qkv + h * HD + s8 * 8);
+        const float4 q1 = *reinterpret_cast<const float4*>(sm.qkv + h * HD + s8 * 8 + 4);
+        qf[h][0] = q0.x; qf[h][1] = q0.y; qf[h][2] = q0.z; qf[h][3] = q0.w;
+        qf[h][4] = q1.x; qf[h][5] = q1.y; qf[h][6] = q1.z; qf[h][7] = q1.w;
+    }
+    if (warp < G) {  // score of the new key (this step's own position), one warp per q head
+        const float* q = sm.qkv + warp * HD;
+        const float* kn = sm.qkv + G * HD;
+        float d = q[lane] * kn[lane] + q[lane + 32] * kn[lane + 32];
+        d = warp_sum(d);
+        if (lane == 0) sm.s_new[warp] = d * 0.125f;
+    }
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        m[h] = NEG_BIG;
+        l[h] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+    }
+    auto consume = [&](const uint4& kraw, const uint4& vraw, bool ok) {
+        float kf[8], vf[8];
+        unpack8(kraw, kf);
+        unpack8(vraw, vf);
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float d = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d = fmaf(qf[h][j], kf[j], d);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (ok) {
+                const float sc = d * 0.125f;
+                const float mn = fmaxf(m[h], sc);
+                const float corr = __expf(m[h] - mn), p = __expf(sc - mn);
+                l[h] = l[h] * corr + p;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(p, vf[j], acc[h][j] * corr);
+                m[h] = mn;
+            }
+        }
+    };
+#pragma unroll
+    for (int it = 0; it < FB_ATT_PRE; ++it) {
+        if (t_begin + it * 32 < t_end) {  // uniform over the CTA
+            const int t = t_begin + it * 32 + warp * 4 + g4;
+            consume(kr[it], vr[it], t < t_end);
+        }
+    }
+    for (int tb = t_begin + FB_ATT_PRE * 32; tb < t_end; tb += 32) {  // longer caches: the rest, block by block
+        const int t = tb + warp * 4 + g4;
+        const bool ok = t < t_end;
+        const uint4 kraw = ok ? ldg_stream(kb + (size_t)t * pos_stride) : make_uint4(0, 0, 0, 0);
+        const uint4 vraw = ok ? ldg_stream(vb + (size_t)t * pos_stride) : make_uint4(0, 0, 0, 0);
+        consume(kraw, vraw, ok);
+    }
+    // merge the warp's 4 key groups, then the CTA's 8 warps
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
+            const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+            float ao[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ao[j] = __shfl_xor_sync(0xffffffffu, acc[h][j], o);
+            softmax_merge(m[h], l[h], acc[h], mo, lo, ao);
+        }
+    }
+    if (g4 == 0) {
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sm.wpart[warp][h][s8][j] = acc[h][j];
+            sm.wpart[warp][h][s8][8] = m[h];
+            sm.wpart[warp][h][s8][9] = l[h];
+        }
+    }
+    __syncthreads();
+    fb_stamp(a.dbg, 10);
+    const int th = tid >> 6, tdim = tid & 63;  // thread (q head, dim) for tid < G * 64
+    if (tid < G * HD) {
+        const int ds = tdim >> 3, dj = tdim & 7;
+        float M_ = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < FB_WARPS; ++w) M_ = fmaxf(M_, sm.wpart[w][th][ds][8]);
+        float L_ = 0.f, O_ = 0.f;
+#pragma unroll
+        for (int w = 0; w < FB_WARPS; ++w) {
+            const float c = __expf(sm.wpart[w][th][ds][8] - M_);
+            L_ += sm.wpart[w][th][ds][9] * c;
+            O_ += sm.wpart[w][th][ds][dj] * c;
+        }
+#pragma unroll
+        for (int c = 0; c < FB_CL; ++c) {
+            float* dst = cluster.map_shared_rank(&sm.part[0][0][0], c) + (rank * G + th) * (HD + 2);
+            dst[tdim] = O_;
+            if (tdim == 0) {
+                dst[HD] = M_;
+                dst[HD + 1] = L_;
+            }
+        }
+    }
+    __syncthreads();
+    fb_stamp(a.dbg, 11);
+    cluster.sync();
+    fb_stamp(a.dbg, 5);
+    if (tid < G * HD) {
+        // every CTA merges the partial states in CTA order, then the new key: same bits everywhere
+        float Mx = sm.s_new[th];
+#pragma unroll
+        for (int c = 0; c < FB_CL; ++c) Mx = fmaxf(Mx, sm.part[c][th][HD]);
+        float Ls = 0.f, Os = 0.f;
+#pragma unroll
+        for (int c = 0; c < FB_CL; ++c) {
+            const float e = __expf(sm.part[c][th][HD] - Mx);
+            Ls += sm.part[c][th][HD + 1] * e;
+            Os += sm.part[c][th][tdim] * e;
+        }
+        const float en = __expf(sm.s_new[th] - Mx);
+        Ls += en;
+        Os += en * sm.qkv[G * HD + HD + tdim];
+        sm.attn[th * HD + tdim] = rbf(Os / Ls);
+    }
+    __syncthreads();
+    fb_stamp(a.dbg, 12);
+
+    // ---- this head group's K-slice of out_proj for the CTA's rows
+    small_matvec<OC, OR / FB_WARPS>(sm.wo, sm.attn, warp * (OR / FB_WARPS), a.parts_out + (size_t)kvh * K + rank * OR, lane);
+    fb_stamp(a.dbg, 6);
+}
+
+// ---------------------------------------------------------------------------
+// MLP block
+// ---------------------------------------------------------------------------
+struct MlpBlockArgs {
+    const bf16* x_in;       // (K) x as the attention block saw it
+    const float* parts_in;  // (n_parts_in, K) out_proj partial rows
+    int n_parts_in;
+    bf16* x_out;            // (K) x after the attention residual (read by the next attention block)
+    const bf16* norm_w;
+    float eps;
+    const bf16* w1;         // (F, K)
+    const bf16* w3;         // (F, K)
+    const bf16* w2;         // (K, F)
+    float* parts_out;       // (clusters, K)
+    // optional: warm L2 with the K/V rows the next attention block reads (rows before the row's position
+    // do not change during a frame)
+    const bf16* next_k;
+    const bf16* next_v;
+    const int32_t* row_slot;
+    const int32_t* row_pos;
+    int max_seq, kvcols;
+    int32_t* flag;
+    unsigned spin_limit;
+    PrefetchList next;
+    unsigned long long* dbg;
+};
+
+// U hidden units per CTA; the grid is F / (U * FB_CL) clusters.
+template <int K, int F, int U, int TH>
+struct MlpBlockSmem {
+    static constexpr int CU = U * FB_CL;     // hidden units of the cluster
+    static constexpr int OR = K / FB_CL;     // w2 rows of this CTA
+    static constexpr int NCL = F / CU;       // clusters
+    static_assert(F % CU == 0 && CU % 8 == 0, "ffn must split evenly into 16-byte pieces");
+    alignas(16) bf16 w1[U * K];
+    alignas(16) bf16 w3[U * K];
+    alignas(16) bf16 w2[OR * CU];
+    alignas(16) bf16 xs[K];
+    alignas(16) float g[CU];
+    float red[TH / 32];
+    alignas(8) uint64_t bar;
+};
+
+template <int K, int F, int U, int TH>
+__global__ void __launch_bounds__(TH, 1) k_mlp_block(MlpBlockArgs a) {
+    using S = MlpBlockSmem<K, F, U, TH>;
+    constexpr int EPT = K / TH;
+    constexpr int NWARP = TH / 32;
+    constexpr int CU = S::CU, OR = S::OR;
+    extern __shared__ __align__(16) unsigned char fb_smem[];
+    S& sm = *reinterpret_cast<S*>(fb_smem);
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int cid = blockIdx.x / FB_CL;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    fb_stamp(a.dbg, 0);
+    pdl_trigger();
+    cluster_arrive();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_init(&sm.bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + OR * CU * 2));
+            const size_t u0 = (size_t)cid * CU + rank * U;
+            bulk_g2s(sm.w1, a.w1 + u0 * K, U * K * 2, &sm.bar);
+            bulk_g2s(sm.w3, a.w3 + u0 * K, U * K * 2, &sm.bar);
+        }
+        __syncwarp();
+        for (int j = lane; j < OR; j += 32)
+            bulk_g2s(sm.w2 + j * CU, a.w2 + (size_t)(rank * OR + j) * F + cid * CU, CU * 2, &sm.bar);
+    }
+    prefetch_l2(a.next, TH);
+    const int k0 = tid * EPT;
+    float nw[EPT];
+    {
+        bf16 t[EPT];
+        if constexpr (EPT == 4) *reinterpret_cast<uint2*>(t) = __ldg(reinterpret_cast<const uint2*>(a.norm_w + k0));
+        else *reinterpret_cast<unsigned*>(t) = __ldg(reinterpret_cast<const unsigned*>(a.norm_w + k0));
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) nw[j] = bf2f(t[j]);
+    }
+    pdl_wait();
+    fb_stamp(a.dbg, 1);
+
+    float x[EPT];
+    load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
+    if (a.next_k) {  // one 128-byte line per thread and step, the grid shares the rows
+        const int slot = __ldcg(a.row_slot), pos = __ldcg(a.row_pos);
+        const size_t row_bytes = (size_t)a.kvcols * sizeof(bf16);
+        const size_t lines = (size_t)pos * row_bytes / 128;
+        const char* kbase = reinterpret_cast<const char*>(a.next_k) + (size_t)slot * a.max_seq * row_bytes;
+        const char* vbase = reinterpret_cast<const char*>(a.next_v) + (size_t)slot * a.max_seq * row_bytes;
+        for (size_t i = (size_t)blockIdx.x * TH + tid; i < 2 * lines; i += (size_t)gridDim.x * TH) {
+            const char* p = i < lines ? kbase + i * 128 : vbase + (i - lines) * 128;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+    }
+    if (blockIdx.x == 0) store_bf16<EPT>(a.x_out + k0, x);
+    norm_to_smem<K, EPT, NWARP>(x, nw, a.eps, sm.xs, k0, sm.red);
+    __syncthreads();
+    fb_stamp(a.dbg, 2);
+    wait_weights(&sm.bar, a.spin_limit, a.flag);
+    cluster_wait();
+    fb_stamp(a.dbg, 3);
+
+    // ---- SiLU(w1 h) * (w3 h) for this CTA's hidden units, two units (four rows) per warp at once,
+    //      sent to every CTA of the cluster
+    {
+        static_assert(U % 2 == 0, "units are taken in pairs");
+        float hf[K / 32];
+        load_h<K>(sm.xs, hf, lane);
+        for (int u0 = 2 * warp; u0 < U; u0 += 2 * NWARP) {
+            const bf16* rows[4] = {sm.w1 + (size_t)u0 * K, sm.w3 + (size_t)u0 * K, sm.w1 + (size_t)(u0 + 1) * K,
+                                   sm.w3 + (size_t)(u0 + 1) * K};
+            float acc[4];
+            dot_rows<K, 4>(rows, hf, lane, acc);
+            // lanes 0-7: w1 sum of unit u0, 8-15: its w3 sum, 16-23 / 24-31: the same for unit u0 + 1
+            const float mine = rbf(GroupReduce<4, 16>::run(acc, lane));
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+            if ((lane & 8) == 0) {
+                const float sl = rbf(mine / (1.0f + expf(-mine)));
+                const float gv = rbf(sl * other);
+                cluster.map_shared_rank(sm.g, lane & 7)[rank * U + u0 + (lane >> 4)] = gv;
+            }
+        }
+    }
+    __syncthreads();
+    fb_stamp(a.dbg, 9);
+    cluster.sync();
+    fb_stamp(a.dbg, 4);
+
+    // ---- the cluster's K-slice of w2 for this CTA's rows
+    static_assert(OR % NWARP == 0, "rows split evenly over the warps");
+    small_matvec<CU, OR / NWARP>(sm.w2, sm.g, warp * (OR / NWARP), a.parts_out + (size_t)cid * K + rank * OR, lane);
+    fb_stamp(a.dbg, 6);
+}
+
+}  // namespace vuib

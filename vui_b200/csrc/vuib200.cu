@@ -13,6 +13,7 @@
 
 #include "decode_kernels.cuh"
 #include "tc_gemm.cuh"
+#include "fused_blocks.cuh"
 
 using namespace vuib;
 
@@ -22,11 +23,13 @@ struct WsLayout {
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
     size_t trace;
     size_t xn, rq_xn, rq_attn, tc_partial, tc_counters;
+    size_t fx_a, fx_b, fparts_a, fparts_b, rq_fx_a, rq_fx_b, rq_fparts_a, rq_fparts_b;
     size_t total;
 };
 
 constexpr int TC_PARTIAL_TILES = 224;  // most (tile, split) pairs of one GEMM launch
-constexpr int TRACE_STAMPS = 32;        // device-clock stamps kept for vuib_read_trace
+constexpr int FUSED_MAX_PARTS = 16;     // most partial rows a fused block leaves (clusters of its grid)
+constexpr int TRACE_STAMPS = 64;        // device-clock stamps kept for vuib_read_trace
 
 // Tensor maps (TMA descriptors) of every weight matrix, built when the weights are bound.
 struct TcMaps {
@@ -55,6 +58,8 @@ struct VuibEngine {
     long long launches;
     int num_sms;        // 0 until a launch first asks the device
     unsigned spin_limit;  // bound of the waits inside kernels, in polls (vuib_set_wait_limit)
+    int fused_backbone;   // 0 = not asked yet, 1 = the two-kernel layers can run here, -1 = they cannot
+    int fused_depth;
     float* cb0_stats;   // optional (max_rows, 2) fp32: entropy and top probability of each cb0 draw
     TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
     char err[256];
@@ -108,6 +113,15 @@ static void make_layout(VuibEngine* e) {
     L.rq_attn = take(2 * RB * rd * 2);
     L.tc_partial = take((size_t)(TC_PARTIAL_TILES + 80) * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
     L.tc_counters = take(2 * 256 * 4);
+    // fused two-kernel layers (single row): x as each block sees it, and the partial rows between blocks
+    L.fx_a = take(d * 2);
+    L.fx_b = take(d * 2);
+    L.fparts_a = take((size_t)FUSED_MAX_PARTS * d * 4);
+    L.fparts_b = take((size_t)FUSED_MAX_PARTS * d * 4);
+    L.rq_fx_a = take(rd * 2);
+    L.rq_fx_b = take(rd * 2);
+    L.rq_fparts_a = take((size_t)FUSED_MAX_PARTS * rd * 4);
+    L.rq_fparts_b = take((size_t)FUSED_MAX_PARTS * rd * 4);
     L.total = off;
 }
 
@@ -575,9 +589,259 @@ static int32_t rq_layers_tc(VuibEngine* e, int M, bf16* x, int rows_per_b, int p
 }
 
 // ---------------------------------------------------------------------------
+// Single-row steps: each layer as two cluster kernels (fused_blocks.cuh).
+// ---------------------------------------------------------------------------
+// Where the residual stream is after a run of fused layers: x + bf16(sum of n_parts partial rows).
+struct Residual {
+    const bf16* x;
+    const float* parts;
+    int n_parts;
+};
+
+template <class... KArgs, class... Args>
+static cudaError_t launch_cluster(void (*kern)(KArgs...), int n_clusters, int threads, size_t smem, cudaStream_t s,
+                                  Args... args) {
+    prefer_max_smem(reinterpret_cast<const void*>(kern));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_clusters * FB_CL);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = FB_CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// Opts the kernel into its shared-memory size on the current device and asks whether `n_clusters`
+// clusters of FB_CL CTAs can be resident at once.
+template <class... KArgs>
+static bool cluster_kernel_fits(void (*kern)(KArgs...), int n_clusters, int threads, size_t smem) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_clusters * FB_CL);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = FB_CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return n >= n_clusters;
+}
+
+constexpr int FB_MLP_TH_BACKBONE = 512, FB_MLP_U_BACKBONE = 32;
+constexpr int FB_MLP_TH_DEPTH = 256, FB_MLP_U_DEPTH = 16;
+
+static bool fused_backbone_ok(VuibEngine* e) {
+    if (e->fused_backbone == 0) {
+        const VuibConfig& c = e->cfg;
+        bool ok = c.d_model == 1024 && c.n_heads == 16 && c.n_kv_heads == 8 && c.ffn == 3072;
+        ok = ok && cluster_kernel_fits(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>));
+        ok = ok && cluster_kernel_fits(k_mlp_block<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>,
+                                       3072 / (FB_MLP_U_BACKBONE * FB_CL), FB_MLP_TH_BACKBONE,
+                                       sizeof(MlpBlockSmem<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>));
+        e->fused_backbone = ok ? 1 : -1;
+    }
+    return e->fused_backbone == 1 && !env_off("VUIB_NO_FUSED");
+}
+
+static bool fused_depth_ok(VuibEngine* e) {
+    if (e->fused_depth == 0) {
+        const VuibConfig& c = e->cfg;
+        bool ok = c.rq_d_model == 512 && c.rq_n_heads == 8 && (c.rq_ffn == 1408 || c.rq_ffn == 1536);
+        ok = ok && cluster_kernel_fits(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>));
+        if (ok && c.rq_ffn == 1408)
+            ok = cluster_kernel_fits(k_mlp_block<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, 1408 / (FB_MLP_U_DEPTH * FB_CL),
+                                     FB_MLP_TH_DEPTH, sizeof(MlpBlockSmem<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>));
+        else if (ok)
+            ok = cluster_kernel_fits(k_mlp_block<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, 1536 / (FB_MLP_U_DEPTH * FB_CL),
+                                     FB_MLP_TH_DEPTH, sizeof(MlpBlockSmem<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>));
+        e->fused_depth = ok ? 1 : -1;
+    }
+    return e->fused_depth == 1 && !env_off("VUIB_NO_FUSED");
+}
+
+static PrefetchList prefetch_of(const void* a, size_t na, const void* b = nullptr, size_t nb = 0, const void* c = nullptr,
+                                size_t nc = 0) {
+    PrefetchList p;
+    if (env_off("VUIB_NO_L2PF")) a = b = c = nullptr;
+    p.ptr[0] = a; p.bytes[0] = na;
+    p.ptr[1] = b; p.bytes[1] = nb;
+    p.ptr[2] = c; p.bytes[2] = nc;
+    return p;
+}
+
+// The backbone's blocks for ONE row whose (slot, position) is row 0 of the workspace table and whose
+// input is L.x.  `after` names what follows the last block (its matrix is pulled into L2).
+static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, const void* after, size_t after_bytes) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    const int d = c.d_model, qc = c.n_heads * HD, kvc = c.n_kv_heads * HD;
+    const size_t qkv_bytes = (size_t)(qc + 2 * kvc) * d * 2, wo_bytes = (size_t)d * qc * 2, ffn_bytes = (size_t)c.ffn * d * 2;
+    constexpr int NCL = 3072 / (FB_MLP_U_BACKBONE * FB_CL);
+    bf16* xa = wsp<bf16>(e, L.fx_a);
+    bf16* xb = wsp<bf16>(e, L.fx_b);
+    float* pa = wsp<float>(e, L.fparts_a);
+    float* pb = wsp<float>(e, L.fparts_b);
+    for (int li = 0; li < c.n_layers; ++li) {
+        AttnBlockArgs aa;
+        memset(&aa, 0, sizeof(aa));
+        aa.x_in = li == 0 ? wsp<bf16>(e, L.x) : xb;
+        aa.parts_in = li == 0 ? nullptr : pb;
+        aa.n_parts_in = li == 0 ? 0 : NCL;
+        aa.x_out = xa;
+        aa.tap = (e->tap_layers && li > 0) ? e->tap_layers + (size_t)(li - 1) * c.max_rows * d : nullptr;
+        aa.norm_w = static_cast<const bf16*>(e->w.attn_norm[li]);
+        aa.eps = c.norm_eps;
+        aa.wqkv = static_cast<const bf16*>(e->w.wqkv[li]);
+        aa.wo = static_cast<const bf16*>(e->w.out_proj[li]);
+        aa.parts_out = pa;
+        aa.k_cache = static_cast<bf16*>(e->k[li]);
+        aa.v_cache = static_cast<bf16*>(e->v[li]);
+        aa.row_slot = wsp<int32_t>(e, L.row_slot);
+        aa.row_pos = wsp<int32_t>(e, L.row_pos);
+        aa.max_seq = c.max_seq;
+        aa.rope = e->rope;
+        aa.Hq = c.n_heads;
+        aa.Hkv = c.n_kv_heads;
+        aa.flag = wsp<int32_t>(e, L.flag);
+        aa.spin_limit = e->spin_limit;
+        aa.next = prefetch_of(e->w.w1[li], ffn_bytes, e->w.w3[li], ffn_bytes, e->w.w2[li], ffn_bytes);
+        if (env_off("VUIB_TRACE") && (li == 5 || li == 6)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 5) * 32;
+        CK(launch_cluster(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>), s, aa));
+        e->launches++;
+
+        MlpBlockArgs ma;
+        memset(&ma, 0, sizeof(ma));
+        ma.x_in = xa;
+        ma.parts_in = pa;
+        ma.n_parts_in = c.n_kv_heads;
+        ma.x_out = xb;
+        ma.norm_w = static_cast<const bf16*>(e->w.mlp_norm[li]);
+        ma.eps = c.norm_eps;
+        ma.w1 = static_cast<const bf16*>(e->w.w1[li]);
+        ma.w3 = static_cast<const bf16*>(e->w.w3[li]);
+        ma.w2 = static_cast<const bf16*>(e->w.w2[li]);
+        ma.parts_out = pb;
+        if (li + 1 < c.n_layers && !env_off("VUIB_NO_KVHINT")) {
+            ma.next_k = static_cast<const bf16*>(e->k[li + 1]);
+            ma.next_v = static_cast<const bf16*>(e->v[li + 1]);
+        }
+        ma.row_slot = wsp<int32_t>(e, L.row_slot);
+        ma.row_pos = wsp<int32_t>(e, L.row_pos);
+        ma.max_seq = c.max_seq;
+        ma.kvcols = kvc;
+        ma.flag = wsp<int32_t>(e, L.flag);
+        ma.spin_limit = e->spin_limit;
+        ma.next = li + 1 < c.n_layers ? prefetch_of(e->w.wqkv[li + 1], qkv_bytes, e->w.out_proj[li + 1], wo_bytes)
+                                      : prefetch_of(after, after_bytes);
+        if (env_off("VUIB_TRACE") && (li == 5 || li == 6)) ma.dbg = wsp<unsigned long long>(e, L.trace) + (li - 5) * 32 + 16;
+        CK(launch_cluster(k_mlp_block<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>, NCL, FB_MLP_TH_BACKBONE,
+                          sizeof(MlpBlockSmem<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>), s, ma));
+        e->launches++;
+    }
+    out->x = xb;
+    out->parts = pb;
+    out->n_parts = NCL;
+    return VUIB_OK;
+}
+
+// The depth transformer's blocks for ONE stream (row 0) at depth position `pos`, input token x.
+static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream_t s, Residual* out, const void* after,
+                               size_t after_bytes) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    const int rd = c.rq_d_model, Q = c.n_quantizers;
+    const size_t qkv_bytes = (size_t)3 * rd * rd * 2, wo_bytes = (size_t)rd * rd * 2, ffn_bytes = (size_t)c.rq_ffn * rd * 2;
+    const int ncl = c.rq_ffn / (FB_MLP_U_DEPTH * FB_CL);
+    bf16* xa = wsp<bf16>(e, L.rq_fx_a);
+    bf16* xb = wsp<bf16>(e, L.rq_fx_b);
+    float* pa = wsp<float>(e, L.rq_fparts_a);
+    float* pb = wsp<float>(e, L.rq_fparts_b);
+    const size_t layer_kv = (size_t)c.max_rows * Q * rd;
+    for (int li = 0; li < c.rq_n_layers; ++li) {
+        AttnBlockArgs aa;
+        memset(&aa, 0, sizeof(aa));
+        aa.x_in = li == 0 ? x : xb;
+        aa.parts_in = li == 0 ? nullptr : pb;
+        aa.n_parts_in = li == 0 ? 0 : ncl;
+        aa.x_out = xa;
+        aa.norm_w = static_cast<const bf16*>(e->w.rq_attn_norm[li]);
+        aa.eps = c.rq_norm_eps;
+        aa.wqkv = static_cast<const bf16*>(e->w.rq_wqkv[li]);
+        aa.wo = static_cast<const bf16*>(e->w.rq_out_proj[li]);
+        aa.parts_out = pa;
+        aa.k_cache = wsp<bf16>(e, L.rq_k) + li * layer_kv;
+        aa.v_cache = wsp<bf16>(e, L.rq_v) + li * layer_kv;
+        aa.fixed_slot = 0;
+        aa.fixed_pos = pos;
+        aa.max_seq = Q;
+        aa.Hq = c.rq_n_heads;
+        aa.Hkv = c.rq_n_heads;
+        aa.flag = wsp<int32_t>(e, L.flag);
+        aa.spin_limit = e->spin_limit;
+        aa.next = prefetch_of(e->w.rq_w1[li], ffn_bytes, e->w.rq_w3[li], ffn_bytes, e->w.rq_w2[li], ffn_bytes);
+        if (env_off("VUIB_TRACE_DEPTH") && pos == 8 && (li == 1 || li == 2)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 1) * 32;
+        CK(launch_cluster(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>), s, aa));
+        e->launches++;
+
+        MlpBlockArgs ma;
+        memset(&ma, 0, sizeof(ma));
+        ma.x_in = xa;
+        ma.parts_in = pa;
+        ma.n_parts_in = c.rq_n_heads;
+        ma.x_out = xb;
+        ma.norm_w = static_cast<const bf16*>(e->w.rq_mlp_norm[li]);
+        ma.eps = c.rq_norm_eps;
+        ma.w1 = static_cast<const bf16*>(e->w.rq_w1[li]);
+        ma.w3 = static_cast<const bf16*>(e->w.rq_w3[li]);
+        ma.w2 = static_cast<const bf16*>(e->w.rq_w2[li]);
+        ma.parts_out = pb;
+        ma.flag = wsp<int32_t>(e, L.flag);
+        ma.spin_limit = e->spin_limit;
+        ma.next = li + 1 < c.rq_n_layers ? prefetch_of(e->w.rq_wqkv[li + 1], qkv_bytes, e->w.rq_out_proj[li + 1], wo_bytes)
+                                         : prefetch_of(after, after_bytes);
+        if (env_off("VUIB_TRACE_DEPTH") && pos == 8 && (li == 1 || li == 2)) ma.dbg = wsp<unsigned long long>(e, L.trace) + (li - 1) * 32 + 16;
+        if (c.rq_ffn == 1408)
+            CK(launch_cluster(k_mlp_block<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, ncl, FB_MLP_TH_DEPTH,
+                              sizeof(MlpBlockSmem<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>), s, ma));
+        else
+            CK(launch_cluster(k_mlp_block<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, ncl, FB_MLP_TH_DEPTH,
+                              sizeof(MlpBlockSmem<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>), s, ma));
+        e->launches++;
+    }
+    out->x = xb;
+    out->parts = pb;
+    out->n_parts = ncl;
+    return VUIB_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Backbone: 24 blocks over M rows whose (slot, position) are in the workspace.
 // ---------------------------------------------------------------------------
-static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s) {
+static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s, Residual* out, const void* after = nullptr,
+                          size_t after_bytes = 0) {
+    out->x = wsp<bf16>(e, e->lay.x);
+    out->parts = nullptr;
+    out->n_parts = 0;
+    if (M == 1 && fused_backbone_ok(e)) return run_layers_fused(e, s, out, after, after_bytes);
     if (tc_ok(e, M)) return run_layers_tc(e, M, s);
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
@@ -647,11 +911,12 @@ extern "C" int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* ro
               wsp<int32_t>(e, L.row_pos), n_rows, e->cfg.n_slots, e->cfg.max_seq, wsp<int32_t>(e, L.flag)));
     e->launches++;
     CK(cudaMemcpyAsync(e->ws + L.x, emb_dev, (size_t)n_rows * d * 2, cudaMemcpyDeviceToDevice, s));
-    rc = run_layers(e, n_rows, s);
+    Residual res;
+    rc = run_layers(e, n_rows, s, &res);
     if (rc) return rc;
-    CK(launch(k_final_norm, n_rows, 128, 0, s, wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
+    CK(launch(k_final_norm, n_rows, 128, 0, s, res.x, static_cast<const bf16*>(e->w.final_norm),
                                         e->cfg.norm_eps, static_cast<bf16*>(hidden_out_dev), d,
-                                        nullptr, nullptr, nullptr, 0));
+                                        nullptr, nullptr, nullptr, 0, res.parts, res.n_parts, nullptr));
     e->launches++;
     CK(cudaGetLastError());
     return VUIB_OK;
@@ -677,11 +942,14 @@ extern "C" int32_t vuib_backbone_step(VuibEngine* e, int32_t B, const int32_t* s
                                     wsp<int32_t>(e, L.flag)));
     e->launches++;
     CK(cudaGetLastError());
-    rc = run_layers(e, B, s);
+    Residual res;
+    rc = run_layers(e, B, s, &res, e->w.codec_head, (size_t)c.codebook_size * c.d_model * 2);
     if (rc) return rc;
-    CK(launch(k_final_norm, B, 128, 0, s, wsp<bf16>(e, L.x), static_cast<const bf16*>(e->w.final_norm),
+    bf16* last_tap = (e->tap_layers && res.n_parts) ? e->tap_layers + (size_t)(c.n_layers - 1) * c.max_rows * c.d_model : nullptr;
+    CK(launch(k_final_norm, B, 128, 0, s, res.x, static_cast<const bf16*>(e->w.final_norm),
                                    c.norm_eps, static_cast<bf16*>(hidden_out_dev), c.d_model,
-                                   wsp<int32_t>(e, L.row_slot), seq_inc_dev, e->seq_lens, 1));
+                                   wsp<int32_t>(e, L.row_slot), seq_inc_dev, e->seq_lens, 1, res.parts, res.n_parts,
+                                   last_tap));
     e->launches++;
     CK(cudaGetLastError());
     return run_heads(e, B, static_cast<const bf16*>(hidden_out_dev), static_cast<bf16*>(cb0_out_dev),
@@ -803,9 +1071,12 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
 
     bf16* logits = wsp<bf16>(e, L.rq_logits);
     const bf16* head = static_cast<const bf16*>(e->w.rq_head);
+    const bool fused = B == 1 && fused_depth_ok(e);
     for (int i = 0; i < Qn - 1; ++i) {
+        Residual res{i == 0 ? x2 : x1, nullptr, 0};
         if (i > 0) {
-            rc = tc ? rq_layers_tc(e, B, x1, 1, i + 1, s) : rq_layers(e, B, x1, 1, i + 1, s);
+            if (fused) rc = rq_layers_fused(e, x1, i + 1, s, &res, head + (size_t)i * CS * rd, (size_t)CS * rd * 2);
+            else rc = tc ? rq_layers_tc(e, B, x1, 1, i + 1, s) : rq_layers(e, B, x1, 1, i + 1, s);
             if (rc) return rc;
         }
         if (tc) {
@@ -816,8 +1087,8 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
             TcEpiLogits el{logits, CS, e->tap_rq ? e->tap_rq + (size_t)i * CS : nullptr, (Q - 1) * CS};
             if ((rc = tc_gemm(e, e->tc->rq_head, e->tc->rq_head, xn, B, rd, CS, i * CS, el, s))) return rc;
         } else {
-            StageNorm sn{i == 0 ? x2 : x1, static_cast<const bf16*>(e->w.rq_norm), c.rq_norm_eps,
-                         i == 0 ? 2 : 1, i == 0 ? 1 : 0};
+            StageNorm sn{res.x, static_cast<const bf16*>(e->w.rq_norm), c.rq_norm_eps,
+                         i == 0 ? 2 : 1, i == 0 ? 1 : 0, res.parts, res.n_parts};
             EpiLogits el{head + (size_t)i * CS * rd, rd, CS, logits, nullptr, nullptr, nullptr,
                          e->tap_rq ? e->tap_rq + (size_t)i * CS : nullptr, (Q - 1) * CS};
             CK(VUIB_GEMV(rd, e, sn, el, B, CS, s));
