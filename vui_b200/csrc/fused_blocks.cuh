@@ -21,7 +21,8 @@
 //
 // Weights reach shared memory through bulk asynchronous copies (cp.async.bulk + mbarrier) issued
 // BEFORE the kernel waits for its predecessor (programmatic dependent launch): the copy engine keeps
-// HBM busy across the hand-over whenever both kernels fit on an SM together; each kernel also asks the
+// HBM busy across the hand-over whenever both kernels fit on an SM together (the column slices of out_proj
+// and w2 come as one tiled copy each: a row-by-row series of small bulk copies measured ~30 ns apiece); each kernel also asks the
 // L2 for its successor's matrices, so that a successor that could not start early still finds them on
 // chip.  No copy here uses cluster multicast.  Every mbarrier wait is
 // bounded; cluster barriers are reached by every CTA unconditionally.
@@ -318,8 +319,8 @@ struct AttnBlockSmem {
     static constexpr int PPW = (NP + FB_WARPS - 1) / FB_WARPS;  // pairs per warp
     static constexpr int OR = K / FB_CL;       // out_proj rows of this CTA
     static constexpr int OC = G * HD;          // out_proj columns (this head group's slice)
+    alignas(128) bf16 wo[OR * OC];             // destination of a tiled copy: first, 128-byte aligned
     alignas(16) bf16 w[NR * K];
-    alignas(16) bf16 wo[OR * OC];
     alignas(16) bf16 xs[K];
     alignas(16) float qkv[G * HD + 2 * HD];    // q heads | new k | new v of the head group (bf16 values)
     float part[FB_CL][G][HD + 2];              // per CTA: acc[64], m, l
@@ -331,12 +332,12 @@ struct AttnBlockSmem {
 };
 
 template <int K, int G>
-__global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(AttnBlockArgs a) {
+__global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_constant__ CUtensorMap map_wo, AttnBlockArgs a) {
     using S = AttnBlockSmem<K, G>;
     constexpr int EPT = K / FB_THREADS;
     constexpr int QR = S::QR, KR = S::KR, OR = S::OR, OC = S::OC, NP = S::NP;
     static_assert(NP <= 2 * FB_WARPS, "at most two row pairs per warp");
-    extern __shared__ __align__(16) unsigned char fb_smem[];
+    extern __shared__ __align__(128) unsigned char fb_smem[];
     S& sm = *reinterpret_cast<S*>(fb_smem);
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
@@ -358,10 +359,9 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(AttnBlockArgs a) {
             bulk_g2s(sm.w + QR * K, a.wqkv + (size_t)(qcols + kvh * HD + rank * KR) * K, KR * K * 2, &sm.bar);
             bulk_g2s(sm.w + (QR + KR) * K, a.wqkv + (size_t)(qcols + kvcols + kvh * HD + rank * KR) * K, KR * K * 2,
                      &sm.bar);
+            // the out_proj slice (OR rows x OC columns of a row-major matrix) as ONE tiled copy
+            tma_load_2d(sm.wo, &map_wo, kvh * OC, rank * OR, &sm.bar);
         }
-        __syncwarp();
-        for (int j = lane; j < OR; j += 32)
-            bulk_g2s(sm.wo + j * OC, a.wo + (size_t)(rank * OR + j) * qcols + kvh * OC, OC * 2, &sm.bar);
     }
     prefetch_l2(a.next, FB_THREADS);
     const int k0 = tid * EPT;
@@ -642,9 +642,9 @@ struct MlpBlockSmem {
     static constexpr int OR = K / FB_CL;     // w2 rows of this CTA
     static constexpr int NCL = F / CU;       // clusters
     static_assert(F % CU == 0 && CU % 8 == 0, "ffn must split evenly into 16-byte pieces");
+    alignas(128) bf16 w2[OR * CU];           // destination of a tiled copy: first, 128-byte aligned
     alignas(16) bf16 w1[U * K];
     alignas(16) bf16 w3[U * K];
-    alignas(16) bf16 w2[OR * CU];
     alignas(16) bf16 xs[K];
     alignas(16) float g[CU];
     float red[TH / 32];
@@ -652,12 +652,12 @@ struct MlpBlockSmem {
 };
 
 template <int K, int F, int U, int TH>
-__global__ void __launch_bounds__(TH, 1) k_mlp_block(MlpBlockArgs a) {
+__global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUtensorMap map_w2, MlpBlockArgs a) {
     using S = MlpBlockSmem<K, F, U, TH>;
     constexpr int EPT = K / TH;
     constexpr int NWARP = TH / 32;
     constexpr int CU = S::CU, OR = S::OR;
-    extern __shared__ __align__(16) unsigned char fb_smem[];
+    extern __shared__ __align__(128) unsigned char fb_smem[];
     S& sm = *reinterpret_cast<S*>(fb_smem);
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
@@ -676,10 +676,9 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(MlpBlockArgs a) {
             const size_t u0 = (size_t)cid * CU + rank * U;
             bulk_g2s(sm.w1, a.w1 + u0 * K, U * K * 2, &sm.bar);
             bulk_g2s(sm.w3, a.w3 + u0 * K, U * K * 2, &sm.bar);
+            // the w2 slice (OR rows x CU columns) as ONE tiled copy
+            tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
         }
-        __syncwarp();
-        for (int j = lane; j < OR; j += 32)
-            bulk_g2s(sm.w2 + j * CU, a.w2 + (size_t)(rank * OR + j) * F + cid * CU, CU * 2, &sm.bar);
     }
     prefetch_l2(a.next, TH);
     const int k0 = tid * EPT;

@@ -28,6 +28,8 @@ struct WsLayout {
 };
 
 constexpr int TC_PARTIAL_TILES = 224;  // most (tile, split) pairs of one GEMM launch
+constexpr int FB_MLP_TH_BACKBONE = 512, FB_MLP_U_BACKBONE = 32;  // threads, hidden units per CTA of the MLP block
+constexpr int FB_MLP_TH_DEPTH = 256, FB_MLP_U_DEPTH = 16;
 constexpr int FUSED_MAX_PARTS = 16;     // most partial rows a fused block leaves (clusters of its grid)
 constexpr int TRACE_STAMPS = 64;        // device-clock stamps kept for vuib_read_trace
 
@@ -38,6 +40,9 @@ struct TcMaps {
     CUtensorMap rq_wqkv[VUIB_MAX_LAYERS], rq_out[VUIB_MAX_LAYERS], rq_w1[VUIB_MAX_LAYERS], rq_w3[VUIB_MAX_LAYERS],
         rq_w2[VUIB_MAX_LAYERS];
     CUtensorMap codec_head, rq_proj, rq_head;
+    // un-swizzled maps whose box is one CTA's column slice of out_proj / w2 (fused single-row layers)
+    CUtensorMap f_out[VUIB_MAX_LAYERS], f_w2[VUIB_MAX_LAYERS], f_rq_out[VUIB_MAX_LAYERS], f_rq_w2[VUIB_MAX_LAYERS];
+    bool fused_backbone, fused_depth;
 };
 
 struct VuibEngine {
@@ -397,6 +402,20 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t co
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D bf16 row-major (rows, cols) tensor, dense boxes of box_rows x box_cols, no swizzle.
+static bool make_map_plain(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                           uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || box_rows > 256 || box_cols > 256) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static void build_tc_maps(VuibEngine* e) {
     delete e->tc;
     e->tc = nullptr;
@@ -421,8 +440,20 @@ static void build_tc_maps(VuibEngine* e) {
     ok = ok && make_map(&t->codec_head, e->w.codec_head, c.codebook_size, d, 64) &&
          make_map(&t->rq_proj, e->w.rq_backbone_proj, rd, d, 64) &&
          make_map(&t->rq_head, e->w.rq_head, (uint64_t)(c.n_quantizers - 1) * c.codebook_size, rd, 64);
-    if (ok) e->tc = t;
-    else delete t;
+    if (!ok) {
+        delete t;
+        return;
+    }
+    // fused single-row layers: shapes checked again where they are used
+    t->fused_backbone = c.d_model == 1024 && c.n_heads == 16 && c.n_kv_heads == 8 && c.ffn == 3072;
+    for (int i = 0; i < c.n_layers && t->fused_backbone; ++i)
+        t->fused_backbone = make_map_plain(&t->f_out[i], e->w.out_proj[i], d, d, d / FB_CL, 2 * HD) &&
+                            make_map_plain(&t->f_w2[i], e->w.w2[i], d, c.ffn, d / FB_CL, FB_MLP_U_BACKBONE * FB_CL);
+    t->fused_depth = rd == 512 && c.rq_n_heads == 8 && (c.rq_ffn == 1408 || c.rq_ffn == 1536);
+    for (int i = 0; i < c.rq_n_layers && t->fused_depth; ++i)
+        t->fused_depth = make_map_plain(&t->f_rq_out[i], e->w.rq_out_proj[i], rd, rd, rd / FB_CL, HD) &&
+                         make_map_plain(&t->f_rq_w2[i], e->w.rq_w2[i], rd, c.rq_ffn, rd / FB_CL, FB_MLP_U_DEPTH * FB_CL);
+    e->tc = t;
 }
 
 static bool tc_ok(VuibEngine* e, int M) {
@@ -646,13 +677,10 @@ static bool cluster_kernel_fits(void (*kern)(KArgs...), int n_clusters, int thre
     return n >= n_clusters;
 }
 
-constexpr int FB_MLP_TH_BACKBONE = 512, FB_MLP_U_BACKBONE = 32;
-constexpr int FB_MLP_TH_DEPTH = 256, FB_MLP_U_DEPTH = 16;
-
 static bool fused_backbone_ok(VuibEngine* e) {
     if (e->fused_backbone == 0) {
         const VuibConfig& c = e->cfg;
-        bool ok = c.d_model == 1024 && c.n_heads == 16 && c.n_kv_heads == 8 && c.ffn == 3072;
+        bool ok = e->tc && e->tc->fused_backbone;
         ok = ok && cluster_kernel_fits(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>));
         ok = ok && cluster_kernel_fits(k_mlp_block<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>,
                                        3072 / (FB_MLP_U_BACKBONE * FB_CL), FB_MLP_TH_BACKBONE,
@@ -665,7 +693,7 @@ static bool fused_backbone_ok(VuibEngine* e) {
 static bool fused_depth_ok(VuibEngine* e) {
     if (e->fused_depth == 0) {
         const VuibConfig& c = e->cfg;
-        bool ok = c.rq_d_model == 512 && c.rq_n_heads == 8 && (c.rq_ffn == 1408 || c.rq_ffn == 1536);
+        bool ok = e->tc && e->tc->fused_depth;
         ok = ok && cluster_kernel_fits(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>));
         if (ok && c.rq_ffn == 1408)
             ok = cluster_kernel_fits(k_mlp_block<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, 1408 / (FB_MLP_U_DEPTH * FB_CL),
@@ -725,7 +753,7 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
         aa.spin_limit = e->spin_limit;
         aa.next = prefetch_of(e->w.w1[li], ffn_bytes, e->w.w3[li], ffn_bytes, e->w.w2[li], ffn_bytes);
         if (env_off("VUIB_TRACE") && (li == 5 || li == 6)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 5) * 32;
-        CK(launch_cluster(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>), s, aa));
+        CK(launch_cluster(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>), s, e->tc->f_out[li], aa));
         e->launches++;
 
         MlpBlockArgs ma;
@@ -754,7 +782,7 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
                                       : prefetch_of(after, after_bytes);
         if (env_off("VUIB_TRACE") && (li == 5 || li == 6)) ma.dbg = wsp<unsigned long long>(e, L.trace) + (li - 5) * 32 + 16;
         CK(launch_cluster(k_mlp_block<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>, NCL, FB_MLP_TH_BACKBONE,
-                          sizeof(MlpBlockSmem<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>), s, ma));
+                          sizeof(MlpBlockSmem<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>), s, e->tc->f_w2[li], ma));
         e->launches++;
     }
     out->x = xb;
@@ -799,7 +827,7 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
         aa.spin_limit = e->spin_limit;
         aa.next = prefetch_of(e->w.rq_w1[li], ffn_bytes, e->w.rq_w3[li], ffn_bytes, e->w.rq_w2[li], ffn_bytes);
         if (env_off("VUIB_TRACE_DEPTH") && pos == 8 && (li == 1 || li == 2)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 1) * 32;
-        CK(launch_cluster(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>), s, aa));
+        CK(launch_cluster(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>), s, e->tc->f_rq_out[li], aa));
         e->launches++;
 
         MlpBlockArgs ma;
@@ -821,10 +849,10 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
         if (env_off("VUIB_TRACE_DEPTH") && pos == 8 && (li == 1 || li == 2)) ma.dbg = wsp<unsigned long long>(e, L.trace) + (li - 1) * 32 + 16;
         if (c.rq_ffn == 1408)
             CK(launch_cluster(k_mlp_block<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, ncl, FB_MLP_TH_DEPTH,
-                              sizeof(MlpBlockSmem<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>), s, ma));
+                              sizeof(MlpBlockSmem<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>), s, e->tc->f_rq_w2[li], ma));
         else
             CK(launch_cluster(k_mlp_block<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, ncl, FB_MLP_TH_DEPTH,
-                              sizeof(MlpBlockSmem<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>), s, ma));
+                              sizeof(MlpBlockSmem<512, 1536, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>), s, e->tc->f_rq_w2[li], ma));
         e->launches++;
     }
     out->x = xb;
