@@ -217,12 +217,22 @@ struct StageNorm {
                     uint4 u = __ldcg(reinterpret_cast<const uint4*>(xr + k));
                     unpack8(u, v[it]);
                     if (n_parts > 0) {
+                        // eight partial rows in flight at a time, added in row order
                         float sp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        for (int p = 0; p < n_parts; ++p) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * K + k));
-                            const float4 b = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * K + k + 4));
-                            sp[0] += a.x; sp[1] += a.y; sp[2] += a.z; sp[3] += a.w;
-                            sp[4] += b.x; sp[5] += b.y; sp[6] += b.z; sp[7] += b.w;
+                        for (int p0 = 0; p0 < n_parts; p0 += 8) {
+                            float4 pa[8], pb[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const bool ok = p0 + u < n_parts;
+                                const float* q = parts + (size_t)(ok ? p0 + u : p0) * K + k;
+                                pa[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                pb[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                sp[0] += pa[u].x; sp[1] += pa[u].y; sp[2] += pa[u].z; sp[3] += pa[u].w;
+                                sp[4] += pb[u].x; sp[5] += pb[u].y; sp[6] += pb[u].z; sp[7] += pb[u].w;
+                            }
                         }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) v[it][j] = rbf(v[it][j] + rbf(sp[j]));
@@ -958,11 +968,20 @@ static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restric
         for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
             float f[8], sp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             unpack8(__ldcg(reinterpret_cast<const uint4*>(xr + k)), f);
-            for (int p = 0; p < n_parts; ++p) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * d + k));
-                const float4 b = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)p * d + k + 4));
-                sp[0] += a.x; sp[1] += a.y; sp[2] += a.z; sp[3] += a.w;
-                sp[4] += b.x; sp[5] += b.y; sp[6] += b.z; sp[7] += b.w;
+            for (int p0 = 0; p0 < n_parts; p0 += 8) {  // eight rows in flight at a time, added in row order
+                float4 pa[8], pb[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const bool ok = p0 + u < n_parts;
+                    const float* q = parts + (size_t)(ok ? p0 + u : p0) * d + k;
+                    pa[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    pb[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    sp[0] += pa[u].x; sp[1] += pa[u].y; sp[2] += pa[u].z; sp[3] += pa[u].w;
+                    sp[4] += pb[u].x; sp[5] += pb[u].y; sp[6] += pb[u].z; sp[7] += pb[u].w;
+                }
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = rbf(f[j] + rbf(sp[j]));

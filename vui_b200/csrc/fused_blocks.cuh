@@ -200,6 +200,61 @@ __device__ __forceinline__ void dot_rows(const bf16* const (&wrow)[NR], const fl
     }
 }
 
+// NROWS dot products of weight rows in shared memory (row-major, K bf16 each, rows contiguous) with the
+// normed row xs (bf16) on the tensor cores: mma.sync m16n8k16, weight rows as the M side, K split over
+// the CTA's NW warps.  A dot product does not care in which order k is visited, so
+//  * a thread feeds two k-steps from ONE 16-byte load per row: the 8 consecutive elements
+//    [8t, 8t+8) of a 32-element block go to fragment positions {2t,2t+1 | 2t+8,2t+9} of step 0 and of
+//    step 1, and the same 8 elements of xs go to the B fragment;
+//  * row g of a tile visits the blocks of the warp's slice rotated by g, and column g of the B operand
+//    carries xs at that same block, so the two rows served in one shared-memory phase read different
+//    banks although their stride is a multiple of 128 bytes; row g's sum is then D[g][g].
+// Partial sums land in red[warp][row]; the caller adds them over the warps after a __syncthreads().
+template <int K, int NROWS, int NW>
+__device__ __forceinline__ void mma_rows(const bf16* rows, const bf16* xs, float* red, int warp, int lane) {
+    constexpr int NT = (NROWS + 15) / 16;      // 16-row tiles
+    constexpr int NBS = K / 32 / NW;           // 32-element blocks per warp
+    static_assert(K % (32 * NW) == 0 && NBS >= 2 && NBS % 2 == 0, "every warp takes an even number of blocks");
+    const int g = lane >> 2, t = lane & 3;
+    float d[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) d[i][0] = d[i][1] = d[i][2] = d[i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NBS; ++i) {
+        const int kb = (warp * NBS + ((i + g) % NBS)) * 32 + 8 * t;
+        const uint4 hb = *reinterpret_cast<const uint4*>(xs + kb);
+#pragma unroll
+        for (int tl = 0; tl < NT; ++tl) {
+            const int r0 = min(tl * 16 + g, NROWS - 1), r1 = min(tl * 16 + 8 + g, NROWS - 1);
+            const uint4 w0 = *reinterpret_cast<const uint4*>(rows + (size_t)r0 * K + kb);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(rows + (size_t)r1 * K + kb);
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(d[tl][0]), "+f"(d[tl][1]), "+f"(d[tl][2]), "+f"(d[tl][3])
+                         : "r"(w0.x), "r"(w1.x), "r"(w0.y), "r"(w1.y), "r"(hb.x), "r"(hb.y));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(d[tl][0]), "+f"(d[tl][1]), "+f"(d[tl][2]), "+f"(d[tl][3])
+                         : "r"(w0.z), "r"(w1.z), "r"(w0.w), "r"(w1.w), "r"(hb.z), "r"(hb.w));
+        }
+    }
+    if (t == (g >> 1)) {  // this thread holds D[g][g] and D[g+8][g] of every tile
+#pragma unroll
+        for (int tl = 0; tl < NT; ++tl) {
+            red[warp * (NT * 16) + tl * 16 + g] = (g & 1) ? d[tl][1] : d[tl][0];
+            red[warp * (NT * 16) + tl * 16 + 8 + g] = (g & 1) ? d[tl][3] : d[tl][2];
+        }
+    }
+}
+
+// Row r's total after mma_rows: the warps' partial sums in warp order.
+template <int NROWS, int NW>
+__device__ __forceinline__ float mma_row_total(const float* red, int r) {
+    constexpr int NT = (NROWS + 15) / 16;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) s += red[w * (NT * 16) + r];
+    return s;
+}
+
 // Sum NV values per lane over a group of lanes (xor offsets O, O/2, ..., 1) with the array halved at
 // every step while it has more than one entry: NV - 1 + (rounds left) shuffles instead of NV x rounds.
 // Afterwards a lane holds the total of ONE value: the halving round at offset o keeps the upper half of
@@ -328,15 +383,19 @@ struct AttnBlockSmem {
     alignas(16) float attn[G * HD];
     float s_new[G];
     float red[FB_WARPS];
+    float dots[FB_WARPS * ((NR + 15) / 16) * 16];  // per-warp partial sums of the q/k/v rows
     alignas(8) uint64_t bar;
 };
 
-template <int K, int G>
+// SHORT: the cache holds at most 16 positions (the depth transformer): every CTA attends over all of
+// them after the q/k/v exchange, which saves the second exchange.
+template <int K, int G, bool SHORT>
 __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_constant__ CUtensorMap map_wo, AttnBlockArgs a) {
     using S = AttnBlockSmem<K, G>;
+    static_assert(!SHORT || G == 1, "the short form handles one query head per cluster");
     constexpr int EPT = K / FB_THREADS;
     constexpr int QR = S::QR, KR = S::KR, OR = S::OR, OC = S::OC, NP = S::NP;
-    static_assert(NP <= 2 * FB_WARPS, "at most two row pairs per warp");
+    static_assert(NP * FB_CL <= FB_THREADS, "eight threads finish each row pair");
     extern __shared__ __align__(128) unsigned char fb_smem[];
     S& sm = *reinterpret_cast<S*>(fb_smem);
     cg::cluster_group cluster = cg::this_cluster();
@@ -386,9 +445,9 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
 
     // old keys [0, pos) split over the cluster's CTAs; this CTA's first FB_ATT_PRE blocks requested now
-    const int n_old = pos;
-    const int chunk = (n_old + FB_CL - 1) / FB_CL;
-    const int t_begin = rank * chunk, t_end = min(n_old, t_begin + chunk);
+    const int n_old = SHORT ? min(pos, 16) : pos;
+    const int chunk = SHORT ? n_old : (n_old + FB_CL - 1) / FB_CL;
+    const int t_begin = SHORT ? 0 : rank * chunk, t_end = min(n_old, t_begin + chunk);
     const int s8 = lane & 7, g4 = lane >> 3;
     const size_t pos_stride = (size_t)kvcols;
     const bf16* kb = a.k_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
@@ -396,7 +455,8 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     uint4 kr[FB_ATT_PRE], vr[FB_ATT_PRE];
 #pragma unroll
     for (int it = 0; it < FB_ATT_PRE; ++it) {
-        const int t = t_begin + it * 32 + warp * 4 + g4;
+        // SHORT: warp 0 alone takes all (<= 16) keys, four per pass
+        const int t = SHORT ? (warp == 0 ? it * 4 + g4 : t_end) : t_begin + it * 32 + warp * 4 + g4;
         if (t < t_end) {
             kr[it] = ldg_stream(kb + (size_t)t * pos_stride);
             vr[it] = ldg_stream(vb + (size_t)t * pos_stride);
@@ -405,11 +465,11 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
             vr[it] = make_uint4(0, 0, 0, 0);
         }
     }
-    // Each warp owns two interleaved row pairs (warp, warp + 8); after the reduction lanes 0-7 hold the
-    // first pair, lanes 16-23 the second.  RoPE factors of the lane's pair:
-    const int my_pair = warp + (lane >> 4) * FB_WARPS;
+    // After the tensor-core dot products eight threads finish each interleaved row pair, one per peer CTA.
+    // RoPE factors of the thread's pair:
+    const int my_pair = tid >> 3;
     const bool pair_live = my_pair < NP;
-    const int prow = 2 * (pair_live ? my_pair : warp);  // first local row of the pair
+    const int prow = 2 * (pair_live ? my_pair : 0);  // first local row of the pair
     const bool is_q = prow < QR, is_k = !is_q && prow < QR + KR;
     const int sub = is_q ? prow : (is_k ? prow - QR : prow - QR - KR);
     float c0 = 1.f, s0 = 0.f, c1 = 1.f, s1 = 0.f;
@@ -433,37 +493,28 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     cluster_wait();
     fb_stamp(a.dbg, 3);
 
-    // ---- q/k/v rows of this CTA: four rows per warp at once, results to every CTA of the cluster
-    {
-        float hf[K / 32];
-        load_h<K>(sm.xs, hf, lane);
-        const int p1 = warp + FB_WARPS < NP ? warp + FB_WARPS : warp;  // a warp without a second pair repeats its first
-        const bf16* rows[4] = {sm.w + (size_t)(2 * warp) * K, sm.w + (size_t)(2 * warp + 1) * K,
-                               sm.w + (size_t)(2 * p1) * K, sm.w + (size_t)(2 * p1 + 1) * K};
-        float acc[4];
-        dot_rows<K, 4>(rows, hf, lane, acc);
-        // lanes 0-7: row 0 of pair one, 8-15: row 1, 16-23: row 0 of pair two, 24-31: row 1
-        const float mine = rbf(GroupReduce<4, 16>::run(acc, lane));
-        const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-        if (pair_live && (lane & 8) == 0) {
-            float t0 = mine, t1 = other;
-            if (a.rope && (is_q || is_k)) {
-                // t*cos + rotate_half(t)*sin, each product and the sum rounded to bf16
-                const float o0 = rbf(rbf(t0 * c0) + rbf((-t1) * s0));
-                const float o1 = rbf(rbf(t1 * c1) + rbf(t0 * s1));
-                t0 = o0;
-                t1 = o1;
-            }
-            // place of the pair inside the head group's [q | k | v] vector; lane & 7 = the peer it goes to
-            const int idx = is_q ? rank * QR + sub : (is_k ? G * HD : G * HD + HD) + rank * KR + sub;
-            float* dst = cluster.map_shared_rank(sm.qkv, lane & 7);
-            *reinterpret_cast<float2*>(dst + idx) = make_float2(t0, t1);
-            if (!is_q && (lane & 7) == 0) {
-                bf16* cache = is_k ? a.k_cache : a.v_cache;
-                const int col = kvh * HD + rank * KR + sub;
-                *reinterpret_cast<__nv_bfloat162*>(cache + ((size_t)slot * a.max_seq + pos) * pos_stride + col) =
-                    __floats2bfloat162_rn(t0, t1);
-            }
+    // ---- q/k/v rows of this CTA on the tensor cores, results to every CTA of the cluster
+    mma_rows<K, S::NR, FB_WARPS>(sm.w, sm.xs, sm.dots, warp, lane);
+    __syncthreads();
+    if (pair_live) {
+        float t0 = rbf(mma_row_total<S::NR, FB_WARPS>(sm.dots, prow));
+        float t1 = rbf(mma_row_total<S::NR, FB_WARPS>(sm.dots, prow + 1));
+        if (a.rope && (is_q || is_k)) {
+            // t*cos + rotate_half(t)*sin, each product and the sum rounded to bf16
+            const float o0 = rbf(rbf(t0 * c0) + rbf((-t1) * s0));
+            const float o1 = rbf(rbf(t1 * c1) + rbf(t0 * s1));
+            t0 = o0;
+            t1 = o1;
+        }
+        // place of the pair inside the head group's [q | k | v] vector; tid & 7 = the peer it goes to
+        const int idx = is_q ? rank * QR + sub : (is_k ? G * HD : G * HD + HD) + rank * KR + sub;
+        float* dst = cluster.map_shared_rank(sm.qkv, tid & 7);
+        *reinterpret_cast<float2*>(dst + idx) = make_float2(t0, t1);
+        if (!is_q && (tid & 7) == 0) {
+            bf16* cache = is_k ? a.k_cache : a.v_cache;
+            const int col = kvh * HD + rank * KR + sub;
+            *reinterpret_cast<__nv_bfloat162*>(cache + ((size_t)slot * a.max_seq + pos) * pos_stride + col) =
+                __floats2bfloat162_rn(t0, t1);
         }
     }
     __syncthreads();
@@ -480,128 +531,189 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
         qf[h][0] = q0.x; qf[h][1] = q0.y; qf[h][2] = q0.z; qf[h][3] = q0.w;
         qf[h][4] = q1.x; qf[h][5] = q1.y; qf[h][6] = q1.z; qf[h][7] = q1.w;
     }
-    if (warp < G) {  // score of the new key (this step's own position), one warp per q head
-        const float* q = sm.qkv + warp * HD;
-        const float* kn = sm.qkv + G * HD;
-        float d = q[lane] * kn[lane] + q[lane + 32] * kn[lane + 32];
-        d = warp_sum(d);
-        if (lane == 0) sm.s_new[warp] = d * 0.125f;
-    }
-    float m[G], l[G], acc[G][8];
+    if constexpr (SHORT) {
+        if (warp == 0) {
+            float m = NEG_BIG, l = 0.f, acc[8];
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        m[h] = NEG_BIG;
-        l[h] = 0.f;
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
-    }
-    auto consume = [&](const uint4& kraw, const uint4& vraw, bool ok) {
-        float kf[8], vf[8];
-        unpack8(kraw, kf);
-        unpack8(vraw, vf);
+            for (int it = 0; it < FB_ATT_PRE; ++it) {
+                if (it * 4 < t_end) {  // uniform over the warp
+                    float kf[8], vf[8];
+                    unpack8(kr[it], kf);
+                    unpack8(vr[it], vf);
+                    float d = 0.f;
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
+                    for (int j = 0; j < 8; ++j) d = fmaf(qf[0][j], kf[j], d);
+                    d += __shfl_xor_sync(0xffffffffu, d, 1);
+                    d += __shfl_xor_sync(0xffffffffu, d, 2);
+                    d += __shfl_xor_sync(0xffffffffu, d, 4);
+                    if (it * 4 + g4 < t_end) {
+                        const float sc = d * 0.125f;
+                        const float mn = fmaxf(m, sc);
+                        const float corr = __expf(m - mn), p = __expf(sc - mn);
+                        l = l * corr + p;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(p, vf[j], acc[j] * corr);
+                        m = mn;
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 8; o <= 16; o <<= 1) {
+                const float mo = __shfl_xor_sync(0xffffffffu, m, o);
+                const float lo = __shfl_xor_sync(0xffffffffu, l, o);
+                float ao[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ao[j] = __shfl_xor_sync(0xffffffffu, acc[j], o);
+                softmax_merge(m, l, acc, mo, lo, ao);
+            }
+            // the new key (this step's own position) from the exchanged vector
+            const float* kn = sm.qkv + G * HD + s8 * 8;
+            const float* vn = sm.qkv + G * HD + HD + s8 * 8;
             float d = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) d = fmaf(qf[h][j], kf[j], d);
+            for (int j = 0; j < 8; ++j) d = fmaf(qf[0][j], kn[j], d);
             d += __shfl_xor_sync(0xffffffffu, d, 1);
             d += __shfl_xor_sync(0xffffffffu, d, 2);
             d += __shfl_xor_sync(0xffffffffu, d, 4);
-            if (ok) {
-                const float sc = d * 0.125f;
-                const float mn = fmaxf(m[h], sc);
-                const float corr = __expf(m[h] - mn), p = __expf(sc - mn);
-                l[h] = l[h] * corr + p;
+            const float sc = d * 0.125f;
+            const float mn = fmaxf(m, sc);
+            const float corr = __expf(m - mn), p = __expf(sc - mn);
+            l = l * corr + p;
+            if (g4 == 0) {
+                const float inv = 1.f / l;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(p, vf[j], acc[h][j] * corr);
-                m[h] = mn;
+                for (int j = 0; j < 8; ++j) sm.attn[s8 * 8 + j] = rbf(fmaf(p, vn[j], acc[j] * corr) * inv);
             }
         }
-    };
-#pragma unroll
-    for (int it = 0; it < FB_ATT_PRE; ++it) {
-        if (t_begin + it * 32 < t_end) {  // uniform over the CTA
-            const int t = t_begin + it * 32 + warp * 4 + g4;
-            consume(kr[it], vr[it], t < t_end);
+        __syncthreads();
+        fb_stamp(a.dbg, 12);
+    } else {
+        if (warp < G) {  // score of the new key (this step's own position), one warp per q head
+            const float* q = sm.qkv + warp * HD;
+            const float* kn = sm.qkv + G * HD;
+            float d = q[lane] * kn[lane] + q[lane + 32] * kn[lane + 32];
+            d = warp_sum(d);
+            if (lane == 0) sm.s_new[warp] = d * 0.125f;
         }
-    }
-    for (int tb = t_begin + FB_ATT_PRE * 32; tb < t_end; tb += 32) {  // longer caches: the rest, block by block
-        const int t = tb + warp * 4 + g4;
-        const bool ok = t < t_end;
-        const uint4 kraw = ok ? ldg_stream(kb + (size_t)t * pos_stride) : make_uint4(0, 0, 0, 0);
-        const uint4 vraw = ok ? ldg_stream(vb + (size_t)t * pos_stride) : make_uint4(0, 0, 0, 0);
-        consume(kraw, vraw, ok);
-    }
-    // merge the warp's 4 key groups, then the CTA's 8 warps
-#pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
-#pragma unroll
+        float m[G], l[G], acc[G][8];
+    #pragma unroll
         for (int h = 0; h < G; ++h) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
-            const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
-            float ao[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ao[j] = __shfl_xor_sync(0xffffffffu, acc[h][j], o);
-            softmax_merge(m[h], l[h], acc[h], mo, lo, ao);
+            m[h] = NEG_BIG;
+            l[h] = 0.f;
+    #pragma unroll
+            for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
         }
-    }
-    if (g4 == 0) {
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sm.wpart[warp][h][s8][j] = acc[h][j];
-            sm.wpart[warp][h][s8][8] = m[h];
-            sm.wpart[warp][h][s8][9] = l[h];
-        }
-    }
-    __syncthreads();
-    fb_stamp(a.dbg, 10);
-    const int th = tid >> 6, tdim = tid & 63;  // thread (q head, dim) for tid < G * 64
-    if (tid < G * HD) {
-        const int ds = tdim >> 3, dj = tdim & 7;
-        float M_ = NEG_BIG;
-#pragma unroll
-        for (int w = 0; w < FB_WARPS; ++w) M_ = fmaxf(M_, sm.wpart[w][th][ds][8]);
-        float L_ = 0.f, O_ = 0.f;
-#pragma unroll
-        for (int w = 0; w < FB_WARPS; ++w) {
-            const float c = __expf(sm.wpart[w][th][ds][8] - M_);
-            L_ += sm.wpart[w][th][ds][9] * c;
-            O_ += sm.wpart[w][th][ds][dj] * c;
-        }
-#pragma unroll
-        for (int c = 0; c < FB_CL; ++c) {
-            float* dst = cluster.map_shared_rank(&sm.part[0][0][0], c) + (rank * G + th) * (HD + 2);
-            dst[tdim] = O_;
-            if (tdim == 0) {
-                dst[HD] = M_;
-                dst[HD + 1] = L_;
+        auto consume = [&](const uint4& kraw, const uint4& vraw, bool ok) {
+            float kf[8], vf[8];
+            unpack8(kraw, kf);
+            unpack8(vraw, vf);
+    #pragma unroll
+            for (int h = 0; h < G; ++h) {
+                float d = 0.f;
+    #pragma unroll
+                for (int j = 0; j < 8; ++j) d = fmaf(qf[h][j], kf[j], d);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (ok) {
+                    const float sc = d * 0.125f;
+                    const float mn = fmaxf(m[h], sc);
+                    const float corr = __expf(m[h] - mn), p = __expf(sc - mn);
+                    l[h] = l[h] * corr + p;
+    #pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(p, vf[j], acc[h][j] * corr);
+                    m[h] = mn;
+                }
+            }
+        };
+    #pragma unroll
+        for (int it = 0; it < FB_ATT_PRE; ++it) {
+            if (t_begin + it * 32 < t_end) {  // uniform over the CTA
+                const int t = t_begin + it * 32 + warp * 4 + g4;
+                consume(kr[it], vr[it], t < t_end);
             }
         }
-    }
-    __syncthreads();
-    fb_stamp(a.dbg, 11);
-    cluster.sync();
-    fb_stamp(a.dbg, 5);
-    if (tid < G * HD) {
-        // every CTA merges the partial states in CTA order, then the new key: same bits everywhere
-        float Mx = sm.s_new[th];
-#pragma unroll
-        for (int c = 0; c < FB_CL; ++c) Mx = fmaxf(Mx, sm.part[c][th][HD]);
-        float Ls = 0.f, Os = 0.f;
-#pragma unroll
-        for (int c = 0; c < FB_CL; ++c) {
-            const float e = __expf(sm.part[c][th][HD] - Mx);
-            Ls += sm.part[c][th][HD + 1] * e;
-            Os += sm.part[c][th][tdim] * e;
+        for (int tb = t_begin + FB_ATT_PRE * 32; tb < t_end; tb += 32) {  // longer caches: the rest, block by block
+            const int t = tb + warp * 4 + g4;
+            const bool ok = t < t_end;
+            const uint4 kraw = ok ? ldg_stream(kb + (size_t)t * pos_stride) : make_uint4(0, 0, 0, 0);
+            const uint4 vraw = ok ? ldg_stream(vb + (size_t)t * pos_stride) : make_uint4(0, 0, 0, 0);
+            consume(kraw, vraw, ok);
         }
-        const float en = __expf(sm.s_new[th] - Mx);
-        Ls += en;
-        Os += en * sm.qkv[G * HD + HD + tdim];
-        sm.attn[th * HD + tdim] = rbf(Os / Ls);
+        // merge the warp's 4 key groups, then the CTA's 8 warps
+    #pragma unroll
+        for (int o = 8; o <= 16; o <<= 1) {
+    #pragma unroll
+            for (int h = 0; h < G; ++h) {
+                const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
+                const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+                float ao[8];
+    #pragma unroll
+                for (int j = 0; j < 8; ++j) ao[j] = __shfl_xor_sync(0xffffffffu, acc[h][j], o);
+                softmax_merge(m[h], l[h], acc[h], mo, lo, ao);
+            }
+        }
+        if (g4 == 0) {
+    #pragma unroll
+            for (int h = 0; h < G; ++h) {
+    #pragma unroll
+                for (int j = 0; j < 8; ++j) sm.wpart[warp][h][s8][j] = acc[h][j];
+                sm.wpart[warp][h][s8][8] = m[h];
+                sm.wpart[warp][h][s8][9] = l[h];
+            }
+        }
+        __syncthreads();
+        fb_stamp(a.dbg, 10);
+        const int th = tid >> 6, tdim = tid & 63;  // thread (q head, dim) for tid < G * 64
+        if (tid < G * HD) {
+            const int ds = tdim >> 3, dj = tdim & 7;
+            float M_ = NEG_BIG;
+    #pragma unroll
+            for (int w = 0; w < FB_WARPS; ++w) M_ = fmaxf(M_, sm.wpart[w][th][ds][8]);
+            float L_ = 0.f, O_ = 0.f;
+    #pragma unroll
+            for (int w = 0; w < FB_WARPS; ++w) {
+                const float c = __expf(sm.wpart[w][th][ds][8] - M_);
+                L_ += sm.wpart[w][th][ds][9] * c;
+                O_ += sm.wpart[w][th][ds][dj] * c;
+            }
+    #pragma unroll
+            for (int c = 0; c < FB_CL; ++c) {
+                float* dst = cluster.map_shared_rank(&sm.part[0][0][0], c) + (rank * G + th) * (HD + 2);
+                dst[tdim] = O_;
+                if (tdim == 0) {
+                    dst[HD] = M_;
+                    dst[HD + 1] = L_;
+                }
+            }
+        }
+        __syncthreads();
+        fb_stamp(a.dbg, 11);
+        cluster.sync();
+        fb_stamp(a.dbg, 5);
+        if (tid < G * HD) {
+            // every CTA merges the partial states in CTA order, then the new key: same bits everywhere
+            float Mx = sm.s_new[th];
+    #pragma unroll
+            for (int c = 0; c < FB_CL; ++c) Mx = fmaxf(Mx, sm.part[c][th][HD]);
+            float Ls = 0.f, Os = 0.f;
+    #pragma unroll
+            for (int c = 0; c < FB_CL; ++c) {
+                const float e = __expf(sm.part[c][th][HD] - Mx);
+                Ls += sm.part[c][th][HD + 1] * e;
+                Os += sm.part[c][th][tdim] * e;
+            }
+            const float en = __expf(sm.s_new[th] - Mx);
+            Ls += en;
+            Os += en * sm.qkv[G * HD + HD + tdim];
+            sm.attn[th * HD + tdim] = rbf(Os / Ls);
+        }
+        __syncthreads();
+        fb_stamp(a.dbg, 12);
+
     }
-    __syncthreads();
-    fb_stamp(a.dbg, 12);
 
     // ---- this head group's K-slice of out_proj for the CTA's rows
     small_matvec<OC, OR / FB_WARPS>(sm.wo, sm.attn, warp * (OR / FB_WARPS), a.parts_out + (size_t)kvh * K + rank * OR, lane);
@@ -643,11 +755,11 @@ struct MlpBlockSmem {
     static constexpr int NCL = F / CU;       // clusters
     static_assert(F % CU == 0 && CU % 8 == 0, "ffn must split evenly into 16-byte pieces");
     alignas(128) bf16 w2[OR * CU];           // destination of a tiled copy: first, 128-byte aligned
-    alignas(16) bf16 w1[U * K];
-    alignas(16) bf16 w3[U * K];
+    alignas(16) bf16 w13[2 * U * K];         // w1 rows of this CTA's units, then their w3 rows
     alignas(16) bf16 xs[K];
     alignas(16) float g[CU];
     float red[TH / 32];
+    float dots[(TH / 32) * ((2 * U + 15) / 16) * 16];  // per-warp partial sums of the w1 / w3 rows
     alignas(8) uint64_t bar;
 };
 
@@ -674,8 +786,8 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + OR * CU * 2));
             const size_t u0 = (size_t)cid * CU + rank * U;
-            bulk_g2s(sm.w1, a.w1 + u0 * K, U * K * 2, &sm.bar);
-            bulk_g2s(sm.w3, a.w3 + u0 * K, U * K * 2, &sm.bar);
+            bulk_g2s(sm.w13, a.w1 + u0 * K, U * K * 2, &sm.bar);
+            bulk_g2s(sm.w13 + U * K, a.w3 + u0 * K, U * K * 2, &sm.bar);
             // the w2 slice (OR rows x CU columns) as ONE tiled copy
             tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
         }
@@ -714,26 +826,17 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
     cluster_wait();
     fb_stamp(a.dbg, 3);
 
-    // ---- SiLU(w1 h) * (w3 h) for this CTA's hidden units, two units (four rows) per warp at once,
-    //      sent to every CTA of the cluster
-    {
-        static_assert(U % 2 == 0, "units are taken in pairs");
-        float hf[K / 32];
-        load_h<K>(sm.xs, hf, lane);
-        for (int u0 = 2 * warp; u0 < U; u0 += 2 * NWARP) {
-            const bf16* rows[4] = {sm.w1 + (size_t)u0 * K, sm.w3 + (size_t)u0 * K, sm.w1 + (size_t)(u0 + 1) * K,
-                                   sm.w3 + (size_t)(u0 + 1) * K};
-            float acc[4];
-            dot_rows<K, 4>(rows, hf, lane, acc);
-            // lanes 0-7: w1 sum of unit u0, 8-15: its w3 sum, 16-23 / 24-31: the same for unit u0 + 1
-            const float mine = rbf(GroupReduce<4, 16>::run(acc, lane));
-            const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-            if ((lane & 8) == 0) {
-                const float sl = rbf(mine / (1.0f + expf(-mine)));
-                const float gv = rbf(sl * other);
-                cluster.map_shared_rank(sm.g, lane & 7)[rank * U + u0 + (lane >> 4)] = gv;
-            }
-        }
+    // ---- SiLU(w1 h) * (w3 h) for this CTA's hidden units: rows on the tensor cores, then eight threads
+    //      per unit, one per peer CTA
+    static_assert(U * FB_CL <= TH, "eight threads finish each hidden unit");
+    mma_rows<K, 2 * U, NWARP>(sm.w13, sm.xs, sm.dots, warp, lane);
+    __syncthreads();
+    if (tid < U * FB_CL) {
+        const int u = tid >> 3;
+        const float a1 = rbf(mma_row_total<2 * U, NWARP>(sm.dots, u));
+        const float a3 = rbf(mma_row_total<2 * U, NWARP>(sm.dots, U + u));
+        const float sl = rbf(a1 / (1.0f + expf(-a1)));
+        cluster.map_shared_rank(sm.g, tid & 7)[rank * U + u] = rbf(sl * a3);
     }
     __syncthreads();
     fb_stamp(a.dbg, 9);

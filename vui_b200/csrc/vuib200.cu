@@ -681,7 +681,7 @@ static bool fused_backbone_ok(VuibEngine* e) {
     if (e->fused_backbone == 0) {
         const VuibConfig& c = e->cfg;
         bool ok = e->tc && e->tc->fused_backbone;
-        ok = ok && cluster_kernel_fits(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>));
+        ok = ok && cluster_kernel_fits(k_attn_block<1024, 2, false>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>));
         ok = ok && cluster_kernel_fits(k_mlp_block<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>,
                                        3072 / (FB_MLP_U_BACKBONE * FB_CL), FB_MLP_TH_BACKBONE,
                                        sizeof(MlpBlockSmem<1024, 3072, FB_MLP_U_BACKBONE, FB_MLP_TH_BACKBONE>));
@@ -694,7 +694,7 @@ static bool fused_depth_ok(VuibEngine* e) {
     if (e->fused_depth == 0) {
         const VuibConfig& c = e->cfg;
         bool ok = e->tc && e->tc->fused_depth;
-        ok = ok && cluster_kernel_fits(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>));
+        ok = ok && cluster_kernel_fits(k_attn_block<512, 1, true>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>));
         if (ok && c.rq_ffn == 1408)
             ok = cluster_kernel_fits(k_mlp_block<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>, 1408 / (FB_MLP_U_DEPTH * FB_CL),
                                      FB_MLP_TH_DEPTH, sizeof(MlpBlockSmem<512, 1408, FB_MLP_U_DEPTH, FB_MLP_TH_DEPTH>));
@@ -753,7 +753,7 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
         aa.spin_limit = e->spin_limit;
         aa.next = prefetch_of(e->w.w1[li], ffn_bytes, e->w.w3[li], ffn_bytes, e->w.w2[li], ffn_bytes);
         if (env_off("VUIB_TRACE") && (li == 5 || li == 6)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 5) * 32;
-        CK(launch_cluster(k_attn_block<1024, 2>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>), s, e->tc->f_out[li], aa));
+        CK(launch_cluster(k_attn_block<1024, 2, false>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>), s, e->tc->f_out[li], aa));
         e->launches++;
 
         MlpBlockArgs ma;
@@ -827,7 +827,7 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
         aa.spin_limit = e->spin_limit;
         aa.next = prefetch_of(e->w.rq_w1[li], ffn_bytes, e->w.rq_w3[li], ffn_bytes, e->w.rq_w2[li], ffn_bytes);
         if (env_off("VUIB_TRACE_DEPTH") && pos == 8 && (li == 1 || li == 2)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 1) * 32;
-        CK(launch_cluster(k_attn_block<512, 1>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>), s, e->tc->f_rq_out[li], aa));
+        CK(launch_cluster(k_attn_block<512, 1, true>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>), s, e->tc->f_rq_out[li], aa));
         e->launches++;
 
         MlpBlockArgs ma;
