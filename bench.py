@@ -4,16 +4,26 @@
 
 A step is one decode frame for every stream of the batch (backbone step, cb0
 sampling, 15 depth-transformer codebooks, gather-sum into the next frame's
-input), i.e. one replay of the captured frame graph.  Default workload is
-benchmark configuration 2: one stream, 256 seeded text ids, greedy decode, KV up to 1024
-positions; weights are seeded random-init (no checkpoint is available offline).
+input), i.e. one replay of the captured frame graph.  The headline workload is
+benchmark configuration 2: one stream, 256 seeded text ids, greedy decode, KV up to
+1024 positions; weights are seeded random-init (no checkpoint is available offline).
+The K-step timed block is repeated (the stream is rewound in between, so every block
+covers the same KV lengths) and the median block is reported.
+
+Beside the headline the same line carries
+  streams64   configuration 3: 64 streams, prompts U[64,512], T=0.8 top-k 50;
+  cfg4        configuration 4: 16 streams x (128 text ids + 125 codec frames): prefill
+              tokens/s, time to first frame, 375 greedy frames;
+  streams256  configuration 5's per-GPU shape: 256 streams, 512-id prompts, 2048-position KV.
 
 Under torchrun (N > 1) every rank is an independent replica with its own streams
 on its own GPU; there is no data-path collective, the process group only aligns
 the timed window and takes the max time over ranks.
 
 `--impl reference` times the CPU restatement of the reference's PyTorch path
-(oracle/, fp32, all host threads) on the same metric.
+(oracle/, fp32, all host threads) on the same metric.  `--profile-frames N` runs N
+frames kernel by kernel (no graph) and exits: the command the ncu summaries under
+profiles/ are taken with.
 """
 
 from __future__ import annotations
@@ -21,6 +31,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -52,7 +63,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -86,16 +97,7 @@ def measured_hbm_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-# DRAM bytes per frame (dram__bytes_read.sum + dram__bytes_write.sum over the launches of one frame)
-# from the ncu capture summarised in profiles/frame_graph_b1_dram_traffic.md.
-NCU_TRAFFIC_BYTES_PER_FRAME = {1: 945989120}
-
-
-def ncu_traffic():
-    return {f"B{b}": v for b, v in NCU_TRAFFIC_BYTES_PER_FRAME.items()}
-
-
-def cpu_oracle_frames_per_s(prompt_len: int, n_frames: int, threads: int):
+def cpu_oracle_frame_times(prompt_len: int, n_frames: int, threads: int):
     """Reference path on the host cores: the fp32 restatement in oracle/, greedy."""
     import torch
     from oracle.vui_oracle import Oracle, OracleConfig, init_weights
@@ -123,10 +125,8 @@ def run_reference(args):
     rank, _, world = _dist_env()
     if rank != 0:
         return
-    import torch
-
     threads = os.cpu_count() or 1
-    times = cpu_oracle_frames_per_s(args.prompt_len, args.warmup + args.steps, threads)[args.warmup:]
+    times = cpu_oracle_frame_times(args.prompt_len, args.warmup + args.steps, threads)[args.warmup:]
     total = sum(times)
     fps = len(times) / total
     line = {
@@ -145,124 +145,250 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def measure(model, dev, rank, world, B, K, W, prompt_len, ragged, sample, max_seq_arg, phases=True):
-    """Prefill B streams, then time K frames device-resident and K frames end to end."""
-    import torch
-    import torch.distributed as dist
+class Bench:
+    def __init__(self, model, dev, rank, world):
+        self.model, self.dev, self.rank, self.world = model, dev, rank, world
 
-    from vui_b200 import Engine, GenConfig
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
 
-    shape = model.shape
-    ceiling = shape.max_seq_len
-    K = min(K, (ceiling - 513 - 2 * W - 40) // 2)  # both timed loops must fit the trained context
-    plen = 512 if ragged else prompt_len
-    max_seq = max_seq_arg or 64 * ((plen + 2 * (K + W) + 16 + 63) // 64 + 1)
-    max_seq = max(max_seq, 1024) if B == 1 else max_seq
-    eng = Engine(model=model, max_rows=B, max_seq=min(max_seq, model.decoder.max_seqlen), seed=1234 + rank)
-    gen = torch.Generator().manual_seed(100 + rank)
-    if ragged:
-        lens = torch.randint(64, 513, (B,), generator=torch.Generator().manual_seed(1)).tolist()
-    else:
-        lens = [prompt_len] * B
-    rows = [eng.new_row() for _ in range(B)]
-    embs = [(r, model.token_emb(torch.randint(0, shape.vocab_size, (1, n), generator=gen))) for r, n in zip(rows, lens)]
-    torch.cuda.synchronize(dev)
-    t_pref0 = time.perf_counter()
-    hs = eng._prefill_many(embs)
-    torch.cuda.synchronize(dev)
-    prefill_s = time.perf_counter() - t_pref0
-    hidden = torch.stack([h[-1] for h in hs])
-    cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.0)
-    greedy = not sample
-    eng._apply_cfg(cfg, greedy=greedy)
-    eng._g_slot_idx[:B] = torch.tensor([r.idx for r in rows], device=dev, dtype=torch.int32)
-    eng._g_seq_inc[:B].fill_(1)
-    eng._g_codes_in[:B] = eng._first_frames(rows, hidden)
-    launches0 = eng.launch_count()
-    graph = eng._frame_graph(B)
-    launches_per_frame = (eng.launch_count() - launches0) // 2  # one warm-up + one captured call
-
-    def barrier():
-        torch.cuda.synchronize(dev)
-        if world > 1:
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
             dist.barrier()
+        torch.cuda.synchronize(self.dev)
+
+    def aggregate(self, units, ms):
+        from vui_b200.replicas import aggregate_rate
+
+        return aggregate_rate(units, ms, self.dev)
+
+    # ------------------------------------------------------------------ decode
+    def decode(self, B, K, W, reps, prompt_lens, sample, max_seq, clocks=False, e2e=True, phases=False):
+        """Prefill B streams, then time `reps` blocks of K frames device-resident (median block) and
+        K frames end to end through host buffers."""
+        import torch
+
+        from vui_b200 import Engine, GenConfig
+
+        model, dev = self.model, self.dev
+        shape = model.shape
+        eng = Engine(model=model, max_rows=B, max_seq=max_seq, max_prefill_rows=1024, seed=1234 + self.rank)
+        gen = torch.Generator().manual_seed(100 + self.rank)
+        rows = [eng.new_row() for _ in range(B)]
+        embs = [(r, model.token_emb(torch.randint(0, shape.vocab_size, (1, n), generator=gen)))
+                for r, n in zip(rows, prompt_lens)]
         torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        hs = eng._prefill_many(embs)
+        torch.cuda.synchronize(dev)
+        prefill_first_s = time.perf_counter() - t0
+        hidden = torch.stack([h[-1] for h in hs])
+        cfg = GenConfig(temperature=0.8, top_k=50, rep_penalty=1.0)
+        eng._apply_cfg(cfg, greedy=not sample)
+        eng._g_slot_idx[:B] = torch.tensor([r.idx for r in rows], device=dev, dtype=torch.int32)
+        eng._g_seq_inc[:B].fill_(1)
+        eng._g_codes_in[:B] = eng._first_frames(rows, hidden)
+        launches0 = eng.launch_count()
+        graph = eng._frame_graph(B)
+        launches_per_frame = (eng.launch_count() - launches0) // 2  # one warm-up + one captured call
 
-    # ---- device-resident timing: K replays between CUDA events ------------------
-    for _ in range(W):
-        graph.replay()
-    seq_after_warm = eng.seq_lens.clone()
-    codes_after_warm = eng._g_codes_in.clone()
-    sampler = ClockSampler(dev.index or 0)
-    barrier()
-    sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(K):
-        graph.replay()
-    ev1.record()
-    barrier()
-    clocks = sampler.stop()
-    ms = ev0.elapsed_time(ev1)
-    eng.check_device()
-    mean_T = float(sum(lens)) / B + W + K / 2.0
-
-    # ---- end to end: host-driven loop, codes H2D + replay + codes/EOS D2H per frame ----
-    eng.seq_lens.copy_(seq_after_warm)
-    eng._g_codes_in.copy_(codes_after_warm)
-    h_in = eng._g_codes_in[:B].cpu().pin_memory()
-    lat = []
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        t1 = time.perf_counter()
-        eng._g_codes_in[:B].copy_(h_in, non_blocking=True)
-        graph.replay()
-        h_codes, h_eos = eng._read_frame(B)
-        h_in.copy_(h_codes)
-        lat.append(time.perf_counter() - t1)
-    torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
-    lat.sort()
-
-    # ---- phase split (eager, events): backbone step vs depth step ---------------
-    eng.seq_lens.copy_(seq_after_warm)
-    phase = {}
-    if rank == 0 and phases:
-        P = lambda t: __import__("ctypes").c_void_p(t.data_ptr())  # noqa: E731
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        reps = 10
-        tb = td = 0.0
+        for _ in range(W):
+            graph.replay()
+        seq0 = eng.seq_lens.clone()
+        codes0 = eng._g_codes_in.clone()
+        sampler = ClockSampler(dev.index or 0) if clocks else None
+        if sampler:
+            sampler.start()
+        block_ms = []
         for _ in range(reps):
-            e0.record()
-            eng._ck(eng._lib.vuib_backbone_step(eng._handle, B, P(eng._g_slot_idx), P(eng._g_seq_inc),
-                                                P(eng._g_codes_in), P(eng._g_hidden_out), P(eng._g_cb0_out),
-                                                P(eng._g_eos_out), eng._stream))
-            e1.record()
-            eng._ck(eng._lib.vuib_depth_step(eng._handle, B, P(eng._g_slot_idx), P(eng._g_hidden_out),
-                                             P(eng._g_cb0_out), P(eng._g_eos_out), 0, P(eng._g_codes_in),
-                                             P(eng._g_eos_prob), eng._stream))
-            e2.record()
+            eng.seq_lens.copy_(seq0)
+            eng._g_codes_in.copy_(codes0)
+            self.barrier()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for _ in range(K):
+                graph.replay()
+            ev1.record()
+            self.barrier()
+            block_ms.append(ev0.elapsed_time(ev1))
+        clk = sampler.stop() if sampler else None
+        eng.check_device()
+        ms = statistics.median(block_ms)
+        mean_T = float(sum(prompt_lens)) / B + W + K / 2.0
+
+        # end to end: host-driven loop, codes H2D + replay + codes/EOS D2H every frame
+        lat, e2e_ms = [], None
+        if e2e:
+            e2e_blocks = []
+            for _ in range(max(1, min(reps, 5))):
+                eng.seq_lens.copy_(seq0)
+                eng._g_codes_in.copy_(codes0)
+                h_in = eng._g_codes_in[:B].cpu().pin_memory()
+                self.barrier()
+                t0 = time.perf_counter()
+                for _ in range(K):
+                    t1 = time.perf_counter()
+                    eng._g_codes_in[:B].copy_(h_in, non_blocking=True)
+                    graph.replay()
+                    h_codes, h_eos = eng._read_frame(B)
+                    h_in.copy_(h_codes)
+                    lat.append(time.perf_counter() - t1)
+                torch.cuda.synchronize(dev)
+                e2e_blocks.append((time.perf_counter() - t0) * 1e3)
+            e2e_ms = statistics.median(e2e_blocks)
+            lat.sort()
+
+        phase = {}
+        if phases and self.rank == 0:
+            import ctypes as C
+
+            P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+            eng.seq_lens.copy_(seq0)
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            tb = td = 0.0
+            n = 10
+            for _ in range(n):
+                e0.record()
+                eng._ck(eng._lib.vuib_backbone_step(eng._handle, B, P(eng._g_slot_idx), P(eng._g_seq_inc),
+                                                    P(eng._g_codes_in), P(eng._g_hidden_out), P(eng._g_cb0_out),
+                                                    P(eng._g_eos_out), eng._stream))
+                e1.record()
+                eng._ck(eng._lib.vuib_depth_step(eng._handle, B, P(eng._g_slot_idx), P(eng._g_hidden_out),
+                                                 P(eng._g_cb0_out), P(eng._g_eos_out), 0, P(eng._g_codes_in),
+                                                 P(eng._g_eos_prob), eng._stream))
+                e2.record()
+                torch.cuda.synchronize(dev)
+                tb += e0.elapsed_time(e1)
+                td += e1.elapsed_time(e2)
+            phase = {"backbone_ms_eager": tb / n, "depth_ms_eager": td / n}
+
+        fps, ms_max = self.aggregate(B * K, ms)
+        e2e_fps = self.aggregate(B * K, e2e_ms)[0] if e2e_ms else None
+        w_bytes = model.weight_bytes_per_step()
+        step_bytes = w_bytes + B * (GATHER_BYTES_PER_STREAM + KV_BYTES_PER_POS * (mean_T + 1))
+        res = {
+            "B": B, "K": K, "reps": reps, "fps": fps, "e2e_fps": e2e_fps, "ms_per_step": ms_max / K,
+            "block_ms_min": min(block_ms), "block_ms_max": max(block_ms), "lat": lat, "mean_T": mean_T,
+            "max_seq": eng.max_seq, "prefill_first_s": prefill_first_s, "prefill_tokens": int(sum(prompt_lens)),
+            "launches_per_frame": launches_per_frame, "step_bytes": step_bytes, "phase": phase, "clocks": clk,
+            "greedy": not sample,
+        }
+        del graph, eng
+        torch.cuda.empty_cache()
+        return res
+
+    # ------------------------------------------------------------------- cfg 4
+    def voice_clone(self, n_streams=16, n_text=128, n_frames_prompt=125, n_decode=375):
+        """Configuration 4: every prompt is 128 text ids followed by 125 codec frames; batched prefill
+        (tcgen05 GEMMs), then greedy frames.  Reports prefill tokens/s (first call and warm) and the
+        time to the first frame on the host."""
+        import torch
+
+        from vui_b200 import Engine
+
+        model, dev = self.model, self.dev
+        eng = Engine(model=model, max_rows=n_streams, max_seq=640, max_prefill_rows=4096, seed=77 + self.rank)
+        g = torch.Generator().manual_seed(400 + self.rank)
+        ids = [torch.randint(0, model.shape.vocab_size, (1, n_text), generator=g) for _ in range(n_streams)]
+        codes = [torch.randint(0, model.shape.codebook_size, (n_frames_prompt, model.shape.n_quantizers), generator=g)
+                 for _ in range(n_streams)]
+        h_ids = [t.pin_memory() for t in ids]
+        h_codes = [t.pin_memory() for t in codes]
+        eng._apply_cfg(None, greedy=True)
+
+        def prefill_and_first_frame():
+            """From host buffers to the first frame's codes back on the host."""
+            rows = list(eng._rows.values())
+            t0 = time.perf_counter()
+            items = []
+            for r, i_, c_ in zip(rows, h_ids, h_codes):
+                items.append((r, model.token_emb(i_.to(dev, non_blocking=True))))
+                items.append((r, eng._audio_emb(c_.to(dev, non_blocking=True))))
+            outs = eng._prefill_many(items)
             torch.cuda.synchronize(dev)
-            tb += e0.elapsed_time(e1)
-            td += e1.elapsed_time(e2)
-        phase = {"backbone_ms_eager": tb / reps, "depth_ms_eager": td / reps}
+            t_prefill = time.perf_counter() - t0
+            hidden = torch.stack([outs[2 * i + 1][-1] for i in range(n_streams)])
+            first = eng._first_frames(rows, hidden)
+            first_host = first.cpu()
+            return t_prefill, time.perf_counter() - t0, hidden, first, first_host
 
-    from vui_b200.replicas import aggregate_rate
+        for _ in range(n_streams):
+            eng.new_row()
+        t_first, ttff_first, *_ = prefill_and_first_frame()
+        warm_p, warm_t = [], []
+        for _ in range(5):
+            for r in eng._rows.values():
+                eng._rewind_row(r, 0)
+            self.barrier()
+            tp, tt, hidden, first, _ = prefill_and_first_frame()
+            warm_p.append(tp)
+            warm_t.append(tt)
+        tokens = n_streams * (n_text + n_frames_prompt)
+        t_warm, ttff = statistics.median(warm_p), statistics.median(warm_t)
+        # decode
+        B = n_streams
+        rows = list(eng._rows.values())
+        eng._g_slot_idx[:B] = torch.tensor([r.idx for r in rows], device=dev, dtype=torch.int32)
+        eng._g_seq_inc[:B].fill_(1)
+        eng._g_codes_in[:B] = first
+        graph = eng._frame_graph(B)
+        for _ in range(3):
+            graph.replay()
+        self.barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(n_decode - 4):
+            graph.replay()
+        ev1.record()
+        self.barrier()
+        ms = ev0.elapsed_time(ev1)
+        eng.check_device()
+        fps, ms_max = self.aggregate(B * (n_decode - 4), ms)
+        tok_s, _ = self.aggregate(tokens, t_warm * 1e3)
+        res = {
+            "workload": f"cfg4: {n_streams} streams x ({n_text} text ids + {n_frames_prompt} codec frames), batched prefill, "
+                        f"{n_decode} greedy frames",
+            "prefill_tokens_per_s": tok_s, "prefill_ms_warm": t_warm * 1e3, "prefill_tokens": tokens,
+            "prefill_tokens_per_s_first_call": tokens / t_first, "time_to_first_frame_ms": ttff * 1e3,
+            "time_to_first_frame_ms_first_call": ttff_first * 1e3,
+            "decode_frames_per_s": fps, "decode_ms_per_step": ms_max / (n_decode - 4),
+            "prefill_flops_frac_of_bf16_peak": None,
+        }
+        # 0.61 GFLOP per position (2 x 302 M backbone parameters + heads); peak from MEASURED_PEAKS.json when present
+        p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(p):
+            with open(p) as f:
+                peak = float(json.load(f).get("bf16_tflops_sustained", 0) or 0)
+            if peak > 0:
+                res["prefill_flops_frac_of_bf16_peak"] = tokens * 0.61e9 / t_warm / (peak * 1e12)
+        del graph, eng
+        torch.cuda.empty_cache()
+        return res
 
-    fps, ms_max = aggregate_rate(B * K, ms, dev)
-    e2e_fps, _ = aggregate_rate(B * K, e2e_s * 1e3, dev)
-    w_bytes = model.weight_bytes_per_step()
-    step_bytes = w_bytes + B * (GATHER_BYTES_PER_STREAM + KV_BYTES_PER_POS * (mean_T + 1))
-    res = {
-        "B": B, "K": K, "fps": fps, "e2e_fps": e2e_fps, "ms_per_step": ms_max / K, "lat": lat, "lens": lens,
-        "mean_T": mean_T, "max_seq": eng.max_seq, "prefill_s": prefill_s, "prefill_tokens": int(sum(lens)),
-        "launches_per_frame": launches_per_frame, "step_bytes": step_bytes, "phase": phase, "clocks": clocks,
-        "greedy": greedy,
-    }
-    del graph, eng
-    torch.cuda.empty_cache()
-    return res
+
+def profile_frames(model, dev, n):
+    """Prefill 256 ids, then `n` frames kernel by kernel (no graph): for `ncu` launch lists / captures."""
+    import torch
+
+    from vui_b200 import Engine
+
+    eng = Engine(model=model, max_rows=1, max_seq=1024)
+    row = eng.new_row()
+    ids = torch.randint(0, model.shape.vocab_size, (256,), generator=torch.Generator().manual_seed(0))
+    h = eng.prefill_ids(row, ids)
+    eng._apply_cfg(None, greedy=True)
+    eng._g_slot_idx[0] = row.idx
+    eng._g_seq_inc[0] = 1
+    eng._g_codes_in[0] = eng._first_frames([row], h[None])[0]
+    torch.cuda.synchronize(dev)
+    before = eng.launch_count()
+    for _ in range(n):
+        eng._frame_call(1)
+    torch.cuda.synchronize(dev)
+    eng.check_device()
+    print(json.dumps({"profile_frames": n, "launches_before_frames": before,
+                      "launches_per_frame": (eng.launch_count() - before) // max(n, 1)}), flush=True)
 
 
 def run_b200(args):
@@ -279,23 +405,40 @@ def run_b200(args):
     from vui_b200 import VuiB200, VuiShape
 
     model = VuiB200.random_init(VuiShape(), seed=0, device=dev)
-    B, W = args.streams, args.warmup
-    m = measure(model, dev, rank, world, B, args.steps, W, args.prompt_len, args.ragged, args.sample, args.max_seq)
-    extra = None
+    if args.profile_frames:
+        profile_frames(model, dev, args.profile_frames)
+        return
+    b = Bench(model, dev, rank, world)
+    B, W, K = args.streams, args.warmup, args.steps
+    ceiling = model.shape.max_seq_len
+    if B == 1 and not args.ragged:
+        lens, max_seq = [args.prompt_len], max(1024, 64 * ((args.prompt_len + K + W + 80) // 64))
+    elif args.ragged:
+        lens = torch.randint(64, 513, (B,), generator=torch.Generator().manual_seed(1)).tolist()
+        max_seq = 64 * ((512 + K + W + 80) // 64)
+    else:
+        lens, max_seq = [args.prompt_len] * B, 64 * ((args.prompt_len + K + W + 80) // 64)
+    K = min(K, ceiling - max(lens) - W - 40)
+    max_seq = min(max_seq, ceiling)
+    m = b.decode(B, K, W, args.reps, lens, args.sample, max_seq, clocks=True, phases=True)
+    extra = cfg4 = wide = None
     if B == 1 and not args.no_batched:
-        # benchmark configuration 3's shape beside the headline: 64 streams, prompts U[64,512], T=0.8 top-k 50
-        extra = measure(model, dev, rank, world, 64, min(args.steps, 100), W, 0, True, True, 0, phases=False)
+        lens64 = torch.randint(64, 513, (64,), generator=torch.Generator().manual_seed(1)).tolist()
+        k64 = min(K, 100)
+        extra = b.decode(64, k64, W, min(args.reps, 5), lens64, True, 64 * ((512 + k64 + W + 80) // 64))
+        cfg4 = b.voice_clone()
+        k256 = min(K, 50)
+        wide = b.decode(256, k256, W, 3, [512] * 256, True, 2048, e2e=False)
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         K, lat = m["K"], m["lat"]
         achieved = m["step_bytes"] / (m["ms_per_step"] * 1e-3) / 1e9
-        traffic = ncu_traffic().get(f"B{B}")
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            ct = cpu_oracle_frames_per_s(64, 24, threads)[4:]
+            ct = cpu_oracle_frame_times(args.prompt_len, 24, threads)[4:]
             cpu = {"value": len(ct) / sum(ct), "unit": "frames/s", "cores": threads, "kind": "port",
-                   "sample": "20 greedy frames after a 64-token prefill (benchmark configuration 1 shape), "
+                   "sample": f"20 greedy frames after a {args.prompt_len}-token prefill (the headline's shape), "
                              "oracle/vui_oracle.py fp32 on torch CPU"}
         line = {
             "metric": "codec frames/s", "value": m["fps"], "unit": "frames/s", "n_gpus": world, "steps": K,
@@ -308,16 +451,21 @@ def run_b200(args):
                                   f"{'greedy' if m['greedy'] else 'T=0.8 top-k 50'}"),
                 "streams_per_gpu": B, "max_seq": m["max_seq"], "mean_kv_len": m["mean_T"],
                 "l2": "inputs larger than L2: 666 MB of weights are streamed every step",
-                "replicas": world, "prefill_s": m["prefill_s"],
-                "prefill_tokens_per_s": m["prefill_tokens"] / m["prefill_s"],
+                "replicas": world,
+                "timing": f"median of {m['reps']} blocks of {K} steps (stream rewound between blocks); "
+                          f"block min/max {m['block_ms_min']:.3f}/{m['block_ms_max']:.3f} ms",
+                "prefill_first_call_s": m["prefill_first_s"],
             },
             "e2e": {"value": m["e2e_fps"], "unit": "frames/s", "h2d_bytes_per_step": B * 16 * 8,
                     "d2h_bytes_per_step": B * 16 * 8 + B * 4,
                     "p50_frame_latency_ms": 1e3 * lat[len(lat) // 2], "p95_frame_latency_ms": 1e3 * lat[int(len(lat) * 0.95)]},
-            "gpu_launches": m["launches_per_frame"] * K,
+            "gpu_launches": m["launches_per_frame"] * K * m["reps"],
             "launches_per_frame": m["launches_per_frame"],
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
+                         "frac": achieved / peak, "traffic": None,
+                         "traffic_note": "per-kernel DRAM bytes of the dominant kernels are in profiles/ (ncu captures of a few "
+                                         "launches each); no whole-frame figure is quoted here",
+                         "peak_source": peak_kind,
                          "kernel": f"frame graph ({m['launches_per_frame']} launches)",
                          "bytes_per_step": m["step_bytes"], **m["phase"]},
             "cpu_baseline": cpu,
@@ -328,11 +476,24 @@ def run_b200(args):
             line["streams64"] = {
                 "workload": "cfg3: 64 streams/GPU, prompts U[64,512], T=0.8 top-k 50 (tcgen05 GEMM path)",
                 "value": extra["fps"], "unit": "frames/s (aggregate)", "x_realtime": extra["fps"] / FRAME_RATE,
-                "ms_per_step": extra["ms_per_step"], "steps": extra["K"], "e2e": extra["e2e_fps"],
+                "ms_per_step": extra["ms_per_step"], "steps": extra["K"], "reps": extra["reps"], "e2e": extra["e2e_fps"],
                 "p50_frame_latency_ms": 1e3 * extra["lat"][len(extra["lat"]) // 2],
                 "launches_per_frame": extra["launches_per_frame"], "mean_kv_len": extra["mean_T"],
-                "prefill_tokens_per_s": extra["prefill_tokens"] / extra["prefill_s"],
+                "prefill_tokens_per_s_first_call": extra["prefill_tokens"] / extra["prefill_first_s"],
                 "roofline_frac": ach / peak, "bytes_per_step": extra["step_bytes"],
+            }
+        if cfg4 is not None:
+            line["cfg4"] = cfg4
+        if wide is not None:
+            ach = wide["step_bytes"] / (wide["ms_per_step"] * 1e-3) / 1e9
+            line["streams256"] = {
+                "workload": "cfg5 per-GPU shape: 256 streams/GPU, 512-id prompts, 2048-position KV, T=0.8 top-k 50; "
+                            "aggregate over all replicas",
+                "value": wide["fps"], "unit": "frames/s (aggregate)", "x_realtime": wide["fps"] / FRAME_RATE,
+                "ms_per_step": wide["ms_per_step"], "steps": wide["K"], "reps": wide["reps"],
+                "launches_per_frame": wide["launches_per_frame"], "mean_kv_len": wide["mean_T"],
+                "prefill_tokens_per_s_first_call": wide["prefill_tokens"] / wide["prefill_first_s"],
+                "roofline_frac": ach / peak, "bytes_per_step": wide["step_bytes"],
             }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -343,22 +504,23 @@ def run_b200(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--reps", type=int, default=25, help="timed blocks of --steps frames; the median is reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--streams", type=int, default=1, help="concurrent streams per GPU")
     ap.add_argument("--prompt-len", type=int, default=256)
-    ap.add_argument("--max-seq", type=int, default=0)
     ap.add_argument("--ragged", action="store_true", help="prompt lengths U[64,512] (config 3)")
     ap.add_argument("--sample", action="store_true", help="T=0.8 top-k 50 instead of greedy")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-batched", action="store_true", help="skip the extra 64-stream measurement")
+    ap.add_argument("--no-batched", action="store_true", help="skip the 64-stream, cfg4 and 256-stream blocks")
+    ap.add_argument("--profile-frames", type=int, default=0, help="run N frames without a graph and exit (for ncu)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         if args.steps > 200:
-            args.steps = 200  # bounded sample: ~0.2 s per CPU frame
+            args.steps = 200  # bounded sample: ~30 ms per CPU frame
         run_reference(args)
     else:
         run_b200(args)

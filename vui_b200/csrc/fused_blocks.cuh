@@ -70,6 +70,41 @@ __device__ __forceinline__ void fb_stamp(unsigned long long* dbg, int i) {
     }
 }
 
+// One-way exchange inside a cluster: a value is stored into a peer's shared memory and, in the same
+// operation, counted on an mbarrier of that peer (st.async ... mbarrier::complete_tx::bytes).  The
+// receiver arms its mbarrier with the number of bytes all peers will send and waits for the phase: one
+// hop, where a cluster barrier costs an arrive, the barrier itself and a wait.  Receivers cannot retire
+// before everything addressed to them has landed, and senders only address peers that still wait.
+__device__ __forceinline__ uint32_t peer_addr(const void* local_smem, int peer_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local_smem)), "r"(peer_rank));
+    return r;
+}
+__device__ __forceinline__ void push_f32(uint32_t dst, uint32_t bar, float v) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+                 ::"r"(dst), "f"(v), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void push_f32x2(uint32_t dst, uint32_t bar, float v0, float v1) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+                 ::"r"(dst), "f"(v0), "f"(v1), "r"(bar) : "memory");
+}
+// Bounded wait for everything peers send to this CTA's mbarrier (phase 0), with cluster-scope acquire.
+__device__ __forceinline__ bool wait_pushed(uint64_t* bar, unsigned limit) {
+    const uint32_t a = smem_u32(bar);
+    for (unsigned spins = 0; spins < limit; ++spins) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], 0;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 constexpr int FLAG_COPY_TIMEOUT = 16;  // same bit as the tensor-core pipeline: "a bounded wait ran out"
 
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -384,7 +419,9 @@ struct AttnBlockSmem {
     float s_new[G];
     float red[FB_WARPS];
     float dots[FB_WARPS * ((NR + 15) / 16) * 16];  // per-warp partial sums of the q/k/v rows
-    alignas(8) uint64_t bar;
+    alignas(8) uint64_t bar;      // weight copies
+    alignas(8) uint64_t bar_qkv;  // q/k/v vector complete (all peers' rows)
+    alignas(8) uint64_t bar_part; // all peers' partial softmax states
 };
 
 // SHORT: the cache holds at most 16 positions (the depth transformer): every CTA attends over all of
@@ -405,14 +442,17 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     const int qcols = a.Hq * HD, kvcols = a.Hkv * HD;
     fb_stamp(a.dbg, 0);
     pdl_trigger();
-    cluster_arrive();
 
     // ---- weights: bulk copies into shared memory, before the predecessor is waited for
     if (warp == 0) {
         if (lane == 0) {
             mbar_init(&sm.bar, 1);
+            mbar_init(&sm.bar_qkv, 1);
+            mbar_init(&sm.bar_part, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&sm.bar_qkv, (uint32_t)((G * HD + 2 * HD) * 4));
+            mbar_expect_tx(&sm.bar_part, (uint32_t)(FB_CL * G * (HD + 2) * 4));
             mbar_expect_tx(&sm.bar, (uint32_t)(S::NR * K * 2 + OR * OC * 2));
             bulk_g2s(sm.w, a.wqkv + (size_t)(kvh * G * HD + rank * QR) * K, QR * K * 2, &sm.bar);
             bulk_g2s(sm.w + QR * K, a.wqkv + (size_t)(qcols + kvh * HD + rank * KR) * K, KR * K * 2, &sm.bar);
@@ -422,6 +462,8 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
             tma_load_2d(sm.wo, &map_wo, kvh * OC, rank * OR, &sm.bar);
         }
     }
+    __syncthreads();
+    cluster_arrive();  // after the mbarriers exist: a peer that has passed cluster_wait() may push to them
     prefetch_l2(a.next, FB_THREADS);
     const int k0 = tid * EPT;
     float nw[EPT];
@@ -508,8 +550,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
         }
         // place of the pair inside the head group's [q | k | v] vector; tid & 7 = the peer it goes to
         const int idx = is_q ? rank * QR + sub : (is_k ? G * HD : G * HD + HD) + rank * KR + sub;
-        float* dst = cluster.map_shared_rank(sm.qkv, tid & 7);
-        *reinterpret_cast<float2*>(dst + idx) = make_float2(t0, t1);
+        push_f32x2(peer_addr(sm.qkv + idx, tid & 7), peer_addr(&sm.bar_qkv, tid & 7), t0, t1);
         if (!is_q && (tid & 7) == 0) {
             bf16* cache = is_k ? a.k_cache : a.v_cache;
             const int col = kvh * HD + rank * KR + sub;
@@ -517,9 +558,8 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
                 __floats2bfloat162_rn(t0, t1);
         }
     }
-    __syncthreads();
     fb_stamp(a.dbg, 9);
-    cluster.sync();
+    if (!wait_pushed(&sm.bar_qkv, a.spin_limit) && tid == 0) atomicOr(a.flag, FLAG_COPY_TIMEOUT);
     fb_stamp(a.dbg, 4);
 
     // ---- attention: this CTA's share of the old keys
@@ -681,17 +721,15 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
             }
     #pragma unroll
             for (int c = 0; c < FB_CL; ++c) {
-                float* dst = cluster.map_shared_rank(&sm.part[0][0][0], c) + (rank * G + th) * (HD + 2);
-                dst[tdim] = O_;
-                if (tdim == 0) {
-                    dst[HD] = M_;
-                    dst[HD + 1] = L_;
-                }
+                float* mine = &sm.part[0][0][0] + (rank * G + th) * (HD + 2);
+                const uint32_t pbar = peer_addr(&sm.bar_part, c);
+                push_f32(peer_addr(mine + tdim, c), pbar, O_);
+                if (tdim == 0) push_f32x2(peer_addr(mine + HD, c), pbar, M_, L_);
             }
         }
         __syncthreads();
         fb_stamp(a.dbg, 11);
-        cluster.sync();
+        if (!wait_pushed(&sm.bar_part, a.spin_limit) && tid == 0) atomicOr(a.flag, FLAG_COPY_TIMEOUT);
         fb_stamp(a.dbg, 5);
         if (tid < G * HD) {
             // every CTA merges the partial states in CTA order, then the new key: same bits everywhere
@@ -760,7 +798,8 @@ struct MlpBlockSmem {
     alignas(16) float g[CU];
     float red[TH / 32];
     float dots[(TH / 32) * ((2 * U + 15) / 16) * 16];  // per-warp partial sums of the w1 / w3 rows
-    alignas(8) uint64_t bar;
+    alignas(8) uint64_t bar;     // weight copies
+    alignas(8) uint64_t bar_g;   // the cluster's activations complete (all peers' units)
 };
 
 template <int K, int F, int U, int TH>
@@ -777,13 +816,14 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     fb_stamp(a.dbg, 0);
     pdl_trigger();
-    cluster_arrive();
 
     if (warp == 0) {
         if (lane == 0) {
             mbar_init(&sm.bar, 1);
+            mbar_init(&sm.bar_g, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&sm.bar_g, (uint32_t)(CU * 4));
             mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + OR * CU * 2));
             const size_t u0 = (size_t)cid * CU + rank * U;
             bulk_g2s(sm.w13, a.w1 + u0 * K, U * K * 2, &sm.bar);
@@ -792,6 +832,8 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
             tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
         }
     }
+    __syncthreads();
+    cluster_arrive();  // after the mbarriers exist: a peer that has passed cluster_wait() may push to them
     prefetch_l2(a.next, TH);
     const int k0 = tid * EPT;
     float nw[EPT];
@@ -836,11 +878,10 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         const float a1 = rbf(mma_row_total<2 * U, NWARP>(sm.dots, u));
         const float a3 = rbf(mma_row_total<2 * U, NWARP>(sm.dots, U + u));
         const float sl = rbf(a1 / (1.0f + expf(-a1)));
-        cluster.map_shared_rank(sm.g, tid & 7)[rank * U + u] = rbf(sl * a3);
+        push_f32(peer_addr(sm.g + rank * U + u, tid & 7), peer_addr(&sm.bar_g, tid & 7), rbf(sl * a3));
     }
-    __syncthreads();
     fb_stamp(a.dbg, 9);
-    cluster.sync();
+    if (!wait_pushed(&sm.bar_g, a.spin_limit) && tid == 0) atomicOr(a.flag, FLAG_COPY_TIMEOUT);
     fb_stamp(a.dbg, 4);
 
     // ---- the cluster's K-slice of w2 for this CTA's rows

@@ -486,11 +486,12 @@ class Engine:
             off = offsets.get(row.idx, row.offset)
             if off + emb.shape[0] > self.max_seq:
                 raise RuntimeError(f"prefill of {emb.shape[0]} positions overflows max_seq={self.max_seq}")
-            # a segment longer than one call is cut; a row appears once per call
+            # a segment longer than one call is cut; a slot may appear several times in a call (its rows
+            # carry consecutive positions, and every row's K/V is in the cache before any row attends)
             start = 0
             while start < emb.shape[0]:
                 room = self.max_prefill_rows - sum(e.shape[0] for _, _, e in pend)
-                if room == 0 or any(s_ == row.idx for s_, _, _ in pend):
+                if room == 0:
                     flush()
                     room = self.max_prefill_rows
                 n = min(room, emb.shape[0] - start)
