@@ -202,8 +202,81 @@ struct StageNorm {
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr) const {
         stage<K>(Xs, r0, nr, preload<K>());
     }
+    // Single row given as x + bf16(sum of partial rows): the whole CTA adds the rows (every thread a few
+    // consecutive elements, all rows requested at once, added in row order) and normalises together.
+    template <int K>
+    __device__ __forceinline__ void stage_parts(bf16* Xs) const {
+        constexpr int EPT = K / GEMV_THREADS;  // 2 (K = 512) or 4 (K = 1024)
+        static_assert(EPT == 2 || EPT == 4, "partial rows come from the fused layers: K is 512 or 1024");
+        constexpr int MAXP = 16;
+        __shared__ float red[GEMV_WARPS];
+        const int k0 = threadIdx.x * EPT;
+        const bf16* xr = x + (size_t)row_add * K;
+        float xv[EPT], wv[EPT], sp[EPT];
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) sp[j] = 0.f;
+        if constexpr (EPT == 4) {
+            const uint2 xraw = __ldcg(reinterpret_cast<const uint2*>(xr + k0));
+            const uint2 wraw = __ldg(reinterpret_cast<const uint2*>(w + k0));
+            float4 p[MAXP];
+#pragma unroll
+            for (int u = 0; u < MAXP; ++u)
+                p[u] = u < n_parts ? __ldcg(reinterpret_cast<const float4*>(parts + (size_t)u * K + k0))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < MAXP; ++u) { sp[0] += p[u].x; sp[1] += p[u].y; sp[2] += p[u].z; sp[3] += p[u].w; }
+            const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xraw);
+            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float2 a = __bfloat1622float2(xh[i]), b = __bfloat1622float2(wh[i]);
+                xv[2 * i] = a.x; xv[2 * i + 1] = a.y; wv[2 * i] = b.x; wv[2 * i + 1] = b.y;
+            }
+        } else {
+            const unsigned xraw = __ldcg(reinterpret_cast<const unsigned*>(xr + k0));
+            const unsigned wraw = __ldg(reinterpret_cast<const unsigned*>(w + k0));
+            float2 p[MAXP];
+#pragma unroll
+            for (int u = 0; u < MAXP; ++u)
+                p[u] = u < n_parts ? __ldcg(reinterpret_cast<const float2*>(parts + (size_t)u * K + k0)) : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < MAXP; ++u) { sp[0] += p[u].x; sp[1] += p[u].y; }
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xraw));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wraw));
+            xv[0] = a.x; xv[1] = a.y; wv[0] = b.x; wv[1] = b.y;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            xv[j] = rbf(xv[j] + rbf(sp[j]));
+            ss = fmaf(xv[j], xv[j], ss);
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < GEMV_WARPS; ++i) tot += red[i];
+        const float rinv = rsqrtf(tot / (float)K + eps);
+        if constexpr (EPT == 4) {
+            uint2 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+            oh[0] = __floats2bfloat162_rn(rbf(xv[0] * rinv) * wv[0], rbf(xv[1] * rinv) * wv[1]);
+            oh[1] = __floats2bfloat162_rn(rbf(xv[2] * rinv) * wv[2], rbf(xv[3] * rinv) * wv[3]);
+            *reinterpret_cast<uint2*>(Xs + k0) = o;
+        } else {
+            *reinterpret_cast<__nv_bfloat162*>(Xs + k0) =
+                __floats2bfloat162_rn(rbf(xv[0] * rinv) * wv[0], rbf(xv[1] * rinv) * wv[1]);
+        }
+    }
     template <int K>
     __device__ __forceinline__ void stage(bf16* Xs, int r0, int nr, const NormW<K>& nw) const {
+        if constexpr (K == 512 || K == 1024) {
+            if (n_parts > 0) {  // uniform over the CTA
+                stage_parts<K>(Xs);
+                return;
+            }
+        }
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int rr = warp; rr < nr; rr += (int)(blockDim.x >> 5)) {
             const bf16* xr = x + ((size_t)(r0 + rr) * row_mul + row_add) * K;
@@ -216,27 +289,6 @@ struct StageNorm {
                 if (k < K) {
                     uint4 u = __ldcg(reinterpret_cast<const uint4*>(xr + k));
                     unpack8(u, v[it]);
-                    if (n_parts > 0) {
-                        // eight partial rows in flight at a time, added in row order
-                        float sp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        for (int p0 = 0; p0 < n_parts; p0 += 8) {
-                            float4 pa[8], pb[8];
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) {
-                                const bool ok = p0 + u < n_parts;
-                                const float* q = parts + (size_t)(ok ? p0 + u : p0) * K + k;
-                                pa[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                                pb[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) {
-                                sp[0] += pa[u].x; sp[1] += pa[u].y; sp[2] += pa[u].z; sp[3] += pa[u].w;
-                                sp[4] += pb[u].x; sp[5] += pb[u].y; sp[6] += pb[u].z; sp[7] += pb[u].w;
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[it][j] = rbf(v[it][j] + rbf(sp[j]));
-                    }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) ss = fmaf(v[it][j], v[it][j], ss);
                 }
