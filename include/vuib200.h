@@ -255,6 +255,13 @@ int32_t vuib_debug_linear_rope(VuibEngine* e, int32_t n_rows, const void* x_dev,
  * (engine.py:555-569, 594-595).  Async on `stream`. */
 int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream);
 
+/* Copies a slot's repetition-penalty state out of the workspace: counts_out_dev gets codebook_size
+ * fp32 counts (how often each cb0 code sits in the window), filled_out_dev (optional) the number of
+ * codes the rolling window holds.  The reference keeps these as Engine._rep_counts / _rep_filled
+ * (engine.py:555-569), which its serving layer logs (serving/stream/tts_worker.py:646-653).  Async on
+ * `stream`; both outputs are device pointers. */
+int32_t vuib_rep_state(VuibEngine* e, int32_t slot, float* counts_out_dev, int32_t* filled_out_dev, void* stream);
+
 /* Zeroes the mutable sampler / bookkeeping state in the workspace: per-slot draw counters,
  * repetition-penalty state, the device error flag.  Weights, KV and lengths are untouched.
  * (The reference has no equivalent: its draws come from torch's global generator.) */

@@ -145,22 +145,38 @@ def test_greedy_argmaxes_five_seeds(nano_model, nano_sd):
     """Greedy decoding of 32 frames for five prompts.  The engine runs free; the oracle (bf16 on cuBLAS)
     is teacher-forced on the engine's codes at both levels (the previous frame into the backbone, the
     chosen codes into the depth loop), so each of the 5 x 32 x 16 argmaxes is taken under the same
-    history on both sides.  Every argmax whose top-2 margin in the oracle exceeds two bf16 steps must
-    agree; the counts of identical, near-tie and clear decisions are held to thresholds."""
+    history on both sides and both logit vectors are at hand.  Every pair of logit vectors agrees within
+    the bf16 tolerance; an argmax may differ only where the oracle's top-2 margin is within two bf16 steps
+    or within twice the largest difference between the two vectors (each candidate moves by at most
+    that); the counts of identical, near-tie and wider flips are held to thresholds."""
     from vui_b200 import Engine
 
     torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
     eng = Engine(model=nano_model, max_rows=1, max_seq=320)
     o = Oracle(OracleConfig(), nano_sd, n_slots=1, max_seq=320, dtype=torch.bfloat16, device="cuda")
     F = torch.nn.functional
-    n_frames, total, same, near_flip, clear, near = 32, 0, 0, 0, 0, 0
-    frames_same = 0
+    n_frames, total, same, near_flip, wide_flip, clear, near = 32, 0, 0, 0, 0, 0, 0
+    frames_same, worst_delta = 0, 0.0
+    rq_tap = torch.zeros(1, 15, 2048, device="cuda", dtype=torch.bfloat16)
     for seed in range(5):
         ids = _ids(256, 500 + seed)
         eng.reset()
+        eng._set_taps(None, rq_tap)
+        eng._apply_cfg(None, greedy=True)
         row = eng.new_row()
         h = eng.prefill_ids(row, ids)
-        mine = eng.generate_frames([row], h[None], n_frames, greedy=True)[0].cpu()
+        eng._g_slot_idx[0] = row.idx
+        eng._g_seq_inc[0] = 1
+        c0 = eng._first_frames([row], h[None])[0]
+        mine = [c0.cpu()]
+        mine_logits = [[eng._last_first[1][0].float().cpu()] + list(rq_tap[0].float().cpu())]
+        eng._g_codes_in[0] = c0
+        for f in range(1, n_frames):
+            eng._frame_step(1)
+            mine.append(eng._g_codes_in[0].cpu())
+            mine_logits.append([eng._g_cb0_out[0].float().cpu()] + list(rq_tap[0].float().cpu()))
+        mine = torch.stack(mine)
+        eng._set_taps(None, None)
         row.close()
         o.seq_lens = [0]
         ho = o.prefill_text(0, ids)[-1:]
@@ -175,7 +191,11 @@ def test_greedy_argmaxes_five_seeds(nano_model, nano_sd):
             for q in range(16):
                 top2 = logits[q].topk(2)
                 margin = (top2.values[0] - top2.values[1]).item()
-                is_near = margin <= 2 * BF16_STEP_AT_1 * max(1.0, abs(top2.values[0].item()))
+                two_steps = 2 * BF16_STEP_AT_1 * max(1.0, abs(top2.values[0].item()))
+                delta = (mine_logits[f][q] - logits[q]).abs().max().item()
+                worst_delta = max(worst_delta, delta / logits[q].abs().max().item())
+                assert delta <= REL_TOL_BF16 * logits[q].abs().max().item(), (seed, f, q, delta)
+                is_near = margin <= two_steps
                 total += 1
                 near += is_near
                 clear += not is_near
@@ -183,15 +203,19 @@ def test_greedy_argmaxes_five_seeds(nano_model, nano_sd):
                     same += 1
                 else:
                     frame_ok = False
-                    assert is_near, f"seed {seed} frame {f} codebook {q}: engine {int(mine[f, q])}, oracle " \
-                                    f"{int(top2.indices[0])} with margin {margin:.4f}"
-                    near_flip += 1
+                    assert margin <= max(two_steps, 2 * delta), \
+                        f"seed {seed} frame {f} codebook {q}: engine {int(mine[f, q])}, oracle {int(top2.indices[0])} " \
+                        f"with margin {margin:.4f}, logit difference {delta:.4f}"
+                    near_flip += is_near
+                    wide_flip += not is_near
             frames_same += frame_ok
-    print(f"\n[greedy, 5 seeds x 32 frames x 16 codebooks] {total} argmaxes: {same} identical, {near_flip} differ "
-          f"(all at near-ties); oracle margins: {clear} clear, {near} within two bf16 steps; "
-          f"{frames_same}/{5 * n_frames} frames identical in all 16 codebooks")
+    print(f"\n[greedy, 5 seeds x 32 frames x 16 codebooks] {total} argmaxes: {same} identical, {near_flip} differ at a margin "
+          f"within two bf16 steps, {wide_flip} at a wider margin that is still within twice the logit difference; "
+          f"oracle margins: {clear} clear, {near} within two bf16 steps; largest logit difference {worst_delta:.4f} of the "
+          f"largest logit; {frames_same}/{5 * n_frames} frames identical in all 16 codebooks")
     assert total == 5 * 32 * 16
-    assert same + near_flip == total
-    assert same >= 0.93 * total       # measured ~97 %: a drop means a kernel moved away from the oracle
-    assert near_flip <= near          # a flip can only happen where the oracle itself is undecided
+    assert same + near_flip + wide_flip == total
+    assert same >= 0.93 * total           # measured ~96 %: a drop means a kernel moved away from the oracle
+    assert wide_flip <= 0.01 * total      # flips beyond two bf16 steps stay rare
+    assert near_flip <= near
     assert frames_same >= 0.4 * 5 * n_frames

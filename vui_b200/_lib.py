@@ -96,6 +96,7 @@ SYMBOLS = {
     "vuib_debug_norm_linear": (C.c_int32, [_P, C.c_int32, _P, _P, _P, C.c_int32, _P, C.c_int32, _P]),
     "vuib_debug_linear_rope": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, C.c_int32, _P]),
     "vuib_rep_reset": (C.c_int32, [_P, C.c_int32, _P]),
+    "vuib_rep_state": (C.c_int32, [_P, C.c_int32, _P, _P, _P]),
     "vuib_reset_state": (C.c_int32, [_P, _P]),
     "vuib_read_trace": (C.c_int32, [_P, C.POINTER(C.c_uint64), C.c_int32]),
     "vuib_set_wait_limit": (C.c_int32, [_P, C.c_uint32]),

@@ -1310,6 +1310,20 @@ extern "C" int32_t vuib_rep_reset(VuibEngine* e, int32_t slot, void* stream) {
     return VUIB_OK;
 }
 
+extern "C" int32_t vuib_rep_state(VuibEngine* e, int32_t slot, float* counts_out_dev, int32_t* filled_out_dev,
+                                  void* stream) {
+    if (!e || !counts_out_dev) return VUIB_ERR_NULL;
+    if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");
+    const VuibConfig& c = e->cfg;
+    if (slot < 0 || slot >= c.n_slots) return fail(e, VUIB_ERR_RANGE, "slot %d out of range", slot);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CK(cudaMemcpyAsync(counts_out_dev, e->ws + e->lay.rep_counts + (size_t)slot * c.codebook_size * 4,
+                       (size_t)c.codebook_size * 4, cudaMemcpyDeviceToDevice, s));
+    if (filled_out_dev)
+        CK(cudaMemcpyAsync(filled_out_dev, e->ws + e->lay.rep_filled + (size_t)slot * 4, 4, cudaMemcpyDeviceToDevice, s));
+    return VUIB_OK;
+}
+
 extern "C" int32_t vuib_reset_state(VuibEngine* e, void* stream) {
     if (!e) return VUIB_ERR_NULL;
     if (!e->have_ws) return fail(e, VUIB_ERR_UNBOUND, "bind the workspace first");

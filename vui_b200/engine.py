@@ -242,10 +242,13 @@ class Engine:
         self._kv = torch.zeros(s.n_layers, 2, n_slots, self.max_seq, s.n_kv_heads, s.head_dim,
                                device=dev, dtype=torch.bfloat16)
         self.seq_lens = torch.zeros(n_slots, device=dev, dtype=torch.int32)
-        self.model.decoder.flash_kv_caches = [
+        # this engine's caches; model.decoder.flash_kv_caches (where the reference keeps them, model.py:473-495)
+        # points at the caches of the engine built last on the model
+        self.flash_kv_caches = [
             SimpleNamespace(k_cache=self._kv[i, 0], v_cache=self._kv[i, 1], seq_lens=self.seq_lens)
             for i in range(s.n_layers)
         ]
+        self.model.decoder.flash_kv_caches = self.flash_kv_caches
         nbytes = C.c_size_t()
         self._ck(self._lib.vuib_workspace_bytes(self._handle, C.byref(nbytes)))
         self._ws = torch.zeros(nbytes.value + 256, device=dev, dtype=torch.uint8)
@@ -339,6 +342,24 @@ class Engine:
     def _rep_reset(self, penalty: float = 1.0, window: int = 0, slot: int = -1) -> None:
         self._ck(self._lib.vuib_rep_reset(self._handle, slot, self._stream))
         self._rep_window_cur = window
+
+    @property
+    def _rep_counts(self) -> Tensor:
+        """(max_rows, CS) fp32: how often each cb0 code sits in a row's repetition window
+        (the tensor of the same name in the reference, engine.py:555-569)."""
+        out = torch.zeros(self.max_rows, self.CS, device=self.device, dtype=torch.float32)
+        for r in range(self.max_rows):
+            self._ck(self._lib.vuib_rep_state(self._handle, r, C.c_void_p(out[r].data_ptr()), None, self._stream))
+        return out
+
+    @property
+    def _rep_filled(self) -> int:
+        """Codes currently held by row 0's rolling repetition window."""
+        cnt = torch.zeros(self.CS, device=self.device, dtype=torch.float32)
+        filled = torch.zeros(1, device=self.device, dtype=torch.int32)
+        self._ck(self._lib.vuib_rep_state(self._handle, 0, C.c_void_p(cnt.data_ptr()), C.c_void_p(filled.data_ptr()),
+                                          self._stream))
+        return int(filled.item())
 
     # ----------------------------------------------------------------- graphs
     def _frame_call(self, B: int) -> None:

@@ -128,7 +128,7 @@ class VuiB200(torch.nn.Module):
             if tuple(t.shape) != shp:
                 raise ValueError(f"'{name}' has shape {tuple(t.shape)}, expected {shp}")
             self.sd[name] = t.to(self.device_, torch.bfloat16).contiguous()
-        for opt in ("spk_proj.weight", "noisy_emb"):
+        for opt in ("spk_proj.weight", "noisy_emb", "sq_proj.weight", "wps_proj.proj.weight"):
             if opt in sd:
                 self.sd[opt] = sd[opt].to(self.device_, torch.bfloat16).contiguous()
         self.text_tokenizer = tokenizer
