@@ -14,6 +14,7 @@
 #include "decode_kernels.cuh"
 #include "tc_gemm.cuh"
 #include "fused_blocks.cuh"
+#include "depth_group.cuh"
 
 using namespace vuib;
 
@@ -65,6 +66,7 @@ struct VuibEngine {
     unsigned spin_limit;  // bound of the waits inside kernels, in polls (vuib_set_wait_limit)
     int fused_backbone;   // 0 = not asked yet, 1 = the two-kernel layers can run here, -1 = they cannot
     int fused_depth;
+    int depth_group;      // same for the one-launch depth loop of many streams
     float* cb0_stats;   // optional (max_rows, 2) fp32: entropy and top probability of each cb0 draw
     TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
     char err[256];
@@ -1030,6 +1032,91 @@ static int32_t rq_layers(VuibEngine* e, int M, bf16* x, int rows_per_b, int pos_
     return VUIB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Many streams: the whole depth loop as one launch (depth_group.cuh).
+// ---------------------------------------------------------------------------
+static bool depth_group_ok(VuibEngine* e) {
+    if (e->depth_group == 0) {
+        const VuibConfig& c = e->cfg;
+        bool ok = e->tc && c.rq_d_model == DG_D && c.rq_n_heads == DG_CL && c.rq_n_layers <= DG_LAYERS &&
+                  c.rq_ffn % DG_CL == 0 && c.rq_ffn / DG_CL <= 192 && c.codebook_size == DG_CL * 256;
+        if (ok) {
+            ok = cudaFuncSetAttribute(k_depth_group<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)sizeof(DepthGroupSmem<8>)) == cudaSuccess &&
+                 cudaFuncSetAttribute(k_depth_group<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)sizeof(DepthGroupSmem<16>)) == cudaSuccess;
+            if (!ok) cudaGetLastError();
+        }
+        e->depth_group = ok ? 1 : -1;
+    }
+    return e->depth_group == 1 && !env_off("VUIB_NO_DEPTH_GROUP");
+}
+
+static int32_t launch_depth_group(VuibEngine* e, int B, const SampleArgs& sa_base, int Qn, cudaStream_t s) {
+    const VuibConfig& c = e->cfg;
+    const WsLayout& L = e->lay;
+    DepthGroupMaps maps;
+    for (int i = 0; i < c.rq_n_layers; ++i) {
+        maps.wqkv[i] = e->tc->rq_wqkv[i];
+        maps.out[i] = e->tc->rq_out[i];
+        maps.w1[i] = e->tc->rq_w1[i];
+        maps.w3[i] = e->tc->rq_w3[i];
+        maps.w2[i] = e->tc->rq_w2[i];
+    }
+    for (int i = c.rq_n_layers; i < DG_LAYERS; ++i) {
+        maps.wqkv[i] = maps.wqkv[0]; maps.out[i] = maps.out[0]; maps.w1[i] = maps.w1[0]; maps.w3[i] = maps.w3[0];
+        maps.w2[i] = maps.w2[0];
+    }
+    maps.head = e->tc->rq_head;
+    DepthGroupArgs a;
+    memset(&a, 0, sizeof(a));
+    a.B = B;
+    a.n_layers = c.rq_n_layers;
+    a.Q = c.n_quantizers;
+    a.Qn = Qn;
+    a.CS = c.codebook_size;
+    a.upc = c.rq_ffn / DG_CL;
+    a.max_rows = c.max_rows;
+    a.eps = c.rq_norm_eps;
+    a.x2 = wsp<bf16>(e, L.rq_x2);
+    a.x1 = wsp<bf16>(e, L.rq_x);
+    a.kc = wsp<bf16>(e, L.rq_k);
+    a.vc = wsp<bf16>(e, L.rq_v);
+    for (int i = 0; i < c.rq_n_layers; ++i) {
+        a.attn_norm[i] = static_cast<const bf16*>(e->w.rq_attn_norm[i]);
+        a.mlp_norm[i] = static_cast<const bf16*>(e->w.rq_mlp_norm[i]);
+    }
+    a.final_norm = static_cast<const bf16*>(e->w.rq_norm);
+    a.logits = wsp<bf16>(e, L.rq_logits);
+    a.tap = e->tap_rq;
+    a.sa = sa_base;
+    a.flag = wsp<int32_t>(e, L.flag);
+    a.spin_limit = e->spin_limit;
+    a.dbg = env_off("VUIB_TRACE_DEPTH") ? wsp<unsigned long long>(e, L.trace) : nullptr;
+    // groups of 8 streams while they fit the clusters that can be resident at once, else of 16
+    const bool r8 = (B + 7) / 8 <= 15;
+    const int groups = r8 ? (B + 7) / 8 : (B + 15) / 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(groups * DG_CL);
+    cfg.blockDim = dim3(DG_THREADS);
+    cfg.dynamicSmemBytes = r8 ? sizeof(DepthGroupSmem<8>) : sizeof(DepthGroupSmem<16>);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = DG_CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    prefer_max_smem(reinterpret_cast<const void*>(r8 ? k_depth_group<8> : k_depth_group<16>));
+    if (r8) CK(cudaLaunchKernelEx(&cfg, k_depth_group<8>, maps, a));
+    else CK(cudaLaunchKernelEx(&cfg, k_depth_group<16>, maps, a));
+    e->launches++;
+    return VUIB_OK;
+}
+
 static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16* hidden,
                          const bf16* cb0_logits, const bf16* eos_logit, int first_frame,
                          int64_t* codes_out, float* eos_prob, cudaStream_t s) {
@@ -1094,6 +1181,7 @@ static int32_t run_depth(VuibEngine* e, int B, const int32_t* slots, const bf16*
         EpiProjPos ep{static_cast<const bf16*>(e->w.rq_backbone_proj), c.d_model, pos_emb, x2, rd, 2};
         CK(VUIB_GEMV(c.d_model, e, sc, ep, B, rd, s));
     }
+    if (tc && depth_group_ok(e)) return launch_depth_group(e, B, sa, Qn, s);
     rc = tc ? rq_layers_tc(e, 2 * B, x2, 2, 0, s) : rq_layers(e, 2 * B, x2, 2, 0, s);
     if (rc) return rc;
 
