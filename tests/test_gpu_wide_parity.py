@@ -24,13 +24,21 @@ def _cos(a, b):
     return torch.nn.functional.cosine_similarity(a.float().cpu().flatten(), b.float().cpu().flatten(), dim=0).item()
 
 
+def _rms_rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return ((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()).item()
+
+
 def _check_close(mine, res, k, what):
-    """`mine` against the fp32 evaluation (2e-2, or as close to it as the bf16 oracle on cuBLAS is) and
-    against that bf16 oracle (two bf16 evaluations that round at different summation orders)."""
+    """`mine` against the fp32 evaluation and against the bf16 oracle on cuBLAS (two bf16 evaluations that
+    round at different summation orders).  The largest element error of ONE row is a noisy statistic (it
+    moves by +-40 % with the summation order), so it is held to 2e-2 or to 1.6x the bf16 oracle's own; the
+    RMS error, which is stable, must be within 1.25x of the bf16 oracle's."""
     ref32, refb = res["fp32"][k], res["bf16"][k]
     e32, eb, ob = _rel(mine, ref32), _rel(mine, refb), _rel(refb, ref32)
     assert _cos(mine, ref32) > COS_TOL and _cos(mine, refb) > COS_TOL, what
-    assert e32 < REL_TOL or e32 < 1.25 * ob + 2e-3, (what, e32, ob)
+    assert e32 < REL_TOL or e32 < 1.6 * ob + 2e-3, (what, e32, ob)
+    assert _rms_rel(mine, ref32) < 1.25 * _rms_rel(refb, ref32) + 1e-3, (what, _rms_rel(mine, ref32), _rms_rel(refb, ref32))
     assert eb < REL_TOL_BF16, (what, eb)
 
 

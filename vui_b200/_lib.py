@@ -19,7 +19,7 @@ _OBJ = os.path.join(_CSRC, "_obj")
 _API_H = os.path.join(_ROOT, "include", "vuib200.h")
 # translation unit -> the headers it includes (a unit is recompiled when one of them changes)
 UNITS = {
-    "vuib200.cu": ["decode_kernels.cuh", "tc_gemm.cuh", "fused_blocks.cuh", "depth_group.cuh"],
+    "vuib200.cu": ["decode_kernels.cuh", "tc_gemm.cuh", "fused_blocks.cuh", "depth_group.cuh", "prefill_attn.cuh"],
 }
 SOURCES = [os.path.join(_CSRC, u) for u in UNITS]
 HEADERS = sorted({os.path.join(_CSRC, h) for hs in UNITS.values() for h in hs}) + [_API_H]

@@ -151,7 +151,7 @@ struct TcEpiQkv {      // RoPE on q,k + K/V append (EpiQkv of the GEMV path)
             dst[i] = __ldg(reinterpret_cast<const uint4*>(rope + (size_t)pos * HD * 2) + c);
         }
     }
-    TcEpiQkv shifted(int m) const {
+    __host__ __device__ TcEpiQkv shifted(int m) const {
         TcEpiQkv o = *this;
         o.q_out += (size_t)m * q_cols;
         if (row_slot) { o.row_slot += m; o.row_pos += m; }
@@ -204,7 +204,7 @@ struct TcEpiResidual {  // x += bf16(acc)
             dst[i] = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * N + tile * TC_TILE_N) + c);
         }
     }
-    TcEpiResidual shifted(int m) const {
+    __host__ __device__ TcEpiResidual shifted(int m) const {
         TcEpiResidual o = *this;
         o.x += (size_t)m * N;
         if (tap) o.tap += (size_t)m * N;
@@ -229,7 +229,7 @@ struct TcEpiSwiGLU {    // tile rows 0..63 = w1 rows, 64..127 = w3 rows of the s
     bf16* act; int F;  // hidden unit of tile row r (< 64) is tile*64 + r
     static constexpr bool PAIRED = true;
     static constexpr bool STAGED = false;
-    TcEpiSwiGLU shifted(int m) const {
+    __host__ __device__ TcEpiSwiGLU shifted(int m) const {
         TcEpiSwiGLU o = *this;
         o.act += (size_t)m * F;
         return o;
@@ -252,7 +252,7 @@ struct TcEpiLogits {    // plain bf16 rows (+ optional second copy with its own 
     bf16* out; int N; bf16* tap; int tap_stride;
     static constexpr bool PAIRED = false;
     static constexpr bool STAGED = false;
-    TcEpiLogits shifted(int m) const {
+    __host__ __device__ TcEpiLogits shifted(int m) const {
         TcEpiLogits o = *this;
         o.out += (size_t)m * N;
         if (tap) o.tap += (size_t)m * tap_stride;
@@ -275,7 +275,7 @@ struct TcEpiProjPos {   // depth position 0: bf16(acc) + pos_emb[0], written to 
     const bf16* pos_emb; bf16* out; int rd, row_mul;
     static constexpr bool PAIRED = false;
     static constexpr bool STAGED = false;
-    TcEpiProjPos shifted(int m) const {
+    __host__ __device__ TcEpiProjPos shifted(int m) const {
         TcEpiProjPos o = *this;
         o.out += (size_t)m * row_mul * rd;
         return o;
@@ -295,12 +295,13 @@ struct TcEpiProjPos {   // depth position 0: bf16(acc) + pos_emb[0], written to 
 struct TcArgs {
     int N;            // weight rows, a multiple of 128 (PAIRED: hidden units, a multiple of 64)
     int row_off;      // first weight row of tile 0 inside the mapped matrix (stacked depth heads)
-    int M, Mpad;      // activation rows, padded to a multiple of 16 (<= 256)
+    int M, Mpad;      // activation rows in all; rows per CTA padded to a multiple of 16 (<= 256).  M > Mpad: the
+                      // grid's z dimension walks blocks of Mpad rows (one launch for a whole prefill)
     int chunks;       // K chunks of 64 in all; split s handles chunks [s*chunks/splits, (s+1)*chunks/splits)
     int stages;       // TMA ring depth (<= TC_MAX_STAGES, <= chunks)
     int splits;       // gridDim.x: 1, 2, 4, 8 or 16 (PAIRED: not 2)
-    float* partial;   // (tiles, splits, 128, Mpad) fp32 scratch (splits > 1)
-    int32_t* counters;  // (2, tiles) arrivals / departures, zero between launches
+    float* partial;   // (row blocks, tiles, splits, 128, Mpad) fp32 scratch (splits > 1)
+    int32_t* counters;  // (2, row blocks x tiles) arrivals / departures, zero between launches
     int tiles;
     int32_t* flag;
     unsigned long long* dbg;  // optional: device-clock stamps of CTA (0,0) (profiling aid)
@@ -318,7 +319,7 @@ __device__ __forceinline__ void tc_stamp(const TcArgs& a, int i) {
 template <class Epi>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
-          const __grid_constant__ CUtensorMap mapX, TcArgs a, Epi ep) {
+          const __grid_constant__ CUtensorMap mapX, TcArgs a, Epi ep_all) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ uint64_t bar_full[TC_MAX_STAGES], bar_empty[TC_MAX_STAGES], bar_done;
     __shared__ uint32_t s_tmem;
@@ -327,6 +328,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, tile = blockIdx.y;  // the CTAs of one tile are neighbours in launch order
+    const int m_base = blockIdx.z * a.Mpad;           // first activation row of this CTA's block
+    const int Mb = min(a.Mpad, a.M - m_base);         // rows of the block
+    const int tile_id = blockIdx.z * a.tiles + tile;  // index of the (block, tile) pair in the split-K scratch
+    const int all_tiles = gridDim.z * a.tiles;
+    const Epi ep = ep_all.shifted(m_base);
     tc_stamp(a, 0);
     const int stages = a.stages;  // <= smallest chunk count of any split
     const uint32_t a_bytes = TC_TILE_N * TC_KCHUNK * 2, b_bytes = (uint32_t)a.Mpad * TC_KCHUNK * 2;
@@ -375,7 +381,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
         }
         pdl_wait();
         for (int c = 0; c < stages; ++c)
-            tma_load_2d(base + (size_t)c * stage_bytes + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, 0, &bar_full[c]);
+            tma_load_2d(base + (size_t)c * stage_bytes + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, m_base, &bar_full[c]);
         for (int c = stages; c < n_chunks; ++c) {
             const int s = c % stages;
             if (!mbar_wait(&bar_empty[s], ((c / stages) & 1) ^ 1, 4 * a.spin_limit)) { s_bad = 1; break; }
@@ -383,7 +389,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
             mbar_expect_tx(&bar_full[s], a_bytes + b_bytes);
             tma_load_2d(st, &mapA0, (k_first + c) * TC_KCHUNK, rowA0, &bar_full[s]);
             tma_load_2d(st + a_bytes / 2, &mapA1, (k_first + c) * TC_KCHUNK, rowA1, &bar_full[s]);
-            tma_load_2d(st + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, 0, &bar_full[s]);
+            tma_load_2d(st + a_bytes, &mapX, (k_first + c) * TC_KCHUNK, m_base, &bar_full[s]);
         }
       }
       __syncwarp();
@@ -414,7 +420,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
     pdl_wait();
     tc_stamp(a, 2);
     unsigned char* es = base + (size_t)stages * stage_bytes;  // epilogue staging, filled while the MMAs run
-    if constexpr (Epi::STAGED) ep.stage(es, tile, a.M, tid);
+    if constexpr (Epi::STAGED) ep.stage(es, tile, Mb, tid);
     // ---- everyone: wait for the accumulator
     const bool done_ok = mbar_wait(&bar_done, 0, 4 * a.spin_limit);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -435,16 +441,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
                     float g[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) g[j] = xchg[(tid + 64) * 8 + j];
-                    ep.apply_pair(tile * 64 + tid, m0, a.M, v, g);
+                    ep.apply_pair(tile * 64 + tid, m0, Mb, v, g);
                 }
                 __syncthreads();
             } else {
-                ep.apply(tile * TC_TILE_N + tid, m0, a.M, v, xchg, es);
+                ep.apply(tile * TC_TILE_N + tid, m0, Mb, v, xchg, es);
             }
         }
     } else {
         // partial tile to scratch as [m][n]: the 128 threads of a CTA write 512 contiguous bytes per m
-        float* mine = a.partial + ((size_t)tile * a.splits + split) * a.Mpad * TC_TILE_N;
+        float* mine = a.partial + ((size_t)tile_id * a.splits + split) * a.Mpad * TC_TILE_N;
         int m0 = 0;
         for (; m0 + 32 <= a.Mpad; m0 += 32) {
             float v[32];
@@ -462,11 +468,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
         __syncthreads();  // orders every thread's partial stores before thread 0's release below
         if (tid == 0) {
             // arrive, then wait (bounded) until every split of this tile has published its partial
-            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(a.counters + tile) : "memory");
+            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(a.counters + tile_id) : "memory");
             int v = 0;
             unsigned spins = 0;
             for (;;) {
-                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.counters + tile) : "memory");
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.counters + tile_id) : "memory");
                 if (v >= a.splits) break;
                 if (++spins > a.spin_limit) { atomicOr(a.flag, FLAG_TC_TIMEOUT); break; }
             }
@@ -483,13 +489,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
         } else {
             row = split * rpc + j_row;
         }
-        const float* all = a.partial + (size_t)tile * a.splits * a.Mpad * TC_TILE_N + row;
+        const float* all = a.partial + (size_t)tile_id * a.splits * a.Mpad * TC_TILE_N + row;
         const size_t split_stride = (size_t)a.Mpad * TC_TILE_N;
         const int n_mchunks = a.Mpad / 8;
         for (int chunk0 = 0; chunk0 < n_mchunks; chunk0 += a.splits) {  // uniform trip count: the
             const bool active = chunk0 + mg < n_mchunks;                // epilogues shuffle within a warp
             const int m0 = (active ? chunk0 + mg : n_mchunks - 1) * 8;
-            const int Meff = active ? a.M : 0;
+            const int Meff = active ? Mb : 0;
             float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int s0 = 0; s0 < a.splits; s0 += 8) {  // up to 64 loads in flight, summed in split order
                 float p[8][8];
@@ -517,10 +523,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUt
         }
         __syncthreads();
         if (tid == 0) {  // the last CTA to leave re-arms both counters for the next launch
-            const int old = atomicAdd(a.counters + a.tiles + tile, 1);
+            const int old = atomicAdd(a.counters + all_tiles + tile_id, 1);
             if (old == a.splits - 1) {
-                a.counters[tile] = 0;
-                a.counters[a.tiles + tile] = 0;
+                a.counters[tile_id] = 0;
+                a.counters[all_tiles + tile_id] = 0;
             }
         }
     }

@@ -15,6 +15,7 @@
 #include "tc_gemm.cuh"
 #include "fused_blocks.cuh"
 #include "depth_group.cuh"
+#include "prefill_attn.cuh"
 
 using namespace vuib;
 
@@ -25,6 +26,7 @@ struct WsLayout {
     size_t trace;
     size_t xn, rq_xn, rq_attn, tc_partial, tc_counters;
     size_t fx_a, fx_b, fparts_a, fparts_b, rq_fx_a, rq_fx_b, rq_fparts_a, rq_fparts_b;
+    size_t att_tiles, att_ntiles;
     size_t total;
 };
 
@@ -129,6 +131,9 @@ static void make_layout(VuibEngine* e) {
     L.rq_fx_b = take(rd * 2);
     L.rq_fparts_a = take((size_t)FUSED_MAX_PARTS * rd * 4);
     L.rq_fparts_b = take((size_t)FUSED_MAX_PARTS * rd * 4);
+    // query tiles of a prefill call (first row, rows) and their count
+    L.att_tiles = take(2 * R * 4);
+    L.att_ntiles = take(256);
     L.total = off;
 }
 
@@ -479,9 +484,14 @@ static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& 
         CK(cudaGetDevice(&dev));
         CK(cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, dev));
     }
+    // Row blocks: up to 256 activation rows per CTA; a prefill of more rows is ONE launch whose grid's z
+    // dimension walks the blocks (every weight tile is then read by its row blocks back to back and stays in
+    // L2), not one launch per block.
+    const int Mpad = M <= 256 ? (M + 15) / 16 * 16 : 256;
+    const int m_blocks = (M + Mpad - 1) / Mpad;
     int splits = 1;
     for (int d = 2; d <= 16; d *= 2) {
-        if (d > chunks_total || tiles * d > e->num_sms + e->num_sms / 2) break;
+        if (d > chunks_total || tiles * m_blocks * d > e->num_sms + e->num_sms / 2) break;
         if (Epi::PAIRED && d == 2) continue;
         splits = d;
     }
@@ -497,37 +507,33 @@ static int32_t tc_gemm(VuibEngine* e, const CUtensorMap& a0, const CUtensorMap& 
             if (dev >= 0 && dev < 64) attr_set[dev] = true;
         }
     }
-    for (int m0 = 0; m0 < M; m0 += 256) {
-        const int Mb = M - m0 < 256 ? M - m0 : 256;
-        const int Mpad = (Mb + 15) / 16 * 16;
-        CUtensorMap mx;
-        if (!make_map(&mx, X + (size_t)m0 * K, Mb, K, Mpad)) return fail(e, VUIB_ERR_CUDA, "cuTensorMapEncodeTiled failed");
-        TcArgs ta;
-        ta.N = units;
-        ta.row_off = row_off;
-        ta.M = Mb;
-        ta.Mpad = Mpad;
-        ta.chunks = chunks_total;
-        ta.splits = splits;
-        ta.tiles = tiles;
-        ta.partial = wsp<float>(e, L.tc_partial);
-        ta.counters = wsp<int32_t>(e, L.tc_counters);
-        ta.flag = wsp<int32_t>(e, L.flag);
-        ta.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) : nullptr;
-        ta.spin_limit = e->spin_limit;
-        const int min_chunks = chunks_total / splits;  // the shortest split
-        const size_t stage_bytes = TC_TILE_N * TC_KCHUNK * 2 + ((Mpad * TC_KCHUNK * 2 + 1023) & ~1023);
-        const size_t epi_bytes = Epi::STAGED ? (size_t)Mpad * TC_EPI_BYTES_PER_M : 0;
-        // two CTAs per SM when split (all CTAs of the grid must be resident), the whole SM otherwise
-        const size_t budget = (splits > 1 ? 100 : 200) * 1024;
-        int stages = epi_bytes + stage_bytes <= budget ? (int)((budget - epi_bytes) / stage_bytes) : 1;
-        if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
-        if (stages > min_chunks) stages = min_chunks;
-        ta.stages = stages;
-        const size_t smem = (size_t)stages * stage_bytes + epi_bytes + 1024;
-        CK(launch(k_gemm_tc<Epi>, dim3(splits, tiles), TC_THREADS, smem, s, a0, a1, mx, ta, ep.shifted(m0)));
-        e->launches++;
-    }
+    CUtensorMap mx;
+    if (!make_map(&mx, X, M, K, Mpad)) return fail(e, VUIB_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+    TcArgs ta;
+    ta.N = units;
+    ta.row_off = row_off;
+    ta.M = M;
+    ta.Mpad = Mpad;
+    ta.chunks = chunks_total;
+    ta.splits = splits;
+    ta.tiles = tiles;
+    ta.partial = wsp<float>(e, L.tc_partial);
+    ta.counters = wsp<int32_t>(e, L.tc_counters);
+    ta.flag = wsp<int32_t>(e, L.flag);
+    ta.dbg = env_off("VUIB_TRACE") ? wsp<unsigned long long>(e, L.trace) : nullptr;
+    ta.spin_limit = e->spin_limit;
+    const int min_chunks = chunks_total / splits;  // the shortest split
+    const size_t stage_bytes = TC_TILE_N * TC_KCHUNK * 2 + ((Mpad * TC_KCHUNK * 2 + 1023) & ~1023);
+    const size_t epi_bytes = Epi::STAGED ? (size_t)Mpad * TC_EPI_BYTES_PER_M : 0;
+    // two CTAs per SM when split (all CTAs of the grid must be resident), the whole SM otherwise
+    const size_t budget = (splits > 1 ? 100 : 200) * 1024;
+    int stages = epi_bytes + stage_bytes <= budget ? (int)((budget - epi_bytes) / stage_bytes) : 1;
+    if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+    if (stages > min_chunks) stages = min_chunks;
+    ta.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + epi_bytes + 1024;
+    CK(launch(k_gemm_tc<Epi>, dim3(splits, tiles, m_blocks), TC_THREADS, smem, s, a0, a1, mx, ta, ep));
+    e->launches++;
     return VUIB_OK;
 }
 
@@ -538,7 +544,7 @@ static int32_t norm_rows(VuibEngine* e, const bf16* x, const void* w, float eps,
     return VUIB_OK;
 }
 
-static int32_t run_layers_tc(VuibEngine* e, int M, cudaStream_t s) {
+static int32_t run_layers_tc(VuibEngine* e, int M, cudaStream_t s, bool prefill) {
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
     bf16* x = wsp<bf16>(e, L.x);
@@ -556,10 +562,21 @@ static int32_t run_layers_tc(VuibEngine* e, int M, cudaStream_t s) {
                     c.max_seq, e->rope, 1, 0, 0};
         if ((rc = tc_gemm(e, e->tc->wqkv[li], e->tc->wqkv[li], xn, M, d, qc + 2 * kvc, 0, eq, s))) return rc;
 
-        AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
-                    row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
-                    c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr, c.n_slots, wsp<int32_t>(e, L.flag)};
-        CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
+        if (prefill && !env_off("VUIB_NO_PREFILL_ATTN")) {
+            // query tile x key tile on the tensor cores; the tiles were cut once for the call
+            PrefillAttnArgs pa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]), row_slot, row_pos,
+                               wsp<int32_t>(e, L.att_tiles), wsp<int32_t>(e, L.att_ntiles), attn, c.n_heads, c.n_kv_heads,
+                               c.max_seq};
+            const int bound = (M + PA_TILE - 1) / PA_TILE + c.n_slots;  // more tiles than this are looped over
+            const int gx = bound < 4 * 148 ? bound : 4 * 148;
+            if (c.n_heads == 2 * c.n_kv_heads) CK(launch(k_prefill_attn<2>, dim3(gx, c.n_kv_heads), 256, 0, s, pa));
+            else CK(launch(k_prefill_attn<1>, dim3(gx, c.n_kv_heads), 128, 0, s, pa));
+        } else {
+            AttnArgs aa{q, static_cast<const bf16*>(e->k[li]), static_cast<const bf16*>(e->v[li]),
+                        row_slot, row_pos, wsp<float>(e, L.part), wsp<int32_t>(e, L.counters), attn,
+                        c.n_heads, c.n_kv_heads, c.max_seq, e->S, nullptr, c.n_slots, wsp<int32_t>(e, L.flag)};
+            CK(launch(k_attn_decode, dim3(e->S, c.n_kv_heads, M), ATT_THREADS, 0, s, aa));
+        }
         e->launches++;
 
         TcEpiResidual eo{x, d, nullptr};
@@ -866,13 +883,13 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
 // ---------------------------------------------------------------------------
 // Backbone: 24 blocks over M rows whose (slot, position) are in the workspace.
 // ---------------------------------------------------------------------------
-static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s, Residual* out, const void* after = nullptr,
-                          size_t after_bytes = 0) {
+static int32_t run_layers(VuibEngine* e, int M, cudaStream_t s, Residual* out, bool prefill = false,
+                          const void* after = nullptr, size_t after_bytes = 0) {
     out->x = wsp<bf16>(e, e->lay.x);
     out->parts = nullptr;
     out->n_parts = 0;
     if (M == 1 && fused_backbone_ok(e)) return run_layers_fused(e, s, out, after, after_bytes);
-    if (tc_ok(e, M)) return run_layers_tc(e, M, s);
+    if (tc_ok(e, M)) return run_layers_tc(e, M, s, prefill);
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
     bf16* x = wsp<bf16>(e, L.x);
@@ -942,7 +959,13 @@ extern "C" int32_t vuib_prefill(VuibEngine* e, int32_t n_rows, const int32_t* ro
     e->launches++;
     CK(cudaMemcpyAsync(e->ws + L.x, emb_dev, (size_t)n_rows * d * 2, cudaMemcpyDeviceToDevice, s));
     Residual res;
-    rc = run_layers(e, n_rows, s, &res);
+    if (tc_ok(e, n_rows)) {
+        CK(launch(k_prefill_tiles, 1, 256, (size_t)n_rows * 4, s, static_cast<const int32_t*>(wsp<int32_t>(e, L.row_slot)),
+                  static_cast<const int32_t*>(wsp<int32_t>(e, L.row_pos)), n_rows, wsp<int32_t>(e, L.att_tiles),
+                  wsp<int32_t>(e, L.att_ntiles)));
+        e->launches++;
+    }
+    rc = run_layers(e, n_rows, s, &res, true);
     if (rc) return rc;
     CK(launch(k_final_norm, n_rows, 128, 0, s, res.x, static_cast<const bf16*>(e->w.final_norm),
                                         e->cfg.norm_eps, static_cast<bf16*>(hidden_out_dev), d,
@@ -973,7 +996,7 @@ extern "C" int32_t vuib_backbone_step(VuibEngine* e, int32_t B, const int32_t* s
     e->launches++;
     CK(cudaGetLastError());
     Residual res;
-    rc = run_layers(e, B, s, &res, e->w.codec_head, (size_t)c.codebook_size * c.d_model * 2);
+    rc = run_layers(e, B, s, &res, false, e->w.codec_head, (size_t)c.codebook_size * c.d_model * 2);
     if (rc) return rc;
     bf16* last_tap = (e->tap_layers && res.n_parts) ? e->tap_layers + (size_t)(c.n_layers - 1) * c.max_rows * c.d_model : nullptr;
     CK(launch(k_final_norm, B, 128, 0, s, res.x, static_cast<const bf16*>(e->w.final_norm),
