@@ -145,6 +145,37 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def reference_cuda_standin(n_streams, lens, K, W, max_seq):
+    """The baseline leg for the many-stream figure: the oracle's algorithm batched in torch bf16 on this GPU,
+    one CUDA graph for the backbone step and one for the depth loop, as the reference captures them
+    (oracle/torch_cuda_standin.py says what it is and is not).  Returns ms per step."""
+    import torch
+    from oracle.torch_cuda_standin import TorchGraphDecoder
+    from oracle.vui_oracle import OracleConfig, init_weights
+
+    cfg = OracleConfig()
+    dec = TorchGraphDecoder(cfg, init_weights(cfg, 0, torch.bfloat16), n_streams, max_seq)
+    g = torch.Generator().manual_seed(7)
+    dec.k_cache.copy_((torch.randn(dec.k_cache.shape[1:], generator=g) * 0.5).to(torch.bfloat16))
+    dec.v_cache.copy_((torch.randn(dec.v_cache.shape[1:], generator=g) * 0.5).to(torch.bfloat16))
+    dec.seq_lens.copy_(torch.tensor(lens))
+    dec.codes.copy_(torch.randint(0, cfg.codebook_size, tuple(dec.codes.shape), generator=g))
+    dec.capture()
+    for _ in range(W):
+        dec.step()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        dec.step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / K
+    del dec
+    torch.cuda.empty_cache()
+    return ms
+
+
 class Bench:
     def __init__(self, model, dev, rank, world):
         self.model, self.dev, self.rank, self.world = model, dev, rank, world
@@ -421,11 +452,16 @@ def run_b200(args):
     K = min(K, ceiling - max(lens) - W - 40)
     max_seq = min(max_seq, ceiling)
     m = b.decode(B, K, W, args.reps, lens, args.sample, max_seq, clocks=True, phases=True)
-    extra = cfg4 = wide = None
+    extra = cfg4 = wide = standin_ms = None
     if B == 1 and not args.no_batched:
         lens64 = torch.randint(64, 513, (64,), generator=torch.Generator().manual_seed(1)).tolist()
         k64 = min(K, 100)
         extra = b.decode(64, k64, W, min(args.reps, 5), lens64, True, 64 * ((512 + k64 + W + 80) // 64))
+        if rank == 0 and world == 1 and not args.no_cpu_baseline:
+            try:
+                standin_ms = reference_cuda_standin(64, lens64, min(k64, 30), 3, 64 * ((512 + k64 + W + 80) // 64))
+            except Exception as exc:  # noqa: BLE001 - the stand-in must never take the bench line down
+                print(f"reference_cuda_standin failed: {exc}", file=sys.stderr)
         cfg4 = b.voice_clone()
         k256 = min(K, 50)
         wide = b.decode(256, k256, W, 3, [512] * 256, True, 2048, e2e=False)
@@ -482,6 +518,14 @@ def run_b200(args):
                 "prefill_tokens_per_s_first_call": extra["prefill_tokens"] / extra["prefill_first_s"],
                 "roofline_frac": ach / peak, "bytes_per_step": extra["step_bytes"],
             }
+            if standin_ms:
+                line["streams64"]["reference_cuda_standin"] = {
+                    "what": "torch bf16 (cuBLAS, SDPA with a length mask) restatement of the reference's CUDA path on this "
+                            "GPU, backbone step and depth loop as two CUDA graphs; stands in for the reference, which "
+                            "cannot run on this box",
+                    "ms_per_step": standin_ms, "value": 64 / (standin_ms * 1e-3), "unit": "frames/s (aggregate)",
+                    "speedup": standin_ms / extra["ms_per_step"],
+                }
         if cfg4 is not None:
             line["cfg4"] = cfg4
         if wide is not None:

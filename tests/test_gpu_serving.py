@@ -267,3 +267,32 @@ def test_conditioning_bias_and_speaker_token(model_tok, nano_sd):
     assert cnt.shape == (1, 2048) and cnt.sum() == 3 and eng._rep_filled == 3
     eng._rep_reset()
     assert eng._rep_counts.sum() == 0
+
+
+def test_torch_cuda_standin_computes_the_oracle_step(nano_sd):
+    """The bench's many-stream baseline (oracle/torch_cuda_standin.py) is the oracle's algorithm, batched and
+    captured in CUDA graphs: one step for three streams at different positions gives the oracle's hidden and
+    cb0 logits, and valid codes."""
+    from oracle.torch_cuda_standin import TorchGraphDecoder
+    from oracle.vui_oracle import Oracle, OracleConfig
+
+    cfg = OracleConfig()
+    g = torch.Generator().manual_seed(5)
+    o = Oracle(cfg, nano_sd, n_slots=3, max_seq=64, dtype=torch.bfloat16, device="cuda")
+    lens = [7, 20, 33]
+    for s_, n in enumerate(lens):
+        o.prefill_text(s_, torch.randint(0, cfg.vocab, (n,), generator=g))
+    dec = TorchGraphDecoder(cfg, nano_sd, 3, 64)
+    dec.k_cache.copy_(o.k_cache)
+    dec.v_cache.copy_(o.v_cache)
+    dec.seq_lens.copy_(torch.tensor(lens))
+    codes = torch.randint(0, 2048, (3, 16), generator=g)
+    dec.codes.copy_(codes)
+    dec.capture()
+    dec.step()
+    torch.cuda.synchronize()
+    h, cb0, _ = o.backbone_step([0, 1, 2], codes)
+    rel = lambda a, b: ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()  # noqa: E731
+    assert rel(dec.hidden, h) < 2e-2 and rel(dec.cb0, cb0) < 2e-2
+    assert dec.seq_lens.tolist() == [n + 1 for n in lens]
+    assert dec.codes.min() >= 0 and dec.codes.max() < 2048
