@@ -398,27 +398,30 @@ class Bench:
         return res
 
 
-def profile_frames(model, dev, n):
-    """Prefill 256 ids, then `n` frames kernel by kernel (no graph): for `ncu` launch lists / captures."""
+def profile_frames(model, dev, n, B, prompt_len):
+    """Prefill B streams of `prompt_len` ids, then `n` frames kernel by kernel (no graph): the command the
+    `ncu` launch lists and captures under profiles/ are taken with."""
     import torch
 
-    from vui_b200 import Engine
+    from vui_b200 import Engine, GenConfig
 
-    eng = Engine(model=model, max_rows=1, max_seq=1024)
-    row = eng.new_row()
-    ids = torch.randint(0, model.shape.vocab_size, (256,), generator=torch.Generator().manual_seed(0))
-    h = eng.prefill_ids(row, ids)
-    eng._apply_cfg(None, greedy=True)
-    eng._g_slot_idx[0] = row.idx
-    eng._g_seq_inc[0] = 1
-    eng._g_codes_in[0] = eng._first_frames([row], h[None])[0]
+    eng = Engine(model=model, max_rows=B, max_seq=1024, max_prefill_rows=4096)
+    rows = [eng.new_row() for _ in range(B)]
+    g = torch.Generator().manual_seed(0)
+    hs = eng._prefill_many([(r, model.token_emb(torch.randint(0, model.shape.vocab_size, (1, prompt_len), generator=g)))
+                            for r in rows])
+    h = torch.stack([x[-1] for x in hs])
+    eng._apply_cfg(GenConfig(temperature=0.8, top_k=50, rep_penalty=1.0), greedy=(B == 1))
+    eng._g_slot_idx[:B] = torch.tensor([r.idx for r in rows], device=dev, dtype=torch.int32)
+    eng._g_seq_inc[:B].fill_(1)
+    eng._g_codes_in[:B] = eng._first_frames(rows, h)
     torch.cuda.synchronize(dev)
     before = eng.launch_count()
     for _ in range(n):
-        eng._frame_call(1)
+        eng._frame_call(B)
     torch.cuda.synchronize(dev)
     eng.check_device()
-    print(json.dumps({"profile_frames": n, "launches_before_frames": before,
+    print(json.dumps({"profile_frames": n, "streams": B, "launches_before_frames": before,
                       "launches_per_frame": (eng.launch_count() - before) // max(n, 1)}), flush=True)
 
 
@@ -437,7 +440,7 @@ def run_b200(args):
 
     model = VuiB200.random_init(VuiShape(), seed=0, device=dev)
     if args.profile_frames:
-        profile_frames(model, dev, args.profile_frames)
+        profile_frames(model, dev, args.profile_frames, args.streams, args.prompt_len)
         return
     b = Bench(model, dev, rank, world)
     B, W, K = args.streams, args.warmup, args.steps
