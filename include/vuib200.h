@@ -294,6 +294,115 @@ int32_t vuib_check_device_flag(VuibEngine* e, void* stream);
 /* Kernel launches issued by this handle since creation (for benchmarks). */
 int64_t vuib_launch_count(VuibEngine* e);
 
+/* ---------------------------------------------------------------------------
+ * Streaming codec decode: one frame of 16 codes -> 1920 samples at 24 kHz, fp32.
+ * Replaces the device work of QwenCodecDecoder's single-frame streaming forward
+ * (src/vui/qwen_codec.py:1191-1224, captured as a CUDA graph by setup_streaming_graph,
+ * 1138-1189) as CodecCtx.decode_frame drives it (625-657); call site
+ * Engine._stream_decode_frame (src/vui/engine.py:1537-1546).
+ * All tensors fp32.  Weight pointers are borrowed; layouts are torch's unless noted.
+ * ------------------------------------------------------------------------- */
+#define VUIB_CODEC_LAYERS 8
+#define VUIB_CODEC_STAGES 2
+#define VUIB_CODEC_BLOCKS 4
+
+/* Fixed architecture of the 12.5 Hz decoder (qwen_codec.py:1080-1125); the fields exist so that a
+ * mismatching checkpoint is refused instead of misread. */
+typedef struct VuibCodecConfig {
+    int32_t n_q;            /* 16 codebooks: 1 semantic + 15 acoustic */
+    int32_t codebook_size;  /* 2048 */
+    int32_t codebook_dim;   /* 256 */
+    int32_t vq_dim;         /* 512 */
+    int32_t latent_dim;     /* 1024 */
+    int32_t d_model;        /* 512 */
+    int32_t n_layers;       /* 8 */
+    int32_t n_heads;        /* 16 (x head_dim 64 = 1024) */
+    int32_t mlp_dim;        /* 1024 */
+    int32_t max_seq;        /* 250 transformer positions */
+    int32_t decoder_dim;    /* 1536 */
+    int32_t rates[VUIB_CODEC_BLOCKS];  /* 8, 5, 4, 3 */
+    float norm_eps;         /* RMSNorm eps 1e-6 */
+} VuibCodecConfig;
+
+typedef struct VuibSnakeW {   /* SnakeBeta (qwen_codec.py:820-829), per channel, precomputed: */
+    const float* ea;          /*   exp(alpha) */
+    const float* ib;          /*   1 / (exp(beta) + 1e-9) */
+} VuibSnakeW;
+typedef struct VuibConvW { const float* w; const float* b; } VuibConvW;
+typedef struct VuibCodecLayerW {   /* DecTransformerBlock (qwen_codec.py:882-974) */
+    const float* ln1;         /* input_layernorm.weight (512) */
+    const float* wqkv;        /* q_proj | k_proj | v_proj weights stacked by rows: (3072, 512) */
+    const float* wo;          /* o_proj.weight (512, 1024) */
+    const float* attn_scale;  /* (512) */
+    const float* ln2;         /* post_attention_layernorm.weight */
+    const float* gate;        /* gate_proj.weight (1024, 512) */
+    const float* up;          /* up_proj.weight (1024, 512) */
+    const float* down;        /* down_proj.weight (512, 1024) */
+    const float* mlp_scale;   /* (512) */
+} VuibCodecLayerW;
+typedef struct VuibUpStageW {      /* upsample[i] = [CausalTransConv1d k=2 s=2, ConvNeXtBlock] (1103-1113) */
+    VuibConvW up;             /* w re-laid as rows (co, j): (1024 * 2, 1024) = weight.permute(1, 2, 0); b (1024) */
+    VuibConvW dw;             /* dwconv.conv.weight (1024, 7), bias (1024) */
+    const float* ln_w; const float* ln_b;
+    VuibConvW pw1;            /* (4096, 1024), (4096) */
+    VuibConvW pw2;            /* (1024, 4096), (1024) */
+    const float* gamma;       /* (1024) */
+} VuibUpStageW;
+typedef struct VuibResUnitW {      /* DecoderResUnit (851-860) */
+    VuibSnakeW act1; VuibConvW conv1;   /* (C, C, 7), dilation 1 / 3 / 9 */
+    VuibSnakeW act2; VuibConvW conv2;   /* (C, C, 1) */
+} VuibResUnitW;
+typedef struct VuibDecBlockW {     /* DecoderBlock (863-879) */
+    VuibSnakeW act;
+    VuibConvW up;             /* w re-laid as rows (co, k): (Cout * 2 * rate, Cin) = weight.permute(1, 2, 0); b (Cout) */
+    VuibResUnitW res[3];
+} VuibDecBlockW;
+typedef struct VuibCodecWeights {
+    const float* codebook[16];     /* quantizer.semantic.codebooks.0.embed, then acoustic 0..14: (2048, 256) */
+    const float* sem_proj;         /* quantizer.semantic.output_proj.weight (512, 256) */
+    const float* acq_proj;         /* quantizer.acoustic.output_proj.weight (512, 256) */
+    VuibConvW pre_conv;            /* (1024, 512, 3), (1024) */
+    VuibConvW in_proj;             /* pre_transformer.input_proj (512, 1024), (512) */
+    VuibCodecLayerW layer[VUIB_CODEC_LAYERS];
+    const float* norm;             /* pre_transformer.norm.weight (512) */
+    VuibConvW out_proj;            /* (1024, 512), (1024) */
+    const float* rope_cos;         /* (max_seq, 64) as RoPE.forward builds them (qwen_codec.py:161-171) */
+    const float* rope_sin;
+    VuibUpStageW stage[VUIB_CODEC_STAGES];
+    VuibConvW dec_in;              /* decoder.0 (1536, 1024, 7), (1536) */
+    VuibDecBlockW block[VUIB_CODEC_BLOCKS];
+    VuibSnakeW final_act;          /* decoder.5 (96) */
+    VuibConvW final_conv;          /* decoder.6 (1, 96, 7), (1) */
+} VuibCodecWeights;
+
+typedef struct VuibCodec VuibCodec;
+
+int32_t vuib_codec_create(const VuibCodecConfig* cfg, VuibCodec** out);
+int32_t vuib_codec_destroy(VuibCodec* c);
+int32_t vuib_codec_last_error(VuibCodec* c, char* buf, size_t n);
+/* Streaming state (convolution histories, transposed-convolution partials, transformer KV and position)
+ * and activations live in one caller-allocated block, 256-byte aligned, zeroed once. */
+int32_t vuib_codec_workspace_bytes(VuibCodec* c, size_t* bytes);
+int32_t vuib_codec_bind_workspace(VuibCodec* c, void* dev, size_t bytes);
+int32_t vuib_codec_bind_weights(VuibCodec* c, const VuibCodecWeights* w);
+/* Fresh streaming state: what entering decoder.streaming(1) / reset_streaming() does to every
+ * StreamingModule (qwen_codec.py:74-90, 122-138, 1011-1032).  Async on `stream`. */
+int32_t vuib_codec_reset(VuibCodec* c, void* stream);
+/* One frame: codes_dev int64[n_q] (n_q <= 16: fewer codebooks decode coarser audio, engine.py:1544-1545),
+ * audio_out_dev float[1920], clamped to [-1, 1].  Advances the streaming state.  Capturable in a graph. */
+int32_t vuib_codec_decode_frame(VuibCodec* c, const int64_t* codes_dev, int32_t n_q, float* audio_out_dev,
+                                void* stream);
+/* Frames decoded since the last reset (= next transformer position).  Synchronises `stream`. */
+int32_t vuib_codec_position(VuibCodec* c, int32_t* pos, void* stream);
+/* Reads and clears the codec's device flag (code outside [0, 2048), position beyond max_seq: both are
+ * clamped, never dereferenced).  Synchronises `stream`. */
+int32_t vuib_codec_check_flag(VuibCodec* c, void* stream);
+/* Intermediate activations of the last frame, for parity tests: which = 0 quantizer output (512),
+ * 1 transformer output (1024), 2 upsampled latent (1024 x 4), 3 decoder.0 output (1536 x 4),
+ * 4..7 output of decoder block 1..4 (C x T).  Copies n floats to out_host.  Synchronous. */
+int32_t vuib_codec_read_tap(VuibCodec* c, int32_t which, float* out_host, int32_t n, void* stream);
+int64_t vuib_codec_launch_count(VuibCodec* c);
+
 #ifdef __cplusplus
 }
 #endif

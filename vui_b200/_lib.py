@@ -20,6 +20,7 @@ _API_H = os.path.join(_ROOT, "include", "vuib200.h")
 # translation unit -> the headers it includes (a unit is recompiled when one of them changes)
 UNITS = {
     "vuib200.cu": ["decode_kernels.cuh", "tc_gemm.cuh", "fused_blocks.cuh", "depth_group.cuh", "prefill_attn.cuh"],
+    "codec.cu": ["codec_kernels.cuh"],
 }
 SOURCES = [os.path.join(_CSRC, u) for u in UNITS]
 HEADERS = sorted({os.path.join(_CSRC, h) for hs in UNITS.values() for h in hs}) + [_API_H]
@@ -68,6 +69,54 @@ class VuibSampling(C.Structure):
     ]
 
 
+VUIB_CODEC_LAYERS, VUIB_CODEC_STAGES, VUIB_CODEC_BLOCKS = 8, 2, 4
+_F = C.c_void_p  # const float* on the device
+
+
+class VuibCodecConfig(C.Structure):
+    _fields_ = [
+        ("n_q", C.c_int32), ("codebook_size", C.c_int32), ("codebook_dim", C.c_int32), ("vq_dim", C.c_int32),
+        ("latent_dim", C.c_int32), ("d_model", C.c_int32), ("n_layers", C.c_int32), ("n_heads", C.c_int32),
+        ("mlp_dim", C.c_int32), ("max_seq", C.c_int32), ("decoder_dim", C.c_int32),
+        ("rates", C.c_int32 * VUIB_CODEC_BLOCKS), ("norm_eps", C.c_float),
+    ]
+
+
+class VuibSnakeW(C.Structure):
+    _fields_ = [("ea", _F), ("ib", _F)]
+
+
+class VuibConvW(C.Structure):
+    _fields_ = [("w", _F), ("b", _F)]
+
+
+class VuibCodecLayerW(C.Structure):
+    _fields_ = [("ln1", _F), ("wqkv", _F), ("wo", _F), ("attn_scale", _F), ("ln2", _F), ("gate", _F), ("up", _F),
+                ("down", _F), ("mlp_scale", _F)]
+
+
+class VuibUpStageW(C.Structure):
+    _fields_ = [("up", VuibConvW), ("dw", VuibConvW), ("ln_w", _F), ("ln_b", _F), ("pw1", VuibConvW),
+                ("pw2", VuibConvW), ("gamma", _F)]
+
+
+class VuibResUnitW(C.Structure):
+    _fields_ = [("act1", VuibSnakeW), ("conv1", VuibConvW), ("act2", VuibSnakeW), ("conv2", VuibConvW)]
+
+
+class VuibDecBlockW(C.Structure):
+    _fields_ = [("act", VuibSnakeW), ("up", VuibConvW), ("res", VuibResUnitW * 3)]
+
+
+class VuibCodecWeights(C.Structure):
+    _fields_ = [
+        ("codebook", _F * 16), ("sem_proj", _F), ("acq_proj", _F), ("pre_conv", VuibConvW), ("in_proj", VuibConvW),
+        ("layer", VuibCodecLayerW * VUIB_CODEC_LAYERS), ("norm", _F), ("out_proj", VuibConvW),
+        ("rope_cos", _F), ("rope_sin", _F), ("stage", VuibUpStageW * VUIB_CODEC_STAGES), ("dec_in", VuibConvW),
+        ("block", VuibDecBlockW * VUIB_CODEC_BLOCKS), ("final_act", VuibSnakeW), ("final_conv", VuibConvW),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/vuib200.h declares
 _P = C.c_void_p
 SYMBOLS = {
@@ -105,6 +154,18 @@ SYMBOLS = {
     "vuib_get_seq_len": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_int32)]),
     "vuib_check_device_flag": (C.c_int32, [_P, _P]),
     "vuib_launch_count": (C.c_int64, [_P]),
+    "vuib_codec_create": (C.c_int32, [C.POINTER(VuibCodecConfig), C.POINTER(_P)]),
+    "vuib_codec_destroy": (C.c_int32, [_P]),
+    "vuib_codec_last_error": (C.c_int32, [_P, C.c_char_p, C.c_size_t]),
+    "vuib_codec_workspace_bytes": (C.c_int32, [_P, C.POINTER(C.c_size_t)]),
+    "vuib_codec_bind_workspace": (C.c_int32, [_P, _P, C.c_size_t]),
+    "vuib_codec_bind_weights": (C.c_int32, [_P, C.POINTER(VuibCodecWeights)]),
+    "vuib_codec_reset": (C.c_int32, [_P, _P]),
+    "vuib_codec_decode_frame": (C.c_int32, [_P, _P, C.c_int32, _P, _P]),
+    "vuib_codec_position": (C.c_int32, [_P, C.POINTER(C.c_int32), _P]),
+    "vuib_codec_check_flag": (C.c_int32, [_P, _P]),
+    "vuib_codec_read_tap": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_float), C.c_int32, _P]),
+    "vuib_codec_launch_count": (C.c_int64, [_P]),
 }
 
 

@@ -8,9 +8,9 @@ What differs is underneath: one decode frame - backbone step, cb0 sampling, the
 one captured CUDA graph of hand-written sm_100a kernels, with no host round trip
 inside the frame and one device->host read (codes + EOS probability) after it.
 
-The codec that turns codes into audio is not part of this package: pass a
-``codec`` object (``decode(codes_bqt)``, optionally ``setup_streaming_graph`` and a
-``CodecCtx``-style streaming decoder) or work with codes only.
+The codec that turns codes into audio is ``vui_b200.codec.QwenCodecDecoder`` (the streaming decode on
+this library's own kernels); pass it, or any object with ``decode(codes_bqt)`` and ``new_ctx()``, as
+``codec=``, or work with codes only.
 """
 
 from __future__ import annotations
@@ -1057,6 +1057,11 @@ class Engine:
                 self._apply_cfg(cfg)
 
     def _stream_row(self, row, text, cfg, cancel=None, *, reset_rep=True, final_turn=False):
+        # seed the codec once per session from the buffered prompt codes (engine.py:1349-1356); later calls
+        # keep the streaming state and start cold at the 10 s boundary inside decode_frame
+        ctx = row._codec_ctx
+        if ctx is not None and hasattr(ctx, "prefill") and getattr(ctx, "_stack", True) is None:
+            ctx.prefill(n_codebooks=cfg.n_codebooks)
         for codes in self._stream_codes(row, text, cfg, cancel, reset_rep=reset_rep, final_turn=final_turn):
             yield self._stream_decode_frame(codes.to(self.device), cfg.n_codebooks)
 
