@@ -14,7 +14,9 @@ Beside the headline the same line carries
   streams64   configuration 3: 64 streams, prompts U[64,512], T=0.8 top-k 50;
   cfg4        configuration 4: 16 streams x (128 text ids + 125 codec frames): prefill
               tokens/s, time to first frame, 375 greedy frames;
-  streams256  configuration 5's per-GPU shape: 256 streams, 512-id prompts, 2048-position KV.
+  streams256  configuration 5's per-GPU shape: 256 streams, 512-id prompts, 2048-position KV;
+  codec       the step after the path: streaming codec decode of one stream's frames (16 codes ->
+              1920 samples, fp32), ms per frame, x realtime, HBM roofline on its 423 MB of weights.
 
 Under torchrun (N > 1) every rank is an independent replica with its own streams
 on its own GPU; there is no data-path collective, the process group only aligns
@@ -23,7 +25,7 @@ the timed window and takes the max time over ranks.
 `--impl reference` times the CPU restatement of the reference's PyTorch path
 (oracle/, fp32, all host threads) on the same metric.  `--profile-frames N` runs N
 frames kernel by kernel (no graph) and exits: the command the ncu summaries under
-profiles/ are taken with.
+profiles/ are taken with; `--profile-codec N` does the same for N streamed codec frames.
 """
 
 from __future__ import annotations
@@ -398,6 +400,120 @@ class Bench:
         return res
 
 
+def codec_weight_bytes() -> int:
+    """Bytes of codec weights one frame touches: every decoder tensor once, except the quantizer's encoder-side
+    input projections (unused when decoding) and the codebooks, of which one 1 KiB row each is gathered."""
+    from vui_b200.codec import codec_param_shapes
+
+    n = 0
+    for name, shape in codec_param_shapes().items():
+        if name.endswith("input_proj.weight") and name.startswith("quantizer."):
+            continue
+        if name.endswith(".embed"):
+            n += 256
+            continue
+        k = 1
+        for d in shape:
+            k *= d
+        n += k
+    return 4 * n
+
+
+def codec_block(dev, cpu_baseline: bool, frames: int = 100, reps: int = 5):
+    """Streaming codec decode of one stream: `frames` consecutive frames per block (transformer positions
+    10..10+frames), median block; device-resident codes for `ms_per_frame`, pinned host codes in and audio out
+    every frame for `e2e`."""
+    import torch
+
+    from vui_b200.codec import QwenCodecDecoder
+
+    dec = QwenCodecDecoder.random_init(0, device=dev)
+    dec.setup_streaming_graph()
+    g = dec._graph_for(16)
+    codes = torch.randint(0, 2048, (16, 10 + frames), generator=torch.Generator().manual_seed(5)).to(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blocks = []
+    for _ in range(reps):
+        with dec.streaming(1):
+            for t in range(10):
+                dec._codes_in.copy_(codes[:, t])
+                g.replay()
+            torch.cuda.synchronize(dev)
+            e0.record()
+            for t in range(10, 10 + frames):
+                dec._codes_in.copy_(codes[:, t])
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            blocks.append(e0.elapsed_time(e1))
+    ms = statistics.median(blocks) / frames
+    # end to end: host codes -> device, replay, audio -> host, every frame
+    h_codes = codes.cpu().pin_memory()
+    h_audio = torch.empty(1920, dtype=torch.float32).pin_memory()
+    with dec.streaming(1):
+        t0 = None
+        for t in range(10 + frames):
+            if t == 10:
+                torch.cuda.synchronize(dev)
+                t0 = time.perf_counter()
+            dec._codes_in.copy_(h_codes[:, t], non_blocking=True)
+            g.replay()
+            h_audio.copy_(dec._audio, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+        e2e_ms = 1e3 * (time.perf_counter() - t0) / frames
+    dec.check_device()
+    wbytes = codec_weight_bytes()
+    kv = 8 * 16 * 64 * 4 * 2 * (10 + frames / 2)
+    peak, _ = measured_hbm_peak()
+    res = {
+        "workload": "streaming codec decode, one stream, 16 codebooks, fp32, seeded random weights; "
+                    f"{frames} consecutive frames per block, median of {reps} blocks",
+        "ms_per_frame": ms, "frames_per_s": 1e3 / ms, "x_realtime": 1e3 / ms / FRAME_RATE,
+        "e2e_ms_per_frame": e2e_ms, "h2d_bytes_per_frame": 128, "d2h_bytes_per_frame": 7680,
+        "launches_per_frame": 87, "weight_bytes_per_frame": wbytes,
+        "roofline_frac": (wbytes + kv) / (ms * 1e-3) / 1e9 / peak,
+    }
+    if cpu_baseline:
+        from oracle.codec_oracle import CodecOracle
+        from vui_b200.codec import random_codec_state
+
+        torch.set_num_threads(os.cpu_count() or 1)
+        orc = CodecOracle(random_codec_state(0))
+        cc = codes.cpu()
+        for t in range(2):
+            orc.decode(cc[None, :, t:t + 1])
+        t0 = time.perf_counter()
+        for t in range(2, 12):
+            orc.decode(cc[None, :, t:t + 1])
+        cpu_ms = 1e3 * (time.perf_counter() - t0) / 10
+        res["cpu_baseline"] = {"value": 1e3 / cpu_ms, "unit": "frames/s", "cores": os.cpu_count() or 1, "kind": "port",
+                               "sample": "10 streamed frames, oracle/codec_oracle.py fp32 on torch CPU"}
+    del dec
+    torch.cuda.empty_cache()
+    return res
+
+
+def profile_codec(dev, n):
+    """`n` streamed codec frames kernel by kernel (no graph) after 3 warm-up frames: for ncu."""
+    import torch
+
+    from vui_b200.codec import QwenCodecDecoder
+
+    dec = QwenCodecDecoder.random_init(0, device=dev)
+    codes = torch.randint(0, 2048, (1, 16, 3 + n), generator=torch.Generator().manual_seed(5)).to(dev)
+    with dec.streaming(1):
+        for t in range(3):
+            dec(codes[:, :, t:t + 1])
+        torch.cuda.synchronize(dev)
+        before = dec.launch_count()
+        for t in range(3, 3 + n):
+            dec(codes[:, :, t:t + 1])
+        torch.cuda.synchronize(dev)
+    dec.check_device()
+    print(json.dumps({"profile_codec": n, "launches_before_frames": before,
+                      "launches_per_frame": (dec.launch_count() - before) // max(n, 1)}), flush=True)
+
+
 def profile_frames(model, dev, n, B, prompt_len):
     """Prefill B streams of `prompt_len` ids, then `n` frames kernel by kernel (no graph): the command the
     `ncu` launch lists and captures under profiles/ are taken with."""
@@ -438,6 +554,9 @@ def run_b200(args):
 
     from vui_b200 import VuiB200, VuiShape
 
+    if args.profile_codec:
+        profile_codec(dev, args.profile_codec)
+        return
     model = VuiB200.random_init(VuiShape(), seed=0, device=dev)
     if args.profile_frames:
         profile_frames(model, dev, args.profile_frames, args.streams, args.prompt_len)
@@ -455,7 +574,12 @@ def run_b200(args):
     K = min(K, ceiling - max(lens) - W - 40)
     max_seq = min(max_seq, ceiling)
     m = b.decode(B, K, W, args.reps, lens, args.sample, max_seq, clocks=True, phases=True)
-    extra = cfg4 = wide = standin_ms = None
+    extra = cfg4 = wide = standin_ms = codec = None
+    if B == 1 and not args.no_batched and rank == 0:
+        try:
+            codec = codec_block(dev, world == 1 and not args.no_cpu_baseline)
+        except Exception as exc:  # noqa: BLE001 - an extra block must never take the bench line down
+            print(f"codec block failed: {exc}", file=sys.stderr)
     if B == 1 and not args.no_batched:
         lens64 = torch.randint(64, 513, (64,), generator=torch.Generator().manual_seed(1)).tolist()
         k64 = min(K, 100)
@@ -531,6 +655,8 @@ def run_b200(args):
                 }
         if cfg4 is not None:
             line["cfg4"] = cfg4
+        if codec is not None:
+            line["codec"] = codec
         if wide is not None:
             ach = wide["step_bytes"] / (wide["ms_per_step"] * 1e-3) / 1e9
             line["streams256"] = {
@@ -562,6 +688,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-batched", action="store_true", help="skip the 64-stream, cfg4 and 256-stream blocks")
     ap.add_argument("--profile-frames", type=int, default=0, help="run N frames without a graph and exit (for ncu)")
+    ap.add_argument("--profile-codec", type=int, default=0, help="run N streamed codec frames without a graph and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -348,13 +348,17 @@ typedef struct VuibUpStageW {      /* upsample[i] = [CausalTransConv1d k=2 s=2, 
     VuibConvW pw2;            /* (1024, 4096), (1024) */
     const float* gamma;       /* (1024) */
 } VuibUpStageW;
+/* The tiled kernel wants a weight per tile of 96 output rows, K-major inside the tile:
+ * [rows / 96][C_in][taps][96], i.e. weight.view(rows / 96, 96, C_in, taps).permute(0, 2, 3, 1). */
 typedef struct VuibResUnitW {      /* DecoderResUnit (851-860) */
-    VuibSnakeW act1; VuibConvW conv1;   /* (C, C, 7), dilation 1 / 3 / 9 */
-    VuibSnakeW act2; VuibConvW conv2;   /* (C, C, 1) */
+    VuibSnakeW act1; VuibConvW conv1;   /* (C, C, 7) re-laid as above, dilation 1 / 3 / 9 */
+    VuibSnakeW act2; VuibConvW conv2;   /* (C, C, 1) re-laid as above */
 } VuibResUnitW;
 typedef struct VuibDecBlockW {     /* DecoderBlock (863-879) */
     VuibSnakeW act;
-    VuibConvW up;             /* w re-laid as rows (co, k): (Cout * 2 * rate, Cin) = weight.permute(1, 2, 0); b (Cout) */
+    VuibConvW up;             /* rows (co, k) = (Cout * 2 * rate) over Cin.  Block 0 (4 columns per frame, row kernel):
+                                 (rows, Cin) = weight.permute(1, 2, 0); blocks 1..3 (tiled kernel): re-laid as above with
+                                 one tap; b (Cout) */
     VuibResUnitW res[3];
 } VuibDecBlockW;
 typedef struct VuibCodecWeights {

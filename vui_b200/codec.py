@@ -211,6 +211,10 @@ class QwenCodecDecoder:
         def rows_of_transposed(wt: Tensor) -> Tensor:   # (Cin, Cout, K) -> rows (co, k) over ci
             return wt.permute(1, 2, 0).reshape(wt.shape[1] * wt.shape[2], wt.shape[0])
 
+        def tiles_of_rows(wt: Tensor) -> Tensor:        # (rows, Cin, taps) -> [rows / 96][Cin][taps][96]
+            rows, cin, taps = wt.shape
+            return wt.reshape(rows // 96, 96, cin, taps).permute(0, 2, 3, 1)
+
         w.codebook[0] = P(sd["quantizer.semantic.codebooks.0.embed"])
         for i in range(15):
             w.codebook[1 + i] = P(sd[f"quantizer.acoustic.codebooks.{i}.embed"])
@@ -246,11 +250,13 @@ class QwenCodecDecoder:
         for b in range(4):
             p, bw = f"decoder.{b + 1}.block.", w.block[b]
             bw.act = snake(p + "0")
-            bw.up = conv(p + "1.conv", rows_of_transposed)
+            # block 0 runs on the row kernel (rows (co, k) over ci); the others on the tiled kernel
+            bw.up = conv(p + "1.conv", rows_of_transposed if b == 0 else
+                         (lambda t: tiles_of_rows(rows_of_transposed(t).unsqueeze(-1))))
             for r in range(3):
                 q, rw = f"{p}{r + 2}.", bw.res[r]
-                rw.act1, rw.conv1 = snake(q + "act1"), conv(q + "conv1.conv")
-                rw.act2, rw.conv2 = snake(q + "act2"), conv(q + "conv2.conv", lambda t: t.reshape(t.shape[0], t.shape[1]))
+                rw.act1, rw.conv1 = snake(q + "act1"), conv(q + "conv1.conv", tiles_of_rows)
+                rw.act2, rw.conv2 = snake(q + "act2"), conv(q + "conv2.conv", tiles_of_rows)
         w.final_act = snake("decoder.5")
         w.final_conv = conv("decoder.6.conv", lambda t: t.reshape(t.shape[1], 7))
         return w

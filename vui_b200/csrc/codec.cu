@@ -21,12 +21,16 @@ constexpr int UP_T[3] = {1, 2, 4};   // columns per frame before / after each x2
 
 struct ConvState { size_t off; int elems; };   // [2][elems] floats at ws + off
 
+// activated input of a k = 7 convolution: [2 parities][C][ld], P history columns in front (codec_kernels.cuh)
+struct PadBuf { size_t off; int ld, P; long long pstride; };
+
 struct Layout {
-    size_t ctr, tile_ctr, state_lo, state_hi;   // [state_lo, state_hi) is what a reset zeroes (with ctr, tile_ctr)
-    ConvState pre_conv, dw[2], dec_in, res[4][3], fin;
+    size_t ctr, tile_ctr, state_lo, state_hi;   // [0, state_hi) is what a reset zeroes
+    ConvState pre_conv, dw[2], dec_in;
+    PadBuf res_in[4][3], fin_in;                // inputs of the residual units' first convolutions, of the last conv
     size_t partial[4];                          // transposed-convolution partials [Cout][rate]
     size_t kc, vc;                              // [layers][heads][max_seq][64]
-    size_t h0, y1, x, qkv, attn, g, lat, u[2], z, a4, d0, p, y[4], r1, part, audio_pad;
+    size_t h0, y1, x, qkv, attn, g, lat, u[2], z, a4, d0, p, y[4], ya[4], r1, part;
     size_t total;
     int C[5], T[5];                             // channels / columns after decoder.0 and after each block
 };
@@ -91,16 +95,22 @@ size_t take(size_t& cur, size_t bytes) {
     return o;
 }
 
-// K-split of a tiled convolution: enough CTAs for every SM, whole staging steps (8 channels) per split
-void pick_split(int Cin, int Cout, int T, int cot, int* splits, int* ci_per_split) {
-    int tiles = ((T + 31) / 32) * ((Cout + cot - 1) / cot);
-    int want = (200 + tiles - 1) / tiles;
-    int max_s = Cin / 16 > 0 ? Cin / 16 : 1;
+// K-split of a tiled convolution: about two CTAs per SM, whole staging steps per split, at most 16 splits
+void pick_split(int Cin, int Cout, int T, int cc, int* splits, int* ci_per_split) {
+    int tiles = ((T + CT_T - 1) / CT_T) * (Cout / CT_CO);
+    int want = (296 + tiles - 1) / tiles;
+    int max_s = Cin / cc < 16 ? Cin / cc : 16;   // the last-arriving CTA adds the partial tiles one after the other
     if (want > max_s) want = max_s;
     if (want < 1) want = 1;
-    int per = ((Cin + want - 1) / want + 7) / 8 * 8;
+    int per = ((Cin + want - 1) / want + cc - 1) / cc * cc;
     *ci_per_split = per;
     *splits = (Cin + per - 1) / per;
+}
+
+int part_floats(int Cin, int Cout, int T, int cc) {
+    int s, per;
+    pick_split(Cin, Cout, T, cc, &s, &per);
+    return s > 1 ? s * ((T + CT_T - 1) / CT_T) * (Cout / CT_CO) * CT_CO * CT_T : 0;
 }
 
 void make_layout(VuibCodec* c) {
@@ -116,15 +126,23 @@ void make_layout(VuibCodec* c) {
     L.tile_ctr = take(cur, 4096 * sizeof(int));
     L.state_lo = cur;
     auto st = [&](int elems) { ConvState s{take(cur, 2 * (size_t)elems * 4), elems}; return s; };
+    auto padbuf = [&](int C, int T, int P) {
+        PadBuf b;
+        b.P = P;
+        b.ld = (P + T + 3) / 4 * 4 + 4;
+        b.pstride = (long long)C * b.ld;
+        b.off = take(cur, 2 * (size_t)b.pstride * 4);
+        return b;
+    };
     L.pre_conv = st(g.vq_dim * 2);
     for (int i = 0; i < 2; ++i) L.dw[i] = st(lat * 6);
     L.dec_in = st(lat * 6);
     const int dil[3] = {1, 3, 9};
     for (int b = 0; b < 4; ++b) {
         L.partial[b] = take(cur, (size_t)L.C[b + 1] * g.rates[b] * 4);
-        for (int r = 0; r < 3; ++r) L.res[b][r] = st(L.C[b + 1] * 6 * dil[r]);
+        for (int r = 0; r < 3; ++r) L.res_in[b][r] = padbuf(L.C[b + 1], L.T[b + 1], 6 * dil[r]);
     }
-    L.fin = st(L.C[4] * 6);
+    L.fin_in = padbuf(L.C[4], L.T[4], 6);
     L.state_hi = cur;
     size_t kv = (size_t)g.n_layers * g.n_heads * g.max_seq * HD * 4;
     L.kc = take(cur, kv);
@@ -142,28 +160,24 @@ void make_layout(VuibCodec* c) {
     L.a4 = take(cur, (size_t)lat * 4 * 4 * 4);
     L.d0 = take(cur, (size_t)L.C[0] * L.T[0] * 4);
     size_t pmax = 0, ymax = 0;
-    int part_max = 0;
+    int part_max = 1;
     for (int b = 0; b < 4; ++b) {
-        size_t rows = (size_t)L.C[b + 1] * 2 * g.rates[b];
+        const int C = L.C[b + 1], T = L.T[b + 1];
+        size_t rows = (size_t)C * 2 * g.rates[b];
         if (rows * L.T[b] > pmax) pmax = rows * L.T[b];
-        L.y[b] = take(cur, (size_t)L.C[b + 1] * L.T[b + 1] * 4);
-        if ((size_t)L.C[b + 1] * L.T[b + 1] > ymax) ymax = (size_t)L.C[b + 1] * L.T[b + 1];
-        // partial-tile scratch of the K-split convolutions of this block
-        int C = L.C[b + 1], T = L.T[b + 1], cot = (C % 64 == 0) ? 64 : 32, s, per;
-        pick_split(C, C, T, cot, &s, &per);
-        int tiles = ((T + 31) / 32) * ((C + cot - 1) / cot);
-        if (s > 1 && s * tiles * cot * 32 > part_max) part_max = s * tiles * cot * 32;
-        if (b > 0) {
-            int rws = C * 2 * g.rates[b], cot2 = (rws % 64 == 0) ? 64 : 32;
-            pick_split(L.C[b], rws, L.T[b], cot2, &s, &per);
-            tiles = ((L.T[b] + 31) / 32) * ((rws + cot2 - 1) / cot2);
-            if (s > 1 && s * tiles * cot2 * 32 > part_max) part_max = s * tiles * cot2 * 32;
-        }
+        L.y[b] = take(cur, (size_t)C * T * 4);
+        L.ya[b] = take(cur, (size_t)C * T * 4);     // activated copy for the next block's transposed convolution
+        if ((size_t)C * T > ymax) ymax = (size_t)C * T;
+        int p7 = part_floats(C, C, T, 8), p1 = part_floats(C, C, T, 32);
+        int pt = b > 0 ? part_floats(L.C[b], (int)rows, L.T[b], 32) : 0;
+        if (p7 > part_max) part_max = p7;
+        if (p1 > part_max) part_max = p1;
+        if (pt > part_max) part_max = pt;
     }
     L.p = take(cur, pmax * 4);
     L.r1 = take(cur, ymax * 4);
-    c->max_part_floats = part_max > 0 ? part_max : 1;
-    L.part = take(cur, (size_t)c->max_part_floats * 4);
+    c->max_part_floats = part_max;
+    L.part = take(cur, (size_t)part_max * 4);
     L.total = cur;
 }
 
@@ -176,9 +190,14 @@ void make_layout(VuibCodec* c) {
 
 // ---- launch helpers ---------------------------------------------------------------------------
 template <int KW, int T, bool DUAL>
-cudaError_t rows_launch(VuibCodec* c, const RowsArgs& a, cudaStream_t s) {
-    int per_cta = 8, grid = (a.rows + per_cta - 1) / per_cta;
-    if (grid > 296) grid = 296;
+cudaError_t rows_launch(VuibCodec* c, RowsArgs a, cudaStream_t s) {
+    // enough warps for every SM: S warps share a row while rows * S is short of ~16 warps per SM
+    const int k4 = a.Cin * KW / 4;
+    int S = 1;
+    while (S < 8 && a.rows * S < 2368 && k4 % (64 * S) == 0) S *= 2;
+    a.ksplit = S;
+    int rpp = 8 / S, grid = (a.rows + rpp - 1) / rpp;
+    if (grid > 592) grid = 592;
     size_t smem = (size_t)a.Cin * (KW == 1 ? T : (KW - 1 + T)) * 4;
     return launch(c, k_crows<KW, T, DUAL>, dim3(grid), dim3(256), smem, s, a);
 }
@@ -203,25 +222,34 @@ RowsArgs rows_args(VuibCodec* c, const float* w, const float* bias, const float*
     return a;
 }
 
-cudaError_t tile(VuibCodec* c, int KW, const float* w, const float* bias, const float* x, const ConvState* st,
-                 const VuibSnakeW* act, const float* res, float* y, int Cin, int Cout, int T, int dil,
-                 cudaStream_t s) {
+struct TileIn { const float* xa; long long pstride; int ld, P; };
+
+TileIn plain_in(const float* x, int T) { return TileIn{x, 0, T, 0}; }
+TileIn pad_in(VuibCodec* c, const PadBuf& b) { return TileIn{wsp<float>(c, b.off), b.pstride, b.ld, b.P}; }
+
+ActOut act_into_pad(VuibCodec* c, const PadBuf& b, const VuibSnakeW& a) {
+    return ActOut{wsp<float>(c, b.off), b.pstride, b.ld, b.P, a.ea, a.ib};
+}
+ActOut act_into_plain(float* dst, int T, const VuibSnakeW& a) { return ActOut{dst, 0, T, 0, a.ea, a.ib}; }
+
+cudaError_t tile(VuibCodec* c, int KW, const float* wt, const float* bias, TileIn in, const float* res, float* y,
+                 ActOut act, int Cin, int Cout, int T, int dil, cudaStream_t s) {
+    const int cc = KW == 1 ? 32 : 8;
+    if (Cout % CT_CO || Cin % cc || T % 4 || in.ld % 4) return cudaErrorInvalidValue;
     TileArgs a = {};
-    a.w = w; a.bias = bias; a.x = x; a.res = res; a.y = y;
-    a.state = st ? wsp<float>(c, st->off) : nullptr;
-    a.ea = act ? act->ea : nullptr; a.ib = act ? act->ib : nullptr;
+    a.wt = wt; a.bias = bias; a.xa = in.xa; a.x_pstride = in.pstride; a.x_ld = in.ld; a.P = in.P;
+    a.res = res; a.y = y; a.act = act;
     a.part = wsp<float>(c, c->lay.part); a.tile_ctr = wsp<int>(c, c->lay.tile_ctr);
     a.ctr = wsp<int>(c, c->lay.ctr);
-    a.Cin = Cin; a.Cout = Cout; a.T = T; a.dil = dil; a.pad = (KW - 1) * dil;
-    const int cot = (Cout % 64 == 0) ? 64 : 32;
-    pick_split(Cin, Cout, T, cot, &a.splits, &a.ci_per_split);
-    dim3 grid((T + 31) / 32, (Cout + cot - 1) / cot, a.splits);
-    if ((int)(grid.x * grid.y) > 4096 || (a.splits > 1 && (int)(a.splits * grid.x * grid.y * cot * 32) > c->max_part_floats))
+    a.Cin = Cin; a.Cout = Cout; a.T = T; a.dil = dil;
+    pick_split(Cin, Cout, T, cc, &a.splits, &a.ci_per_split);
+    dim3 grid((T + CT_T - 1) / CT_T, Cout / CT_CO, a.splits);
+    if ((int)(grid.x * grid.y) > 4096 ||
+        (a.splits > 1 && (int)(a.splits * grid.x * grid.y * CT_CO * CT_T) > c->max_part_floats) ||
+        in.P != (KW - 1) * dil)
         return cudaErrorInvalidValue;
-    if (KW == 7 && cot == 64) return launch(c, k_ctile<7, 64>, grid, dim3(128), 0, s, a);
-    if (KW == 7 && cot == 32) return launch(c, k_ctile<7, 32>, grid, dim3(128), 0, s, a);
-    if (KW == 1 && cot == 64) return launch(c, k_ctile<1, 64>, grid, dim3(128), 0, s, a);
-    if (KW == 1 && cot == 32) return launch(c, k_ctile<1, 32>, grid, dim3(128), 0, s, a);
+    if (KW == 7) return launch(c, k_ctile<7>, grid, dim3(CT_THREADS), ct_smem_bytes<7>(), s, a);
+    if (KW == 1) return launch(c, k_ctile<1>, grid, dim3(CT_THREADS), ct_smem_bytes<1>(), s, a);
     return cudaErrorInvalidValue;
 }
 
@@ -447,8 +475,9 @@ extern "C" int32_t vuib_codec_decode_frame(VuibCodec* c, const int64_t* codes_de
         a.state = wsp<float>(c, L.dec_in.off);
         CK(rows(c, 7, 4, a, s));
     }
-    cur = wsp<float>(c, L.d0);
+    cur = wsp<float>(c, L.d0);   // not activated: the first block's row kernel applies its SnakeBeta while staging
     const int dil[3] = {1, 3, 9};
+    const ActOut no_act = {};
     for (int b = 0; b < 4; ++b) {
         const VuibDecBlockW& bw = w.block[b];
         const int Cin = L.C[b], Cout = L.C[b + 1], Tin = L.T[b], Tout = L.T[b + 1], rate = g.rates[b];
@@ -456,31 +485,38 @@ extern "C" int32_t vuib_codec_decode_frame(VuibCodec* c, const int64_t* codes_de
         float* p = wsp<float>(c, L.p);
         float* y = wsp<float>(c, L.y[b]);
         float* r1 = wsp<float>(c, L.r1);
-        if (Tin <= 4) {
+        if (b == 0) {
             RowsArgs a = rows_args(c, bw.up.w, nullptr, cur, Tin, 1, Cin, prow, p, Tin, 1);
             a.pro = PRO_SNAKE; a.p0 = bw.act.ea; a.p1 = bw.act.ib;
             CK(rows(c, 1, Tin, a, s));
-        } else {
-            CK(tile(c, 1, bw.up.w, nullptr, cur, nullptr, &bw.act, nullptr, p, Cin, prow, Tin, 1, s));
+        } else {   // the previous block left its output activated in ya[b - 1]
+            CK(tile(c, 1, bw.up.w, nullptr, plain_in(wsp<float>(c, L.ya[b - 1]), Tin), nullptr, p, no_act, Cin, prow, Tin,
+                    1, s));
         }
         {
             OlaArgs a = {};
             a.p = p; a.bias = bw.up.b; a.partial = wsp<float>(c, L.partial[b]); a.y = y;
+            a.act = act_into_pad(c, L.res_in[b][0], bw.res[0].act1); a.ctr = ctr;
             a.Cout = Cout; a.s = rate; a.Tin = Tin;
             CK(launch(c, k_overlap_add, dim3((Cout * Tout + 255) / 256), dim3(256), 0, s, a));
         }
         for (int r = 0; r < 3; ++r) {
             const VuibResUnitW& rw = bw.res[r];
-            CK(tile(c, 7, rw.conv1.w, rw.conv1.b, y, &L.res[b][r], &rw.act1, nullptr, r1, Cout, Cout, Tout, dil[r], s));
-            CK(tile(c, 1, rw.conv2.w, rw.conv2.b, r1, nullptr, &rw.act2, y, y, Cout, Cout, Tout, 1, s));
+            // conv1: activated padded input -> r1 = act2(conv1(...)), only the activated form is needed
+            CK(tile(c, 7, rw.conv1.w, rw.conv1.b, pad_in(c, L.res_in[b][r]), nullptr, nullptr,
+                    act_into_plain(r1, Tout, rw.act2), Cout, Cout, Tout, dil[r], s));
+            // conv2: y += conv2(r1); the activated copy goes to whoever consumes y next
+            ActOut nxt = r < 2   ? act_into_pad(c, L.res_in[b][r + 1], bw.res[r + 1].act1)
+                         : b < 3 ? act_into_plain(wsp<float>(c, L.ya[b]), Tout, w.block[b + 1].act)
+                                 : act_into_pad(c, L.fin_in, w.final_act);
+            CK(tile(c, 1, rw.conv2.w, rw.conv2.b, plain_in(r1, Tout), y, y, nxt, Cout, Cout, Tout, 1, s));
         }
-        cur = y;
     }
     {
         FinalArgs a = {};
-        a.x = cur; a.w = w.final_conv.w; a.bias = w.final_conv.b; a.ea = w.final_act.ea; a.ib = w.final_act.ib;
-        a.state = wsp<float>(c, L.fin.off); a.ctr = ctr; a.audio = audio_out_dev; a.C = L.C[4]; a.T = L.T[4];
-        CK(launch(c, k_final_conv, dim3((a.T + 63) / 64), dim3(64), (size_t)a.C * 70 * 4, s, a));
+        a.xa = wsp<float>(c, L.fin_in.off); a.x_pstride = L.fin_in.pstride; a.x_ld = L.fin_in.ld;
+        a.w = w.final_conv.w; a.bias = w.final_conv.b; a.ctr = ctr; a.audio = audio_out_dev; a.C = L.C[4]; a.T = L.T[4];
+        CK(launch(c, k_final_conv, dim3((a.T + 31) / 32), dim3(128), 0, s, a));
     }
     CK(launch(c, k_advance, dim3(1), dim3(32), 0, s, ctr));
     return VUIB_OK;

@@ -15,8 +15,9 @@
 //   k_crows : a warp per output row streams that row's weights once (HBM bound;
 //             all columns of the frame share the pass); prologues RMSNorm / SnakeBeta,
 //             epilogues bias / GELU / layer-scale + residual / SiLU-gate / scatter.
-//   k_ctile : register-tiled (co x t) convolution with dilation for the long stages,
-//             K split over CTAs with an ordered last-arriver reduction.
+//   k_ctile : register-tiled (co x t) convolution with dilation for the long stages: a cp.async
+//             ring of K-major weight slabs and input windows, K split over CTAs with an ordered
+//             last-arriver reduction; its input was activated (SnakeBeta) by the producing kernel.
 // Streaming state is double-buffered by frame parity (read [parity], write
 // [parity ^ 1]) so no CTA can overwrite history another CTA still reads.
 #pragma once
@@ -30,6 +31,7 @@ constexpr int CTR_POS = 1;     // next transformer position
 constexpr int CTR_FLAG = 2;    // sticky error bits
 constexpr int FLAG_BAD_CODE = 1;
 constexpr int FLAG_POS_OVERFLOW = 2;
+constexpr int FLAG_WAIT = 4;        // a bounded wait on an asynchronous copy ran out
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -76,16 +78,20 @@ __global__ void __launch_bounds__(256) k_cq_embed(EmbedArgs a) {
     pdl_wait();
     pdl_launch();
     int c = threadIdx.x;
-    float sem = 0.f, acq = 0.f;
-    for (int q = 0; q < a.n_q; ++q) {
-        long long code = a.codes[q];
-        if (code < 0 || code >= 2048) {
-            if (c == 0) atomicOr(a.ctr + CTR_FLAG, FLAG_BAD_CODE);
-            code = code < 0 ? 0 : 2047;
-        }
-        float v = a.table[q][code * 256 + c];
-        if (q == 0) sem += v; else acq += v;
-    }
+    long long code[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) code[q] = q < a.n_q ? a.codes[q] : 0;
+    bool bad = false;
+#pragma unroll
+    for (int q = 0; q < 16; ++q)
+        if (code[q] < 0 || code[q] >= 2048) { bad = true; code[q] = code[q] < 0 ? 0 : 2047; }
+    if (bad && c == 0) atomicOr(a.ctr + CTR_FLAG, FLAG_BAD_CODE);
+    float v[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) v[q] = q < a.n_q ? __ldg(a.table[q] + code[q] * 256 + c) : 0.f;
+    float sem = v[0], acq = 0.f;
+#pragma unroll
+    for (int q = 1; q < 16; ++q) acq += v[q];     // codebook order, as the reference's running sum
     s_sem[c] = sem;
     s_acq[c] = acq;
     __syncthreads();
@@ -114,6 +120,7 @@ struct RowsArgs {
     float* state;         // [2][Cin * (KW-1)] history of the input, or null when KW == 1
     const int* ctr;
     int Cin, rows;
+    int ksplit;           // warps that share one row: 1, 2, 4 or 8 (Cin * KW / 4 divisible by 32 * ksplit)
     int pro;              // PRO_*
     const float* p0;      // RMSNorm weight | snake ea
     const float* p1;      // snake ib
@@ -130,6 +137,7 @@ template <int KW, int T, bool DUAL>
 __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
     extern __shared__ float xs[];   // KW == 1: [T][Cin];  KW > 1: [Cin][P], P = KW - 1 + T
     __shared__ float red[32];
+    __shared__ float ksum[8][2 * T];
     constexpr int PAD = KW - 1, P = PAD + T;
     pdl_wait();
     pdl_launch();
@@ -144,15 +152,25 @@ __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
         ss = block_sum(ss, red);
         float r = rsqrtf(ss / (float)Cin + a.eps);
         for (int c = tid; c < Cin; c += blockDim.x) xs[c] = (a.x[c * a.x_cs] * r) * a.p0[c];
+    } else if (KW == 1 && a.x_cs == 1 && a.pro == PRO_NONE) {
+        // time-major input: every column is a contiguous run of Cin floats
+        for (int t = 0; t < T; ++t) {
+            const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)t * a.x_ts);
+            float4* dst = reinterpret_cast<float4*>(xs + t * Cin);
+#pragma unroll 4
+            for (int i = tid; i < Cin / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+        }
     } else {
+#pragma unroll 4
         for (int i = tid; i < Cin * T; i += blockDim.x) {
             int c = (KW == 1) ? i % Cin : i / T, t = (KW == 1) ? i / Cin : i % T;
-            float v = a.x[c * a.x_cs + t * a.x_ts];
-            if (a.pro == PRO_SNAKE) v = snake(v, a.p0[c], a.p1[c]);
+            float v = __ldg(a.x + c * a.x_cs + t * a.x_ts);
+            if (a.pro == PRO_SNAKE) v = snake(v, __ldg(a.p0 + c), __ldg(a.p1 + c));
             if (KW == 1) xs[t * Cin + c] = v; else xs[c * P + PAD + t] = v;
         }
         if constexpr (KW > 1) {
             const float* hist = a.state + parity * Cin * PAD;
+#pragma unroll 4
             for (int i = tid; i < Cin * PAD; i += blockDim.x) xs[(i / PAD) * P + (i % PAD)] = hist[i];
         }
     }
@@ -163,34 +181,41 @@ __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
         for (int i = tid; i < Cin * PAD; i += blockDim.x) nxt[i] = xs[(i / PAD) * P + T + (i % PAD)];
     }
 
-    const int lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-    const int Kd = Cin * KW;
-    for (int row = blockIdx.x * nw + warp; row < a.rows; row += gridDim.x * nw) {
-        const float4* wr = reinterpret_cast<const float4*>(a.w + (size_t)row * Kd);
-        const float4* wr2 = DUAL ? reinterpret_cast<const float4*>(a.w2 + (size_t)row * Kd) : nullptr;
+    // S warps share a row (each a contiguous 1/S of K), 8 / S rows per pass; partial sums meet in shared memory
+    // and are added in warp order, so the result does not depend on timing.
+    const int lane = tid & 31, warp = tid >> 5;
+    const int S = a.ksplit, rpp = 8 / S, sub = warp % S;
+    const int Kd = Cin * KW, per4 = Kd / 4 / S;
+    for (int rowbase = blockIdx.x * rpp; rowbase < a.rows; rowbase += gridDim.x * rpp) {
+        const int row = rowbase + warp / S;
         float acc[T], acc2[T];
 #pragma unroll
         for (int t = 0; t < T; ++t) acc[t] = 0.f, acc2[t] = 0.f;
-#pragma unroll 4
-        for (int f4 = lane; f4 < Kd / 4; f4 += 32) {
-            float4 w4 = __ldg(wr + f4);
-            float4 u4 = DUAL ? __ldg(wr2 + f4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            const float we[4] = {w4.x, w4.y, w4.z, w4.w};
-            const float ue[4] = {u4.x, u4.y, u4.z, u4.w};
-            if (KW == 1) {
+        if (row < a.rows) {
+            const float4* wr = reinterpret_cast<const float4*>(a.w + (size_t)row * Kd) + sub * per4;
+            const float4* wr2 = DUAL ? reinterpret_cast<const float4*>(a.w2 + (size_t)row * Kd) + sub * per4 : nullptr;
+#pragma unroll 8
+            for (int f4 = lane; f4 < per4; f4 += 32) {
+                float4 w4 = __ldg(wr + f4);
+                float4 u4 = DUAL ? __ldg(wr2 + f4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float we[4] = {w4.x, w4.y, w4.z, w4.w};
+                const float ue[4] = {u4.x, u4.y, u4.z, u4.w};
+                const int g4 = sub * per4 + f4;
+                if (KW == 1) {
 #pragma unroll
-                for (int t = 0; t < T; ++t) {
-                    float4 x4 = *reinterpret_cast<const float4*>(xs + t * Cin + f4 * 4);
-                    acc[t] += we[0] * x4.x + we[1] * x4.y + we[2] * x4.z + we[3] * x4.w;
-                    if (DUAL) acc2[t] += ue[0] * x4.x + ue[1] * x4.y + ue[2] * x4.z + ue[3] * x4.w;
-                }
-            } else {
+                    for (int t = 0; t < T; ++t) {
+                        float4 x4 = *reinterpret_cast<const float4*>(xs + t * Cin + g4 * 4);
+                        acc[t] += we[0] * x4.x + we[1] * x4.y + we[2] * x4.z + we[3] * x4.w;
+                        if (DUAL) acc2[t] += ue[0] * x4.x + ue[1] * x4.y + ue[2] * x4.z + ue[3] * x4.w;
+                    }
+                } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    int idx = f4 * 4 + e, ci = idx / KW, j = idx - ci * KW;
-                    const float* xp = xs + ci * P + j;
+                    for (int e = 0; e < 4; ++e) {
+                        int idx = g4 * 4 + e, ci = idx / KW, j = idx - ci * KW;
+                        const float* xp = xs + ci * P + j;
 #pragma unroll
-                    for (int t = 0; t < T; ++t) acc[t] += we[e] * xp[t];
+                        for (int t = 0; t < T; ++t) acc[t] += we[e] * xp[t];
+                    }
                 }
             }
         }
@@ -199,7 +224,22 @@ __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
             acc[t] = warp_sum(acc[t]);
             if (DUAL) acc2[t] = warp_sum(acc2[t]);
         }
-        if (lane == 0) {
+        if (S > 1) {
+            __syncthreads();
+            if (lane == 0) {
+#pragma unroll
+                for (int t = 0; t < T; ++t) { ksum[warp][t] = acc[t]; if (DUAL) ksum[warp][T + t] = acc2[t]; }
+            }
+            __syncthreads();
+            if (lane == 0 && sub == 0) {
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    acc[t] = 0.f; acc2[t] = 0.f;
+                    for (int q = 0; q < S; ++q) { acc[t] += ksum[warp + q][t]; if (DUAL) acc2[t] += ksum[warp + q][T + t]; }
+                }
+            }
+        }
+        if (lane == 0 && sub == 0 && row < a.rows) {
             int g = row / a.row_div, r = row - g * a.row_div;
             float b = a.bias ? a.bias[g] : 0.f;
 #pragma unroll
@@ -335,112 +375,245 @@ __global__ void __launch_bounds__(256) k_dwconv_ln(DwLnArgs a) {
 }
 
 // ---------------------------------------------------------------- register-tiled convolution for long frames
-struct TileArgs {
-    const float* w;       // [Cout][Cin][KW]
-    const float* bias;    // [Cout] or null
-    const float* x;       // [Cin][T]
-    float* state;         // [2][Cin * pad] activated history, or null when pad == 0
-    const float* ea; const float* ib;   // SnakeBeta on the input, per input channel, or null
-    const float* res;     // [Cout][T] residual or null
-    float* y;             // [Cout][T]
-    float* part;          // [splits][tiles][COT * 32] partial tiles
-    int* tile_ctr;        // [tiles] arrival counters (zero between launches)
-    const int* ctr;
-    int Cin, Cout, T, dil, pad, splits, ci_per_split;
+// Activations that feed a convolution are stored ALREADY ACTIVATED by their producer (SnakeBeta applied once
+// per element, in the producer's epilogue), in a buffer the convolution can copy from without arithmetic:
+//   k = 1 : plain [C][T];
+//   k = 7 : [2 parities][C][ld] with the P = 6 * dilation history columns in front: column c < P is history,
+//           column P + t is this frame's t.  The frame of parity p reads buffer p; the convolution itself copies
+//           its last P columns into the history columns of buffer p ^ 1 for the next frame.
+struct ActOut {           // optional second output of a producer: snake(v) into a consumer's input buffer
+    float* base;          // parity-0 buffer (null: none)
+    long long pstride;    // elements between the two parity buffers (0: not double-buffered)
+    int ld, off;          // element (co, t) at base[parity * pstride + co * ld + off + t]
+    const float* ea; const float* ib;
 };
 
-// y[co][t] = bias[co] + sum_{ci, j} w[co][ci][j] * act(X)[ci][t + j * dil - pad]   (+ res[co][t])
-// grid (T / 32, ceil(Cout / COT), splits); 128 threads, each (COT / 16) x 4 outputs.
-template <int KW, int COT>
-__global__ void __launch_bounds__(128) k_ctile(TileArgs a) {
-    constexpr int CC = 8;                       // input channels per staging step
-    constexpr int CPT = COT / 16;               // output channels per thread
-    constexpr int WS = CC * KW + 1;             // padded row stride of the weight tile
-    constexpr int XW = 32 + (KW - 1) * 9;       // widest input window (dilation <= 9)
-    __shared__ float ws[COT * WS];
-    __shared__ float xw[CC * XW];
+__device__ __forceinline__ void act_store(const ActOut& o, int parity, int co, int t, float v) {
+    if (o.base) o.base[(size_t)parity * o.pstride + (size_t)co * o.ld + o.off + t] = snake(v, o.ea[co], o.ib[co]);
+}
+
+struct TileArgs {
+    const float* wt;      // weights per 96-channel output tile, K-major inside: [Cout / 96][Cin][KW][96]
+    const float* bias;    // [Cout] or null
+    const float* xa;      // activated input, parity-0 buffer
+    long long x_pstride;  // elements between the parity buffers (0 when P == 0)
+    int x_ld, P;          // row stride; history columns (KW - 1) * dil
+    const float* res;     // [Cout][T] residual or null
+    float* y;             // [Cout][T] plain output or null
+    ActOut act;
+    float* part;          // [splits][tiles][96 * 32] partial tiles
+    int* tile_ctr;        // [tiles] arrival counters (zero between launches)
+    const int* ctr;
+    int Cin, Cout, T, dil, splits, ci_per_split;
+};
+
+// ---- bulk asynchronous copies counted on an mbarrier (no multicast), bounded waits
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned limit) {
+    const uint32_t a = smem_u32(bar);
+    for (unsigned spins = 0; spins < limit; ++spins) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+// this thread's earlier cp.async copies count as one arrival on `bar` once they have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+#ifdef VUIC_TRACE
+__device__ long long g_ct_trace[16];
+#define CT_STAMP(n) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_ct_trace[n] = clock64(); } while (0)
+#else
+#define CT_STAMP(n) do {} while (0)
+#endif
+
+constexpr int CT_CO = 96, CT_T = 32, CT_GROUPS = 4, CT_THREADS = 96 * CT_GROUPS, CT_STAGES = 4;
+constexpr unsigned CT_WAIT_LIMIT = 1u << 22;
+template <int KW> struct CtCfg {
+    static constexpr int CC = KW == 1 ? 32 : 8;                      // input channels per staging step
+    static constexpr int XW = (32 + (KW - 1) * 9 + 3) / 4 * 4;       // widest input window (dilation <= 9)
+};
+template <int KW> constexpr int ct_smem_bytes() {
+    return CT_STAGES * (CtCfg<KW>::CC * KW * CT_CO + CtCfg<KW>::CC * CtCfg<KW>::XW) * 4;
+}
+
+// y[co][t] = bias[co] + sum_{ci, j} w[ci][j][co] * xa[ci][t + j * dil]  (+ res[co][t]), xa as described above.
+// Weights are stored per 96-channel output tile, K-major inside it: wt[co / 96][ci][j][co % 96], so the slab of
+// one staging step (CC input channels) is one contiguous run.
+// grid (T / 32, Cout / 96, splits); 384 threads = four groups of 96, each thread 8 output channels x 4 columns
+// (t = tx + 8 k); the groups take every fourth input channel of a staging step and add up at the end: twelve
+// warps per tile, three per scheduler, so shared-memory latency hides behind other warps' FMAs.
+// The launch is a chain of memory round trips around little arithmetic, so each is started as early as it can be:
+// thread 0 requests the first four weight slabs (one bulk copy each) before the dependency wait, all threads the
+// input windows right after it (16-byte cp.async pieces that arrive on the same mbarrier), and a stage is refilled
+// as soon as it has been consumed; partial tiles and outputs move as whole rows.  Waits on the copies are bounded
+// and set FLAG_WAIT instead of hanging.
+template <int KW>
+__global__ void __launch_bounds__(CT_THREADS, 2) k_ctile(TileArgs a) {
+    constexpr int CC = CtCfg<KW>::CC, XW = CtCfg<KW>::XW, KK = CC * KW, NST = CT_STAGES;
+    constexpr int WST = KK * CT_CO, XST = CC * XW, SST = WST + XST;
+    extern __shared__ __align__(128) float sm[];        // [stages][weight slab | input windows]
+    __shared__ __align__(8) uint64_t full[NST];
     __shared__ int s_last;
+    const int tid = threadIdx.x, grp = tid / 96, lt = tid - grp * 96, tx = lt & 7, ty = lt >> 3;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int t0 = blockIdx.x * CT_T, co0 = blockIdx.y * CT_CO;
+    const int Cin = a.Cin, T = a.T, dil = a.dil, P = a.P;
+    const int ci_lo = blockIdx.z * a.ci_per_split, ci_hi = min(Cin, ci_lo + a.ci_per_split);
+    const int nchunks = (ci_hi - ci_lo) / CC;
+    const int win4 = (CT_T + P + 3) / 4;                // 16-byte pieces of one input window
+    const float* wt = a.wt + (size_t)blockIdx.y * Cin * KW * CT_CO;
+    CT_STAMP(0);
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < NST; ++s) mbar_init(&full[s], 1 + CT_THREADS);   // thread 0's expect_tx + everyone's windows
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    auto arm_and_load_w = [&](int st, int ch) {         // thread 0
+        mbar_expect_tx(&full[st], WST * 4);
+        bulk_g2s(sm + st * SST, wt + (size_t)(ci_lo + ch * CC) * KW * CT_CO, WST * 4, &full[st]);
+    };
+    if (tid == 0)
+        for (int s = 0; s < NST && s < nchunks; ++s) arm_and_load_w(s, s);
     pdl_wait();
     pdl_launch();
-    const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;
-    const int t0 = blockIdx.x * 32, co0 = blockIdx.y * COT;
-    const int Cin = a.Cin, T = a.T, dil = a.dil, pad = a.pad;
-    const int win = 32 + (KW - 1) * dil;
     const int parity = a.ctr[CTR_FRAME] & 1;
-    const float* hist = a.state ? a.state + (size_t)parity * Cin * pad : nullptr;
-    const int ci_lo = blockIdx.z * a.ci_per_split, ci_hi = min(Cin, ci_lo + a.ci_per_split);
-
-    // the next frame's history (last `pad` columns of [history | act(x)]), shared out over the whole grid
-    if (a.state) {
-        float* nxt = a.state + (size_t)(parity ^ 1) * Cin * pad;
-        int nblk = gridDim.x * gridDim.y * gridDim.z;
-        int blk = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        for (int i = blk * 128 + tid; i < Cin * pad; i += nblk * 128) {
-            int c = i / pad, p = T + (i - c * pad);     // column in [history(pad) | new(T)]
-            float v;
-            if (p < pad) v = hist[c * pad + p];
-            else {
-                v = a.x[(size_t)c * T + (p - pad)];
-                if (a.ea) v = snake(v, a.ea[c], a.ib[c]);
-            }
-            nxt[i] = v;
+    CT_STAMP(1);
+    const float* xa = a.xa + (size_t)parity * a.x_pstride;
+    auto load_x = [&](int st, int ch) {                 // all threads: piece q of channel c's window
+        for (int i = tid; i < CC * win4; i += CT_THREADS) {
+            const int c = i / win4, q = i - c * win4;
+            cp_async16(sm + st * SST + WST + c * XW + q * 4, xa + (size_t)(ci_lo + ch * CC + c) * a.x_ld + t0 + q * 4);
         }
-    }
+        cp_async_arrive(&full[st]);
+    };
+    for (int s = 0; s < NST && s < nchunks; ++s) load_x(s, s);
 
-    float acc[CPT][4];
+    float acc[8][4];
 #pragma unroll
-    for (int i = 0; i < CPT; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[i][k] = 0.f;
 
-    for (int c0 = ci_lo; c0 < ci_hi; c0 += CC) {
-        const int nc = min(CC, ci_hi - c0);
-        for (int i = tid; i < COT * CC * KW; i += 128) {
-            int r = i / (CC * KW), e = i - r * (CC * KW);
-            int co = co0 + r;
-            float v = 0.f;
-            if (co < a.Cout && e < nc * KW) v = a.w[((size_t)co * Cin + c0) * KW + e];
-            ws[r * WS + e] = v;
-        }
-        for (int i = tid; i < CC * win; i += 128) {
-            int c = i / win, p = i - c * win;
-            float v = 0.f;
-            if (c < nc) {
-                int ci = c0 + c, tt = t0 + p - pad;     // time index relative to this frame's first column
-                if (tt < 0) { if (hist) v = hist[ci * pad + (pad + tt)]; }
-                else if (tt < T) {
-                    v = a.x[(size_t)ci * T + tt];
-                    if (a.ea) v = snake(v, a.ea[ci], a.ib[ci]);
-                }
+    CT_STAMP(2);
+    constexpr int NIT = (CC / CT_GROUPS) * KW;          // (channel, tap) steps of one group per staging step
+    for (int ch = 0; ch < nchunks; ++ch) {
+        const int st = ch % NST;
+        if (!mbar_wait(&full[st], (ch / NST) & 1, CT_WAIT_LIMIT) && lt == 0)
+            atomicOr(const_cast<int*>(a.ctr) + CTR_FLAG, FLAG_WAIT);
+        if (ch < 4) CT_STAMP(3 + ch);
+        const float* w = sm + st * SST + grp * (KW * CT_CO) + ty * 8;
+        const float* x = sm + st * SST + WST + grp * XW + tx;
+        // operands of step it + 1 are requested before the FMAs of step it
+        float4 a0 = *reinterpret_cast<const float4*>(w), a1 = *reinterpret_cast<const float4*>(w + 4);
+        float bv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bv[k] = x[8 * k];
+#pragma unroll
+        for (int it = 0; it < NIT; ++it) {
+            float4 n0 = a0, n1 = a1;
+            float nb[4] = {0.f, 0.f, 0.f, 0.f};
+            if (it + 1 < NIT) {
+                const int cc = (it + 1) / KW, j = (it + 1) - cc * KW;
+                const float* wn = w + (cc * CT_GROUPS * KW + j) * CT_CO;
+                n0 = *reinterpret_cast<const float4*>(wn);
+                n1 = *reinterpret_cast<const float4*>(wn + 4);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) nb[k] = x[cc * CT_GROUPS * XW + 8 * k + j * dil];
             }
-            xw[c * XW + p] = v;
-        }
-        __syncthreads();
 #pragma unroll
-        for (int c = 0; c < CC; ++c) {
-#pragma unroll
-            for (int j = 0; j < KW; ++j) {
-                float wv[CPT], xv[4];
-#pragma unroll
-                for (int i = 0; i < CPT; ++i) wv[i] = ws[(ty * CPT + i) * WS + c * KW + j];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) xv[k] = xw[c * XW + tx * 4 + k + j * dil];
-#pragma unroll
-                for (int i = 0; i < CPT; ++i)
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) acc[i][k] += wv[i] * xv[k];
+            for (int k = 0; k < 4; ++k) {
+                acc[0][k] += a0.x * bv[k]; acc[1][k] += a0.y * bv[k];
+                acc[2][k] += a0.z * bv[k]; acc[3][k] += a0.w * bv[k];
+                acc[4][k] += a1.x * bv[k]; acc[5][k] += a1.y * bv[k];
+                acc[6][k] += a1.z * bv[k]; acc[7][k] += a1.w * bv[k];
             }
+            a0 = n0; a1 = n1;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) bv[k] = nb[k];
         }
-        __syncthreads();
+        __syncthreads();                                 // the stage has been read by everyone: refill it
+        if (ch + NST < nchunks) {
+            if (tid == 0) arm_and_load_w(st, ch + NST);
+            load_x(st, ch + NST);
+        }
     }
+    CT_STAMP(7);
+    // the groups' sums meet in the (now idle) staging memory; groups 1..3 park theirs element-major (element e of
+    // thread lt at [e][lt]: no bank conflicts), group 0 adds in group order and lays the tile out by rows
+    float* const tl = sm;                                // final tile [96][TLS]
+    constexpr int TLS = CT_T + 1, TL = CT_CO * CT_T;
+    float* const park = sm + CT_CO * TLS;                // [3][32][96]
+    if (grp > 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) park[((grp - 1) * 32 + i * 4 + k) * 96 + lt] = acc[i][k];
+    }
+    __syncthreads();
+    if (grp > 0 && P > 0) {
+        // meanwhile the other groups copy the next frame's history: my last P columns into the other parity's first P
+        float* nxt = const_cast<float*>(a.xa) + (size_t)(parity ^ 1) * a.x_pstride;
+        const int nthr = gridDim.x * gridDim.y * gridDim.z * (CT_THREADS - 96);
+        const int me = ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (CT_THREADS - 96) + (tid - 96);
+        for (int i0 = me; i0 < Cin * P; i0 += 4 * nthr) {
+            float hv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                int i = i0 + u * nthr, c = i / P, p = i - c * P;
+                hv[u] = i < Cin * P ? xa[(size_t)c * a.x_ld + T + p] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                int i = i0 + u * nthr, c = i / P, p = i - c * P;
+                if (i < Cin * P) nxt[(size_t)c * a.x_ld + p] = hv[u];
+            }
+        }
+    }
+    if (grp == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int e = (i * 4 + k) * 96 + lt;
+                tl[(ty * 8 + i) * TLS + tx + 8 * k] = ((acc[i][k] + park[e]) + park[32 * 96 + e]) + park[2 * 32 * 96 + e];
+            }
+    }
+    __syncthreads();
+    CT_STAMP(8);
 
     const int tile = blockIdx.y * gridDim.x + blockIdx.x, ntiles = gridDim.x * gridDim.y;
+    constexpr int EPT = TL / CT_THREADS;                 // tile elements per thread (8), lane = column
     if (a.splits > 1) {
-        float* mine = a.part + ((size_t)blockIdx.z * ntiles + tile) * (COT * 32);
+        float* mine = a.part + ((size_t)blockIdx.z * ntiles + tile) * TL;
 #pragma unroll
-        for (int i = 0; i < CPT; ++i)
-            *reinterpret_cast<float4*>(mine + (ty * CPT + i) * 32 + tx * 4) =
-                make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        for (int u = 0; u < EPT; ++u) {
+            const int e = tid + u * CT_THREADS;
+            mine[e] = tl[(e >> 5) * TLS + (e & 31)];
+        }
         __threadfence();
         __syncthreads();
         if (tid == 0) {
@@ -451,33 +624,47 @@ __global__ void __launch_bounds__(128) k_ctile(TileArgs a) {
         __syncthreads();
         if (!s_last) return;
         __threadfence();
+        float sum[EPT];
 #pragma unroll
-        for (int i = 0; i < CPT; ++i)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) acc[i][k] = 0.f;
+        for (int u = 0; u < EPT; ++u) sum[u] = 0.f;
+#pragma unroll 4
         for (int s = 0; s < a.splits; ++s) {     // split order: the sum does not depend on arrival order
-            const float* p = a.part + ((size_t)s * ntiles + tile) * (COT * 32);
+            const float* p = a.part + ((size_t)s * ntiles + tile) * TL;
 #pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                float4 v = __ldcg(reinterpret_cast<const float4*>(p + (ty * CPT + i) * 32 + tx * 4));
-                acc[i][0] += v.x; acc[i][1] += v.y; acc[i][2] += v.z; acc[i][3] += v.w;
-            }
+            for (int u = 0; u < EPT; ++u) sum[u] += __ldcg(p + tid + u * CT_THREADS);
+        }
+#pragma unroll
+        for (int u = 0; u < EPT; ++u) {
+            const int e = tid + u * CT_THREADS;
+            tl[(e >> 5) * TLS + (e & 31)] = sum[u];
+        }
+        __syncthreads();
+    }
+
+    // epilogue by rows: warp w owns 8 output channels, lane = column; operands first, then the stores
+    const int t = t0 + lane;
+    constexpr int RPW = CT_CO / (CT_THREADS / 32);
+    float bv2[RPW], ea[RPW], ib[RPW], rv[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        const int co = co0 + warp * RPW + r;
+        bv2[r] = a.bias ? __ldg(a.bias + co) : 0.f;
+        ea[r] = a.act.base ? __ldg(a.act.ea + co) : 0.f;
+        ib[r] = a.act.base ? __ldg(a.act.ib + co) : 0.f;
+        rv[r] = (a.res && t < T) ? a.res[(size_t)co * T + t] : 0.f;
+    }
+    float* act_dst = a.act.base ? a.act.base + (size_t)parity * a.act.pstride + a.act.off : nullptr;
+    CT_STAMP(9);
+    if (t < T) {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const int col = warp * RPW + r, co = co0 + col;
+            float v = tl[col * TLS + lane] + bv2[r] + rv[r];
+            if (a.y) a.y[(size_t)co * T + t] = v;
+            if (act_dst) act_dst[(size_t)co * a.act.ld + t] = snake(v, ea[r], ib[r]);
         }
     }
-#pragma unroll
-    for (int i = 0; i < CPT; ++i) {
-        int co = co0 + ty * CPT + i;
-        if (co >= a.Cout) continue;
-        float b = a.bias ? a.bias[co] : 0.f;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            int t = t0 + tx * 4 + k;
-            if (t >= T) continue;
-            float v = acc[i][k] + b;
-            if (a.res) v += a.res[(size_t)co * T + t];
-            a.y[(size_t)co * T + t] = v;
-        }
-    }
+    CT_STAMP(10);
 }
 
 // ---------------------------------------------------------------- overlap-add of a transposed convolution
@@ -486,6 +673,8 @@ struct OlaArgs {
     const float* bias;    // [Cout]
     float* partial;       // [Cout][s]: what the previous frame's last column adds to this frame's first s samples
     float* y;             // [Cout][Tin * s]
+    ActOut act;           // activated copy for the first residual unit
+    const int* ctr;
     int Cout, s, Tin;
 };
 
@@ -504,49 +693,55 @@ __global__ void __launch_bounds__(256) k_overlap_add(OlaArgs a) {
         a.partial[co * s + j] = a.p[(size_t)(co * K + j + s) * Tin + Tin - 1];   // read above by this thread only
     }
     a.y[i] = v;
+    act_store(a.act, a.ctr[CTR_FRAME] & 1, co, u, v);
 }
 
 // ---------------------------------------------------------------- last convolution (96 -> 1, k = 7) + clamp
 struct FinalArgs {
-    const float* x;       // [C][T]
+    const float* xa;      // activated input [2][C][ld] with 6 history columns in front (as for k_ctile)
+    long long x_pstride; int x_ld;
     const float* w;       // [C][7]
     const float* bias;    // [1]
-    const float* ea; const float* ib;
-    float* state;         // [2][C * 6]
     const int* ctr;
     float* audio;         // [T]
     int C, T;
 };
 
-__global__ void __launch_bounds__(64) k_final_conv(FinalArgs a) {
-    extern __shared__ float xs[];   // [C][70] activated window
+// 32 outputs per CTA; four groups of threads each sum a quarter of the channels
+__global__ void __launch_bounds__(128) k_final_conv(FinalArgs a) {
+    __shared__ float part[4][32];
     pdl_wait();
     pdl_launch();
-    const int tid = threadIdx.x, t0 = blockIdx.x * 64, C = a.C, T = a.T;
+    const int tid = threadIdx.x, lane = tid & 31, grp = tid >> 5, C = a.C, T = a.T;
     const int parity = a.ctr[CTR_FRAME] & 1;
-    const float* hist = a.state + parity * C * 6;
-    for (int i = tid; i < C * 70; i += 64) {
-        int c = i / 70, p = i - c * 70, tt = t0 + p - 6;
-        float v = 0.f;
-        if (tt < 0) v = hist[c * 6 + 6 + tt];
-        else if (tt < T) v = snake(a.x[c * T + tt], a.ea[c], a.ib[c]);
-        xs[i] = v;
-    }
-    __syncthreads();
-    if (blockIdx.x == gridDim.x - 1) {   // T >= 6: the new history is the last six activated columns
-        float* nxt = a.state + (parity ^ 1) * C * 6;
-        for (int i = tid; i < C * 6; i += 64) {
+    const float* xa = a.xa + (size_t)parity * a.x_pstride;
+    if (blockIdx.x == 0) {
+        float* nxt = const_cast<float*>(a.xa) + (size_t)(parity ^ 1) * a.x_pstride;
+        for (int i = tid; i < C * 6; i += 128) {
             int c = i / 6, p = i - c * 6;
-            nxt[i] = xs[c * 70 + (T - t0) + p];
+            nxt[(size_t)c * a.x_ld + p] = xa[(size_t)c * a.x_ld + T + p];
         }
     }
-    int t = t0 + tid;
-    if (t >= T) return;
-    float acc = a.bias[0];
-    for (int c = 0; c < C; ++c)
+    const int t = blockIdx.x * 32 + lane, per = (C + 3) / 4;
+    float acc = 0.f;
+    if (t < T) {
+        const int c_lo = grp * per, c_hi = min(C, (grp + 1) * per);
+#pragma unroll 4
+        for (int c = c_lo; c < c_hi; ++c) {
+            const float* xr = xa + (size_t)c * a.x_ld + t;
+            float xv[7];
 #pragma unroll
-        for (int j = 0; j < 7; ++j) acc += a.w[c * 7 + j] * xs[c * 70 + tid + j];
-    a.audio[t] = fminf(1.f, fmaxf(-1.f, acc));
+            for (int j = 0; j < 7; ++j) xv[j] = xr[j];
+#pragma unroll
+            for (int j = 0; j < 7; ++j) acc += __ldg(a.w + c * 7 + j) * xv[j];
+        }
+    }
+    part[grp][lane] = acc;
+    __syncthreads();
+    if (grp == 0 && t < T) {
+        float v = a.bias[0] + ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane]));
+        a.audio[t] = fminf(1.f, fmaxf(-1.f, v));
+    }
 }
 
 // one frame done: advance the state parity and the transformer position
