@@ -419,7 +419,7 @@ def codec_weight_bytes() -> int:
     return 4 * n
 
 
-def codec_block(dev, cpu_baseline: bool, frames: int = 100, reps: int = 5):
+def codec_block(dev, cpu_baseline: bool, frames: int = 100, reps: int = 5, model=None):
     """Streaming codec decode of one stream: `frames` consecutive frames per block (transformer positions
     10..10+frames), median block; device-resident codes for `ms_per_frame`, pinned host codes in and audio out
     every frame for `e2e`."""
@@ -462,6 +462,42 @@ def codec_block(dev, cpu_baseline: bool, frames: int = 100, reps: int = 5):
             torch.cuda.current_stream(dev).synchronize()
         e2e_ms = 1e3 * (time.perf_counter() - t0) / frames
     dec.check_device()
+    stream_ms = frame_graph = None
+    if model is not None:
+        from vui_b200 import Engine, GenConfig
+
+        eng = Engine(model=model, max_rows=1, max_seq=1024)
+        row = eng.new_row()
+        hid = eng.prefill_ids(row, torch.randint(0, model.shape.vocab_size, (64,), generator=torch.Generator().manual_seed(0)))
+        eng._apply_cfg(GenConfig(), greedy=True)
+        eng._g_slot_idx[:1] = row.idx
+        eng._g_seq_inc[:1].fill_(1)
+        eng._g_codes_in[:1] = eng._first_frames([row], hid[None])
+        frame_graph = eng._frame_graph(1)
+    if frame_graph is not None:
+        # what Row.stream costs per frame of audio: one generation step + one codec frame, on one stream, and with
+        # the codec frame of step k on a second stream beside the generation of step k + 1
+        stream_ms = {}
+        main, side = torch.cuda.current_stream(dev), torch.cuda.Stream(dev)
+        for mode in ("one_stream", "codec_on_second_stream"):
+            with dec.streaming(1):
+                for t in range(8 + frames):
+                    if t == 8:
+                        torch.cuda.synchronize(dev)
+                        e0.record()
+                    frame_graph.replay()
+                    dec._codes_in.copy_(codes[:, t % codes.shape[1]])
+                    if mode == "one_stream":
+                        g.replay()
+                    else:
+                        side.wait_stream(main)
+                        with torch.cuda.stream(side):
+                            g.replay()
+                        if t + 1 == 8 + frames:
+                            main.wait_stream(side)
+                e1.record()
+                torch.cuda.synchronize(dev)
+            stream_ms[mode] = e0.elapsed_time(e1) / frames
     wbytes = codec_weight_bytes()
     kv = 8 * 16 * 64 * 4 * 2 * (10 + frames / 2)
     peak, _ = measured_hbm_peak()
@@ -473,6 +509,8 @@ def codec_block(dev, cpu_baseline: bool, frames: int = 100, reps: int = 5):
         "launches_per_frame": 87, "weight_bytes_per_frame": wbytes,
         "roofline_frac": (wbytes + kv) / (ms * 1e-3) / 1e9 / peak,
     }
+    if stream_ms is not None:
+        res["generation_plus_codec_ms_per_frame"] = stream_ms
     if cpu_baseline:
         from oracle.codec_oracle import CodecOracle
         from vui_b200.codec import random_codec_state
@@ -577,7 +615,7 @@ def run_b200(args):
     extra = cfg4 = wide = standin_ms = codec = None
     if B == 1 and not args.no_batched and rank == 0:
         try:
-            codec = codec_block(dev, world == 1 and not args.no_cpu_baseline)
+            codec = codec_block(dev, world == 1 and not args.no_cpu_baseline, model=model)
         except Exception as exc:  # noqa: BLE001 - an extra block must never take the bench line down
             print(f"codec block failed: {exc}", file=sys.stderr)
     if B == 1 and not args.no_batched:

@@ -159,3 +159,23 @@ def test_engine_streams_audio_through_the_codec(dec, nano_sd):
         codes, audio = row.render("And this is the offline path.", cfg)
         assert audio is not None and audio.shape[-1] == codes.shape[0] * 1920
     dec.check_device()
+
+
+def test_codec_on_second_stream_yields_the_same_audio(dec, nano_sd):
+    """Row.stream with overlap_codec: frame k's audio is decoded beside the generation of frame k + 1; the frames
+    handed out are the same tensors in the same order as without the overlap."""
+    from vui_b200 import Engine, GenConfig, Segment, VuiB200, VuiShape
+
+    model = VuiB200(VuiShape(), nano_sd, device="cuda", tokenizer=StubTok())
+    cfg = GenConfig(temperature=0.8, top_k=50, max_secs=1.0, eos_threshold=0.999)
+    prompt = torch.randint(0, 2048, (9, 16), generator=torch.Generator().manual_seed(3))
+    outs = []
+    for overlap in (False, True):
+        eng = Engine(model=model, codec=dec, max_rows=1, max_seq=1024, seed=11)
+        eng.overlap_codec = overlap
+        with eng.new_row() as row:
+            row.prefill([Segment("A short prompt.", prompt)])
+            outs.append(torch.cat([a.cpu() for a in row.stream("Hello there, this is streaming audio.", cfg)], dim=-1))
+    assert outs[0].shape == outs[1].shape and outs[0].shape[-1] >= 1920
+    assert torch.equal(outs[0], outs[1])
+    dec.check_device()

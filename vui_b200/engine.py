@@ -191,6 +191,8 @@ class Engine:
             model = VuiB200.from_checkpoint(self.NAMES.get(name, name))
         self.model = model
         self.codec = codec
+        self.overlap_codec = False   # True: Row.stream decodes frame k's audio beside the generation of frame k + 1
+        self._codec_stream = None
         self.max_rows = max_rows
         self.vocoder_ctx = vocoder_ctx
         self.device = model.device
@@ -1062,8 +1064,32 @@ class Engine:
         ctx = row._codec_ctx
         if ctx is not None and hasattr(ctx, "prefill") and getattr(ctx, "_stack", True) is None:
             ctx.prefill(n_codebooks=cfg.n_codebooks)
+        if not self.overlap_codec:
+            for codes in self._stream_codes(row, text, cfg, cancel, reset_rep=reset_rep, final_turn=final_turn):
+                yield self._stream_decode_frame(codes.to(self.device), cfg.n_codebooks)
+            return
+        # frame k's audio is decoded on a second stream while frame k + 1 is generated on the first: the same
+        # audio in the same order, each frame handed out one generation step later
+        main = torch.cuda.current_stream(self.device)
+        if self._codec_stream is None:
+            self._codec_stream = torch.cuda.Stream(self.device)
+        side, pending = self._codec_stream, None
         for codes in self._stream_codes(row, text, cfg, cancel, reset_rep=reset_rep, final_turn=final_turn):
-            yield self._stream_decode_frame(codes.to(self.device), cfg.n_codebooks)
+            dev_codes = codes.to(self.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                audio = self._stream_decode_frame(dev_codes, cfg.n_codebooks)
+                done = torch.cuda.Event()
+                done.record(side)
+            audio.record_stream(side)
+            if pending is not None:
+                pending[0].synchronize()
+                yield pending[1]
+            pending = (done, audio)
+        if pending is not None:
+            pending[0].synchronize()
+            yield pending[1]
+        main.wait_stream(side)
 
     def _stream_decode_frame(self, frame_codes: Tensor, n_codebooks: int) -> Tensor:
         if 0 not in self._rows or self._rows[0]._codec_ctx is None:
