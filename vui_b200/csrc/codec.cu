@@ -30,7 +30,7 @@ struct Layout {
     PadBuf res_in[4][3], fin_in;                // inputs of the residual units' first convolutions, of the last conv
     size_t partial[4];                          // transposed-convolution partials [Cout][rate]
     size_t kc, vc;                              // [layers][heads][max_seq][64]
-    size_t h0, y1, x, qkv, attn, g, lat, u[2], z, a4, d0, p, y[4], ya[4], r1, part;
+    size_t h0, y1, x, qkv, attn, g, lat, u[2], z, a4, d0, d0a, p, y[4], ya[4], r1, part;
     size_t total;
     int C[5], T[5];                             // channels / columns after decoder.0 and after each block
 };
@@ -159,6 +159,7 @@ void make_layout(VuibCodec* c) {
     L.z = take(cur, lat * 4 * 4);
     L.a4 = take(cur, (size_t)lat * 4 * 4 * 4);
     L.d0 = take(cur, (size_t)L.C[0] * L.T[0] * 4);
+    L.d0a = take(cur, (size_t)L.C[0] * L.T[0] * 4);
     size_t pmax = 0, ymax = 0;
     int part_max = 1;
     for (int b = 0; b < 4; ++b) {
@@ -473,9 +474,10 @@ extern "C" int32_t vuib_codec_decode_frame(VuibCodec* c, const int64_t* codes_de
     {   // decoder.0 (k = 7) on 4 columns
         RowsArgs a = rows_args(c, w.dec_in.w, w.dec_in.b, cur, 4, 1, lat, L.C[0], wsp<float>(c, L.d0), 4, 1);
         a.state = wsp<float>(c, L.dec_in.off);
+        a.y_act = wsp<float>(c, L.d0a); a.act_ea = w.block[0].act.ea; a.act_ib = w.block[0].act.ib;
         CK(rows(c, 7, 4, a, s));
     }
-    cur = wsp<float>(c, L.d0);   // not activated: the first block's row kernel applies its SnakeBeta while staging
+    cur = wsp<float>(c, L.d0a);  // decoder.0's output with the first block's SnakeBeta already applied
     const int dil[3] = {1, 3, 9};
     const ActOut no_act = {};
     for (int b = 0; b < 4; ++b) {
@@ -487,7 +489,6 @@ extern "C" int32_t vuib_codec_decode_frame(VuibCodec* c, const int64_t* codes_de
         float* r1 = wsp<float>(c, L.r1);
         if (b == 0) {
             RowsArgs a = rows_args(c, bw.up.w, nullptr, cur, Tin, 1, Cin, prow, p, Tin, 1);
-            a.pro = PRO_SNAKE; a.p0 = bw.act.ea; a.p1 = bw.act.ib;
             CK(rows(c, 1, Tin, a, s));
         } else {   // the previous block left its output activated in ya[b - 1]
             CK(tile(c, 1, bw.up.w, nullptr, plain_in(wsp<float>(c, L.ya[b - 1]), Tin), nullptr, p, no_act, Cin, prow, Tin,
@@ -516,7 +517,7 @@ extern "C" int32_t vuib_codec_decode_frame(VuibCodec* c, const int64_t* codes_de
         FinalArgs a = {};
         a.xa = wsp<float>(c, L.fin_in.off); a.x_pstride = L.fin_in.pstride; a.x_ld = L.fin_in.ld;
         a.w = w.final_conv.w; a.bias = w.final_conv.b; a.ctr = ctr; a.audio = audio_out_dev; a.C = L.C[4]; a.T = L.T[4];
-        CK(launch(c, k_final_conv, dim3((a.T + 31) / 32), dim3(128), 0, s, a));
+        CK(launch(c, k_final_conv, dim3((a.T + 31) / 32), dim3(128), (size_t)a.C * 40 * 4, s, a));
     }
     CK(launch(c, k_advance, dim3(1), dim3(32), 0, s, ctr));
     return VUIB_OK;

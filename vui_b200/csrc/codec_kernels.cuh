@@ -130,6 +130,8 @@ struct RowsArgs {
     int row_div, y_rs, y_js, y_ts;
     const float* scale;   // EPI_SCALE_RES: per-(row / row_div) factor
     const float* res;     // EPI_SCALE_RES: residual, indexed like y
+    float* y_act;         // optional: snake(v) with the consumer's per-row parameters, indexed like y
+    const float* act_ea; const float* act_ib;
 };
 
 // out[row][t] = sum_{ci, j} w[row][ci][j] * X[ci][t + j]  with X = [history | new columns] (causal, dilation 1)
@@ -157,11 +159,11 @@ __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
         for (int t = 0; t < T; ++t) {
             const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)t * a.x_ts);
             float4* dst = reinterpret_cast<float4*>(xs + t * Cin);
-#pragma unroll 4
+#pragma unroll 8
             for (int i = tid; i < Cin / 4; i += blockDim.x) dst[i] = __ldg(src + i);
         }
     } else {
-#pragma unroll 4
+#pragma unroll 8
         for (int i = tid; i < Cin * T; i += blockDim.x) {
             int c = (KW == 1) ? i % Cin : i / T, t = (KW == 1) ? i / Cin : i % T;
             float v = __ldg(a.x + c * a.x_cs + t * a.x_ts);
@@ -170,8 +172,8 @@ __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
         }
         if constexpr (KW > 1) {
             const float* hist = a.state + parity * Cin * PAD;
-#pragma unroll 4
-            for (int i = tid; i < Cin * PAD; i += blockDim.x) xs[(i / PAD) * P + (i % PAD)] = hist[i];
+#pragma unroll 8
+            for (int i = tid; i < Cin * PAD; i += blockDim.x) xs[(i / PAD) * P + (i % PAD)] = __ldg(hist + i);
         }
     }
     __syncthreads();
@@ -250,6 +252,7 @@ __global__ void __launch_bounds__(256) k_crows(RowsArgs a) {
                 else if (a.epi == EPI_SCALE_RES) v = a.res[o] + a.scale[g] * v;
                 else if (a.epi == EPI_SILU_MUL) v = (v / (1.f + expf(-v))) * acc2[t];
                 a.y[o] = v;
+                if (a.y_act) a.y_act[o] = snake(v, a.act_ea[g], a.act_ib[g]);
             }
         }
     }
@@ -707,14 +710,22 @@ struct FinalArgs {
     int C, T;
 };
 
-// 32 outputs per CTA; four groups of threads each sum a quarter of the channels
+// 32 outputs per CTA; the CTA's input window (C x 38) goes to shared memory with every load in flight, then four
+// groups of threads each sum a quarter of the channels
 __global__ void __launch_bounds__(128) k_final_conv(FinalArgs a) {
+    extern __shared__ float win[];       // [C][40]
     __shared__ float part[4][32];
     pdl_wait();
     pdl_launch();
     const int tid = threadIdx.x, lane = tid & 31, grp = tid >> 5, C = a.C, T = a.T;
     const int parity = a.ctr[CTR_FRAME] & 1;
     const float* xa = a.xa + (size_t)parity * a.x_pstride;
+    const int t0 = blockIdx.x * 32;
+#pragma unroll 8
+    for (int i = tid; i < C * 10; i += 128) {      // 10 float4 pieces per channel: columns t0 .. t0 + 39
+        const int c = i / 10, q = i - c * 10;
+        reinterpret_cast<float4*>(win)[i] = *reinterpret_cast<const float4*>(xa + (size_t)c * a.x_ld + t0 + q * 4);
+    }
     if (blockIdx.x == 0) {
         float* nxt = const_cast<float*>(a.xa) + (size_t)(parity ^ 1) * a.x_pstride;
         for (int i = tid; i < C * 6; i += 128) {
@@ -722,19 +733,15 @@ __global__ void __launch_bounds__(128) k_final_conv(FinalArgs a) {
             nxt[(size_t)c * a.x_ld + p] = xa[(size_t)c * a.x_ld + T + p];
         }
     }
-    const int t = blockIdx.x * 32 + lane, per = (C + 3) / 4;
+    __syncthreads();
+    const int t = t0 + lane, per = (C + 3) / 4;
     float acc = 0.f;
-    if (t < T) {
-        const int c_lo = grp * per, c_hi = min(C, (grp + 1) * per);
+    const int c_lo = grp * per, c_hi = min(C, (grp + 1) * per);
 #pragma unroll 4
-        for (int c = c_lo; c < c_hi; ++c) {
-            const float* xr = xa + (size_t)c * a.x_ld + t;
-            float xv[7];
+    for (int c = c_lo; c < c_hi; ++c) {
+        const float* xr = win + c * 40 + lane;
 #pragma unroll
-            for (int j = 0; j < 7; ++j) xv[j] = xr[j];
-#pragma unroll
-            for (int j = 0; j < 7; ++j) acc += __ldg(a.w + c * 7 + j) * xv[j];
-        }
+        for (int j = 0; j < 7; ++j) acc += __ldg(a.w + c * 7 + j) * xr[j];
     }
     part[grp][lane] = acc;
     __syncthreads();
