@@ -48,10 +48,73 @@ constexpr int DG_XS = DG_D + 8;   // padded row strides (elements): conflict-fre
 constexpr int DG_GS = 192 + 8;
 constexpr int DG_AS = HD + 8;
 
-struct DepthGroupMaps {
-    CUtensorMap wqkv[DG_LAYERS], out[DG_LAYERS], w1[DG_LAYERS], w3[DG_LAYERS], w2[DG_LAYERS];
-    CUtensorMap head;
+// The weights reach the ring as ONE contiguous 32 KB bulk copy per stage (four boxes): measured on this part, a
+// tiled TMA box (64 rows of 128 bytes, 1-2.8 KB apart in the matrix) arrives at ~43 GB/s per SM however many are
+// in flight or however many lanes request them, a contiguous 32 KB bulk copy at ~200 GB/s.  So the depth weights
+// are copied once, when they are bound, into a "box stream": for every (layer, CTA of the cluster) the boxes in
+// exactly the order the kernel consumes them, each box already in its 128-byte-swizzled shared-memory image
+// (row r, 16-byte piece q at r * 128 + ((q ^ (r & 7)) << 4)); the heads of the 15 codebooks likewise per
+// (codebook, CTA).  Rows or columns beyond a matrix are zeros, as the tensor-map fill was.
+struct DepthGroupStream {
+    const unsigned char* layers;   // [n_layers][8 CTAs][boxes_per_layer][8192]
+    const unsigned char* head;     // [Q - 1][8 CTAs][32][8192]
+    int boxes_per_layer;           // 32 + 24 * n_ub
 };
+
+__host__ __device__ inline int dg_boxes_per_layer(int n_ub) { return 24 + 8 + 16 * n_ub + 8 * n_ub; }
+
+struct DgStreamBuild {
+    const bf16* wqkv[DG_LAYERS]; const bf16* out[DG_LAYERS]; const bf16* w1[DG_LAYERS]; const bf16* w3[DG_LAYERS];
+    const bf16* w2[DG_LAYERS];
+    const bf16* head;              // ((Q - 1) * CS, 512)
+    unsigned char* layers; unsigned char* head_out;
+    int n_layers, ffn, upc, n_ub, CS, n_head_pos;   // n_head_pos = Q - 1
+};
+
+// One CTA per box of the stream; the box sequence of a layer is q|k|v rows of head c (8 K-chunks each), the
+// head's K-slice of out_proj (8 row blocks), w1/w3 of the CTA's hidden units (per 64 units: 8 K-chunks, w1 and w3
+// alternating), the CTA's K-slice of w2 (8 row blocks x n_ub column blocks).
+__global__ void __launch_bounds__(256) k_build_dg_stream(DgStreamBuild b) {
+    const int bpl = dg_boxes_per_layer(b.n_ub);
+    const int n_layer_boxes = b.n_layers * DG_CL * bpl;
+    int box = blockIdx.x;
+    const bf16* W;
+    int N, K, x, y;
+    unsigned char* dst;
+    if (box < n_layer_boxes) {
+        const int l = box / (DG_CL * bpl), c = (box / bpl) % DG_CL;
+        int j = box % bpl;
+        dst = b.layers + (size_t)box * DG_BOX_BYTES;
+        if (j < 24) { W = b.wqkv[l]; N = 3 * DG_D; K = DG_D; x = (j % 8) * 64; y = (j / 8) * DG_D + c * HD; }
+        else if ((j -= 24) < 8) { W = b.out[l]; N = DG_D; K = DG_D; x = c * HD; y = j * 64; }
+        else if ((j -= 8) < 16 * b.n_ub) {
+            const int ub = j / 16, kb = (j % 16) / 2;
+            W = (j & 1) ? b.w3[l] : b.w1[l]; N = b.ffn; K = DG_D; x = kb * 64; y = c * b.upc + ub * 64;
+        } else {
+            j -= 16 * b.n_ub;
+            W = b.w2[l]; N = DG_D; K = b.ffn; x = c * b.upc + (j % b.n_ub) * 64; y = (j / b.n_ub) * 64;
+        }
+    } else {
+        box -= n_layer_boxes;
+        const int p = box / (DG_CL * 32), c = (box / 32) % DG_CL, j = box % 32;
+        dst = b.head_out + (size_t)box * DG_BOX_BYTES;
+        W = b.head; N = b.n_head_pos * b.CS; K = DG_D; x = (j % 8) * 64; y = p * b.CS + c * 256 + (j / 8) * 64;
+    }
+    for (int i = threadIdx.x; i < 64 * 8; i += 256) {       // 16-byte pieces: row r, piece q
+        const int r = i >> 3, q = i & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (y + r < N) {
+            const int col = x + q * 8;
+            if (col + 8 <= K) v = __ldg(reinterpret_cast<const uint4*>(W + (size_t)(y + r) * K + col));
+            else if (col < K) {
+                bf16 tmp[8];
+                for (int e = 0; e < 8; ++e) tmp[e] = col + e < K ? W[(size_t)(y + r) * K + col + e] : f2bf(0.f);
+                v = *reinterpret_cast<const uint4*>(tmp);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + r * 128 + ((q ^ (r & 7)) << 4)) = v;
+    }
+}
 
 struct DepthGroupArgs {
     int B;            // streams
@@ -132,6 +195,15 @@ struct DgState {
     unsigned limit;
 };
 
+// Wait on a barrier that only this CTA's own copies complete (the weight ring): CTA scope is enough.
+__device__ __forceinline__ void dg_wait_local_or_die(DgState& st, uint64_t* bar, unsigned parity) {
+    if (st.dead) return;
+    if (!mbar_wait(bar, parity, st.limit)) {
+        if ((threadIdx.x & 31) == 0) atomicOr(st.flag, FLAG_COPY_TIMEOUT);
+        st.dead = true;
+    }
+}
+
 __device__ __forceinline__ void dg_wait_or_die(DgState& st, uint64_t* bar, unsigned parity) {
     if (st.dead) return;
     if (!dg_wait(bar, parity, st.limit)) {
@@ -140,42 +212,81 @@ __device__ __forceinline__ void dg_wait_or_die(DgState& st, uint64_t* bar, unsig
     }
 }
 
-// One row group of 64 weight rows: `nbox` boxes, box j read by warp set (j & 1); its slice of the
-// activation rows starts at element (j >> kshift) * kmul.  Leaves this warp's accumulators in acc.
+// One row group of 64 weight rows: `nbox` boxes; its slice of the activation rows starts at element
+// (j >> kshift) * kmul.  owner < 0: box j is read by warp set (j & 1) and the two sets' sums are combined
+// afterwards (dg_combine); owner = 0 / 1: that set reads every box and owns the result, the other set skips the
+// row group - successive row groups then alternate between the sets and need neither a combine nor a barrier.
+// Leaves this warp's accumulators in acc.
 template <int R>
 __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, int nbox, const bf16* act, int astride,
-                                            int kshift, int kmul, float (&acc)[R / 8][4]) {
+                                            int kshift, int kmul, float (&acc)[R / 8][4], int owner = -1) {
     constexpr int NT = R / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int set = warp >> 2, mt = warp & 3, g = lane >> 2, t = lane & 3;
+    const int base = st.bi;
+    st.bi += nbox;
+    // A warp's chain per box (wait, ldmatrix, fragment loads, MMAs, release) bounds the kernel: the four k-steps of
+    // a box go to four independent accumulators (added at the end) instead of one dependent chain, and the
+    // fragments of the warp's next box are fetched while the MMAs of the current one are in flight.
+    float c4[4][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    for (int j = 0; j < nbox; ++j, ++st.bi) {
-        if ((j & 1) != set) continue;
-        const int slot = st.bi % DG_RING, stage = slot / DG_STAGE;
-        dg_wait_or_die(st, &sm.full[stage], (st.bi / DG_RING) & 1);
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) c4[ks][nt][0] = c4[ks][nt][1] = c4[ks][nt][2] = c4[ks][nt][3] = 0.f;
+    struct Frag { uint32_t a[4][4]; uint32_t b[4][NT][2]; };
+    Frag f0, f1;   // two named buffers (a run-time buffer index would put them in local memory)
+    const int first = owner < 0 ? set : 0, step = owner < 0 ? 2 : 1;   // this set's boxes: first, first + step, ...
+    const bool mine = owner < 0 || owner == set;
+    auto fetch = [&](int j, Frag& f) {
+        const int bi = base + j, slot = bi % DG_RING, stage = slot / DG_STAGE;
+        dg_wait_local_or_die(st, &sm.full[stage], (bi / DG_RING) & 1);
         const uint32_t bx = smem_u32(sm.ring[slot]);
         const int k0 = (j >> kshift) * kmul;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
             const int row = mt * 16 + (lane & 15), chunk = ks * 2 + (lane >> 4);
-            uint32_t a0, a1, a2, a3;
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                         : "=r"(f.a[ks][0]), "=r"(f.a[ks][1]), "=r"(f.a[ks][2]), "=r"(f.a[ks][3])
                          : "r"(bx + row * 128 + ((chunk ^ (row & 7)) << 4)));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const bf16* ap = act + (size_t)(nt * 8 + g) * astride + k0 + ks * 16 + 2 * t;
-                const uint32_t bb0 = *reinterpret_cast<const uint32_t*>(ap);
-                const uint32_t bb1 = *reinterpret_cast<const uint32_t*>(ap + 8);
-                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                             : "+f"(acc[nt][0]), "+f"(acc[nt][1]), "+f"(acc[nt][2]), "+f"(acc[nt][3])
-                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bb0), "r"(bb1));
+                f.b[ks][nt][0] = *reinterpret_cast<const uint32_t*>(ap);
+                f.b[ks][nt][1] = *reinterpret_cast<const uint32_t*>(ap + 8);
             }
         }
+    };
+    // MMAs of box j, then its release: issuing the MMAs has taken the box's fragments out of shared memory
+    auto consume = [&](int j, const Frag& f) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(c4[ks][nt][0]), "+f"(c4[ks][nt][1]), "+f"(c4[ks][nt][2]), "+f"(c4[ks][nt][3])
+                             : "r"(f.a[ks][0]), "r"(f.a[ks][1]), "r"(f.a[ks][2]), "r"(f.a[ks][3]),
+                               "r"(f.b[ks][nt][0]), "r"(f.b[ks][nt][1]));
         __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.empty[stage])) : "memory");
+        if (lane == 0) {
+            const int stage = ((base + j) % DG_RING) / DG_STAGE;
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.empty[stage])) : "memory");
+        }
+    };
+    if (mine) {
+        if (first < nbox) fetch(first, f0);
+        for (int j = first; j < nbox; j += 2 * step) {
+            consume(j, f0);
+            if (j + step < nbox) {
+                fetch(j + step, f1);
+                consume(j + step, f1);
+                if (j + 2 * step < nbox) fetch(j + 2 * step, f0);
+            }
+        }
     }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = (c4[0][nt][i] + c4[1][nt][i]) + (c4[2][nt][i] + c4[3][nt][i]);
 }
 
 // Hand the odd-box accumulators (warps 4-7) to the even-box warps (0-3); true in the warps that go on
@@ -282,7 +393,7 @@ __device__ __forceinline__ void dg_residual_exchange(DepthGroupSmem<R>& sm, DgSt
 
 template <int R>
 __global__ void __launch_bounds__(DG_THREADS, 1)
-k_depth_group(const __grid_constant__ DepthGroupMaps maps, DepthGroupArgs a) {
+k_depth_group(const DepthGroupStream strm, DepthGroupArgs a) {
     using S = DepthGroupSmem<R>;
     constexpr int NT = S::NT;
     extern __shared__ __align__(1024) unsigned char dg_smem[];
@@ -317,56 +428,48 @@ k_depth_group(const __grid_constant__ DepthGroupMaps maps, DepthGroupArgs a) {
     // ------------------------------------------------------------------ producer warp
     if (warp == DG_CONSUMERS / 32) {
         if (lane == 0) {
-            int i = 0;
+            int i = 0;   // stages issued so far (a stage = DG_STAGE consecutive boxes = one contiguous 32 KB copy)
             bool dead = false;
-            // A stage (DG_STAGE boxes) is re-armed once its previous boxes have all been read; the wait
-            // polls without suspending, so that the producer wakes as soon as the last reader arrives.
-            auto issue = [&](const CUtensorMap* m, int x, int y) {
+            // A stage is re-armed once its previous boxes have all been read; the wait polls without suspending, so
+            // that the producer wakes as soon as the last reader arrives.
+            auto issue_stage = [&](const unsigned char* src) {
                 if (dead) return;
-                const int stage = (i / DG_STAGE) % DG_STAGES;
-                if (i % DG_STAGE == 0) {
-                    if (i >= DG_RING) {
-                        const uint32_t ea = smem_u32(&sm.empty[stage]);
-                        const unsigned parity = ((i / DG_RING) - 1) & 1;
-                        unsigned spins = 0;
-                        for (;;) {
-                            uint32_t ok;
-                            asm volatile(
-                                "{\n\t.reg .pred p;\n\t"
-                                "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                                "selp.u32 %0, 1, 0, p;\n\t}"
-                                : "=r"(ok)
-                                : "r"(ea), "r"(parity)
-                                : "memory");
-                            if (ok) break;
-                            if (++spins > 16u * a.spin_limit) {
-                                atomicOr(a.flag, FLAG_COPY_TIMEOUT);
-                                dead = true;
-                                return;
-                            }
+                const int stage = i % DG_STAGES;
+                if (i >= DG_STAGES) {
+                    const uint32_t ea = smem_u32(&sm.empty[stage]);
+                    const unsigned parity = ((i / DG_STAGES) - 1) & 1;
+                    unsigned spins = 0;
+                    for (;;) {
+                        uint32_t ok;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\t"
+                            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                            "selp.u32 %0, 1, 0, p;\n\t}"
+                            : "=r"(ok)
+                            : "r"(ea), "r"(parity)
+                            : "memory");
+                        if (ok) break;
+                        if (++spins > 16u * a.spin_limit) {
+                            atomicOr(a.flag, FLAG_COPY_TIMEOUT);
+                            dead = true;
+                            return;
                         }
                     }
-                    mbar_expect_tx(&sm.full[stage], DG_STAGE * DG_BOX_BYTES);
                 }
-                tma_load_2d(sm.ring[i % DG_RING], m, x, y, &sm.full[stage]);
+                mbar_expect_tx(&sm.full[stage], DG_STAGE * DG_BOX_BYTES);
+                bulk_g2s(sm.ring[stage * DG_STAGE], src, DG_STAGE * DG_BOX_BYTES, &sm.full[stage]);
                 ++i;
             };
+            const int spl = strm.boxes_per_layer / DG_STAGE;   // stages per layer
             for (int pos = 0; pos < n_pos; ++pos) {
                 for (int l = 0; l < a.n_layers; ++l) {
-                    for (int rg = 0; rg < 3; ++rg)
-                        for (int kb = 0; kb < 8; ++kb) issue(&maps.wqkv[l], kb * 64, rg * DG_D + c * HD);
-                    for (int rb = 0; rb < 8; ++rb) issue(&maps.out[l], c * HD, rb * 64);
-                    for (int ub = 0; ub < n_ub; ++ub)
-                        for (int kb = 0; kb < 8; ++kb) {
-                            issue(&maps.w1[l], kb * 64, c * a.upc + ub * 64);
-                            issue(&maps.w3[l], kb * 64, c * a.upc + ub * 64);
-                        }
-                    for (int rb = 0; rb < 8; ++rb)
-                        for (int cb = 0; cb < n_ub; ++cb) issue(&maps.w2[l], c * a.upc + cb * 64, rb * 64);
+                    const unsigned char* src = strm.layers + (size_t)(l * DG_CL + c) * strm.boxes_per_layer * DG_BOX_BYTES;
+                    for (int sg = 0; sg < spl; ++sg) issue_stage(src + (size_t)sg * DG_STAGE * DG_BOX_BYTES);
                 }
-                if (pos >= 1)
-                    for (int rb = 0; rb < 4; ++rb)
-                        for (int kb = 0; kb < 8; ++kb) issue(&maps.head, kb * 64, (pos - 1) * a.CS + c * 256 + rb * 64);
+                if (pos >= 1) {
+                    const unsigned char* src = strm.head + (size_t)((pos - 1) * DG_CL + c) * 32 * DG_BOX_BYTES;
+                    for (int sg = 0; sg < 32 / DG_STAGE; ++sg) issue_stage(src + (size_t)sg * DG_STAGE * DG_BOX_BYTES);
+                }
             }
         }
         __syncwarp();
@@ -403,11 +506,21 @@ k_depth_group(const __grid_constant__ DepthGroupMaps maps, DepthGroupArgs a) {
             dg_norm<R>(sm, a.attn_norm[l], a.eps);
             dg_bar();
             fb_stamp(dbg, 1);
-            // ---- q, k, v rows of head c
+            // ---- q, k, v rows of head c: q is the first warp set's, k the second's (both row groups fit the ring at
+            // once), v is split over K between them; one hand-over instead of three
             for (int rg = 0; rg < 3; ++rg) {
                 float acc[NT][4], oth[NT][4];
-                dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, acc);
-                if (dg_combine<R>(sm, st, acc, oth)) {
+                bool mine;
+                if (rg < 2) {
+                    dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, acc, rg);
+                    mine = set == rg;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) oth[nt][0] = oth[nt][1] = oth[nt][2] = oth[nt][3] = 0.f;
+                } else {
+                    dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, acc);
+                    mine = dg_combine<R>(sm, st, acc, oth);
+                }
+                if (mine) {
                     float (*dst)[HD] = rg == 0 ? sm.q : (rg == 1 ? sm.kn : sm.vn);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
@@ -498,10 +611,10 @@ k_depth_group(const __grid_constant__ DepthGroupMaps maps, DepthGroupArgs a) {
             dg_bar();
             fb_stamp(dbg, 3);
             // ---- this head's K-slice of out_proj, all 512 output rows
-            for (int rb = 0; rb < 8; ++rb) {
+            for (int rb = 0; rb < 8; ++rb) {   // row blocks alternate between the warp sets
                 float acc[NT][4];
-                dg_rowgroup<R>(sm, st, 1, &sm.attn[0][0], DG_AS, 0, 0, acc);
-                if (set == 0) dg_push_partial<R>(sm, c, rb, acc);
+                dg_rowgroup<R>(sm, st, 1, &sm.attn[0][0], DG_AS, 0, 0, acc, rb & 1);
+                if (set == (rb & 1)) dg_push_partial<R>(sm, c, rb, acc);
             }
             fb_stamp(dbg, 4);
             dg_residual_exchange<R>(sm, st, c, ph_rs, ph_ag);
@@ -527,16 +640,10 @@ k_depth_group(const __grid_constant__ DepthGroupMaps maps, DepthGroupArgs a) {
             }
             dg_bar();
             fb_stamp(dbg, 7);
-            for (int rb = 0; rb < 8; ++rb) {
-                float acc[NT][4], oth[NT][4];
-                dg_rowgroup<R>(sm, st, n_ub, &sm.g[0][0], DG_GS, 0, 64, acc);
-                if (dg_combine<R>(sm, st, acc, oth)) {
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) acc[nt][i] += oth[nt][i];
-                    dg_push_partial<R>(sm, c, rb, acc);
-                }
+            for (int rb = 0; rb < 8; ++rb) {   // a row block's boxes all go to one warp set: no combine, no barrier
+                float acc[NT][4];
+                dg_rowgroup<R>(sm, st, n_ub, &sm.g[0][0], DG_GS, 0, 64, acc, rb & 1);
+                if (set == (rb & 1)) dg_push_partial<R>(sm, c, rb, acc);
             }
             fb_stamp(dbg, 8);
             dg_residual_exchange<R>(sm, st, c, ph_rs, ph_ag);
@@ -549,16 +656,16 @@ k_depth_group(const __grid_constant__ DepthGroupMaps maps, DepthGroupArgs a) {
         dg_norm<R>(sm, a.final_norm, a.eps);
         dg_bar();
         for (int rb = 0; rb < 4; ++rb) {
-            float acc[NT][4], oth[NT][4];
-            dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, acc);
-            if (dg_combine<R>(sm, st, acc, oth)) {
+            float acc[NT][4];
+            dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, acc, rb & 1);
+            if (set == (rb & 1)) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int n = nt * 8 + 2 * t + (i & 1), row = c * 256 + rb * 64 + mt * 16 + g + (i >> 1) * 8;
                         if (n < n_valid) {
-                            const bf16 o = f2bf(acc[nt][i] + oth[nt][i]);
+                            const bf16 o = f2bf(acc[nt][i]);
                             a.logits[(size_t)(b0 + n) * a.CS + row] = o;
                             if (a.tap) a.tap[(size_t)(b0 + n) * (a.Q - 1) * a.CS + (size_t)(pos - 1) * a.CS + row] = o;
                         }

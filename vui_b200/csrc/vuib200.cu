@@ -25,6 +25,7 @@ struct WsLayout {
     size_t frame_ctr, rep_counts, rep_hist, rep_head, rep_filled;
     size_t trace;
     size_t xn, rq_xn, rq_attn, tc_partial, tc_counters;
+    size_t dg_layers, dg_head;   // box stream of the depth weights for k_depth_group (depth_group.cuh), 0 if none
     size_t fx_a, fx_b, fparts_a, fparts_b, rq_fx_a, rq_fx_b, rq_fparts_a, rq_fparts_b;
     size_t att_tiles, att_ntiles;
     size_t total;
@@ -69,6 +70,7 @@ struct VuibEngine {
     int fused_backbone;   // 0 = not asked yet, 1 = the two-kernel layers can run here, -1 = they cannot
     int fused_depth;
     int depth_group;      // same for the one-launch depth loop of many streams
+    bool dg_stream_ready; // the depth weights' box stream has been built in the workspace
     float* cb0_stats;   // optional (max_rows, 2) fp32: entropy and top probability of each cb0 draw
     TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
     char err[256];
@@ -122,6 +124,13 @@ static void make_layout(VuibEngine* e) {
     L.rq_attn = take(2 * RB * rd * 2);
     L.tc_partial = take((size_t)(TC_PARTIAL_TILES + 80) * TC_TILE_N * (R < 256 ? ((R + 15) / 16) * 16 : 256) * 4);
     L.tc_counters = take(2 * 256 * 4);
+    L.dg_layers = L.dg_head = 0;
+    if (c.rq_d_model == DG_D && c.rq_n_heads == DG_CL && c.rq_n_layers <= DG_LAYERS && c.rq_ffn % DG_CL == 0 &&
+        c.rq_ffn / DG_CL <= 192 && c.codebook_size == DG_CL * 256) {
+        const int n_ub = (c.rq_ffn / DG_CL + 63) / 64;
+        L.dg_layers = take((size_t)c.rq_n_layers * DG_CL * dg_boxes_per_layer(n_ub) * DG_BOX_BYTES);
+        L.dg_head = take((size_t)(c.n_quantizers - 1) * DG_CL * 32 * DG_BOX_BYTES);
+    }
     // fused two-kernel layers (single row): x as each block sees it, and the partial rows between blocks
     L.fx_a = take(d * 2);
     L.fx_b = take(d * 2);
@@ -186,6 +195,7 @@ template <class T>
 static T* wsp(VuibEngine* e, size_t off) { return reinterpret_cast<T*>(e->ws + off); }
 
 static void build_tc_maps(VuibEngine* e);
+static int32_t build_dg_stream(VuibEngine* e);
 
 // ---------------------------------------------------------------------------
 // GEMV launch: pick the row-tile size from M, K from the supported set.
@@ -288,7 +298,7 @@ extern "C" int32_t vuib_bind_workspace(VuibEngine* e, void* dev, size_t bytes) {
                     e->lay.total, bytes, dev);
     e->ws = static_cast<unsigned char*>(dev);
     e->have_ws = true;
-    return VUIB_OK;
+    return build_dg_stream(e);
 }
 
 extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
@@ -306,7 +316,7 @@ extern "C" int32_t vuib_bind_weights(VuibEngine* e, const VuibWeights* w) {
     e->w = *w;
     e->have_w = true;
     build_tc_maps(e);
-    return VUIB_OK;
+    return build_dg_stream(e);
 }
 
 extern "C" int32_t vuib_bind_kv(VuibEngine* e, void* const* k_dev, void* const* v_dev,
@@ -461,6 +471,38 @@ static void build_tc_maps(VuibEngine* e) {
         t->fused_depth = make_map_plain(&t->f_rq_out[i], e->w.rq_out_proj[i], rd, rd, rd / FB_CL, HD) &&
                          make_map_plain(&t->f_rq_w2[i], e->w.rq_w2[i], rd, c.rq_ffn, rd / FB_CL, FB_MLP_U_DEPTH * FB_CL);
     e->tc = t;
+}
+
+// Copies the depth weights into the box stream k_depth_group reads (once per binding; needs both the weights and
+// the workspace).  Runs on the legacy default stream and waits for it: binding happens outside any capture.
+static int32_t build_dg_stream(VuibEngine* e) {
+    e->dg_stream_ready = false;
+    if (!e->have_w || !e->have_ws || !e->lay.dg_layers) return VUIB_OK;
+    const VuibConfig& c = e->cfg;
+    DgStreamBuild b;
+    memset(&b, 0, sizeof(b));
+    for (int i = 0; i < c.rq_n_layers; ++i) {
+        b.wqkv[i] = static_cast<const bf16*>(e->w.rq_wqkv[i]);
+        b.out[i] = static_cast<const bf16*>(e->w.rq_out_proj[i]);
+        b.w1[i] = static_cast<const bf16*>(e->w.rq_w1[i]);
+        b.w3[i] = static_cast<const bf16*>(e->w.rq_w3[i]);
+        b.w2[i] = static_cast<const bf16*>(e->w.rq_w2[i]);
+    }
+    b.head = static_cast<const bf16*>(e->w.rq_head);
+    b.layers = e->ws + e->lay.dg_layers;
+    b.head_out = e->ws + e->lay.dg_head;
+    b.n_layers = c.rq_n_layers;
+    b.ffn = c.rq_ffn;
+    b.upc = c.rq_ffn / DG_CL;
+    b.n_ub = (b.upc + 63) / 64;
+    b.CS = c.codebook_size;
+    b.n_head_pos = c.n_quantizers - 1;
+    const int boxes = c.rq_n_layers * DG_CL * dg_boxes_per_layer(b.n_ub) + b.n_head_pos * DG_CL * 32;
+    k_build_dg_stream<<<boxes, 256>>>(b);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(0));
+    e->dg_stream_ready = true;
+    return VUIB_OK;
 }
 
 static bool tc_ok(VuibEngine* e, int M) {
@@ -1072,25 +1114,16 @@ static bool depth_group_ok(VuibEngine* e) {
         }
         e->depth_group = ok ? 1 : -1;
     }
-    return e->depth_group == 1 && !env_off("VUIB_NO_DEPTH_GROUP");
+    return e->depth_group == 1 && e->dg_stream_ready && !env_off("VUIB_NO_DEPTH_GROUP");
 }
 
 static int32_t launch_depth_group(VuibEngine* e, int B, const SampleArgs& sa_base, int Qn, cudaStream_t s) {
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
-    DepthGroupMaps maps;
-    for (int i = 0; i < c.rq_n_layers; ++i) {
-        maps.wqkv[i] = e->tc->rq_wqkv[i];
-        maps.out[i] = e->tc->rq_out[i];
-        maps.w1[i] = e->tc->rq_w1[i];
-        maps.w3[i] = e->tc->rq_w3[i];
-        maps.w2[i] = e->tc->rq_w2[i];
-    }
-    for (int i = c.rq_n_layers; i < DG_LAYERS; ++i) {
-        maps.wqkv[i] = maps.wqkv[0]; maps.out[i] = maps.out[0]; maps.w1[i] = maps.w1[0]; maps.w3[i] = maps.w3[0];
-        maps.w2[i] = maps.w2[0];
-    }
-    maps.head = e->tc->rq_head;
+    DepthGroupStream maps;
+    maps.layers = e->ws + L.dg_layers;
+    maps.head = e->ws + L.dg_head;
+    maps.boxes_per_layer = dg_boxes_per_layer((c.rq_ffn / DG_CL + 63) / 64);
     DepthGroupArgs a;
     memset(&a, 0, sizeof(a));
     a.B = B;
