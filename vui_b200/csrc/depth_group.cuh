@@ -191,6 +191,7 @@ struct DgState {
     int bi;         // boxes of the schedule passed so far
     int comb_buf;   // which hand-over buffer the next combine() uses
     bool dead;      // a wait of this thread ran out: skip the rest of its waits
+    int waited;     // the stage fill (bi / DG_STAGE) this thread last waited for: its other boxes need no second wait
     int32_t* flag;
     unsigned limit;
 };
@@ -239,7 +240,10 @@ __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, 
     const bool mine = owner < 0 || owner == set;
     auto fetch = [&](int j, Frag& f) {
         const int bi = base + j, slot = bi % DG_RING, stage = slot / DG_STAGE;
-        dg_wait_local_or_die(st, &sm.full[stage], (bi / DG_RING) & 1);
+        if (bi / DG_STAGE != st.waited) {   // an mbarrier wait costs ~250 cycles even when the copy has landed
+            dg_wait_local_or_die(st, &sm.full[stage], (bi / DG_RING) & 1);
+            st.waited = bi / DG_STAGE;
+        }
         const uint32_t bx = smem_u32(sm.ring[slot]);
         const int k0 = (j >> kshift) * kmul;
 #pragma unroll
@@ -482,7 +486,7 @@ k_depth_group(const DepthGroupStream strm, DepthGroupArgs a) {
     cluster_wait();
     const int set = warp >> 2, mt = warp & 3;   // warp set (even / odd boxes of a row group), 16-row tile of the box
     const int g = lane >> 2, t = lane & 3;
-    DgState st{0, 0, false, a.flag, a.spin_limit};
+    DgState st{0, 0, false, -1, a.flag, a.spin_limit};
     unsigned ph_rs = 0, ph_ag = 0, ph_lg = 0, ph_x = 0;
 
     for (int pos = 0; pos < n_pos; ++pos) {
