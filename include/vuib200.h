@@ -407,6 +407,57 @@ int32_t vuib_codec_check_flag(VuibCodec* c, void* stream);
 int32_t vuib_codec_read_tap(VuibCodec* c, int32_t which, float* out_host, int32_t n, void* stream);
 int64_t vuib_codec_launch_count(VuibCodec* c);
 
+/* ---------------------------------------------------------------------------
+ * Codec encoder: 24 kHz audio -> 16 codebook indices per 80 ms frame, fp32.
+ * Replaces the device work of QwenCodecEncoder.forward (src/vui/qwen_codec.py:385-390) as
+ * StreamingCodecEncoder re-runs it over its fixed 10 s buffer on every feed()/flush() (671-805).
+ * Weight pointers are borrowed and in torch's layouts.
+ * ------------------------------------------------------------------------- */
+typedef struct VuibCodecEncConfig {
+    int32_t base_dim;        /* 64 */
+    int32_t ratios[4];       /* 4, 5, 6, 8 */
+    int32_t d_model;         /* 512 */
+    int32_t n_layers;        /* 8 */
+    int32_t n_heads;         /* 8 (x 64) */
+    int32_t mlp_dim;         /* 2048 */
+    int32_t max_samples;     /* 240000: the 10 s buffer; a multiple of 1920 */
+} VuibCodecEncConfig;
+
+typedef struct VuibEncResBlockW { VuibConvW c3; VuibConvW c1; } VuibEncResBlockW;   /* ResBlock, 278-290 */
+typedef struct VuibEncLayerW {       /* EncTransformerBlock, 314-344 */
+    const float *ln1_w, *ln1_b, *wq, *wk, *wv, *wo, *attn_scale, *ln2_w, *ln2_b, *fc1, *fc2, *mlp_scale;
+} VuibEncLayerW;
+typedef struct VuibCodecEncWeights {
+    VuibConvW conv_in;               /* conv_encoder.layers.0: (64, 1, 7) */
+    VuibEncResBlockW res[4];         /* layers.1, 4, 7, 10: (C/2, C, 3), (C, C/2, 1) */
+    VuibConvW down[4];               /* layers.3, 6, 9, 12: (2C, C, 2r), stride r */
+    VuibConvW conv_out;              /* layers.14: (512, 1024, 3) */
+    VuibEncLayerW layer[VUIB_CODEC_LAYERS];
+    const float* rope_cos;           /* (max_samples / 960, 64), RoPE.forward (161-171) */
+    const float* rope_sin;
+    const float* downsample;         /* downsample.conv.weight (512, 512, 4), stride 2, no bias */
+    const float* sem_in;             /* quantizer.semantic.input_proj.weight (256, 512) */
+    const float* acq_in;             /* quantizer.acoustic.input_proj.weight (256, 512) */
+    const float* codebook[16];       /* semantic codebook 0, then acoustic 0..14: (2048, 256) */
+    const float* codebook_norm2[16]; /* squared norm of every code: (2048) */
+} VuibCodecEncWeights;
+
+typedef struct VuibCodecEnc VuibCodecEnc;
+
+int32_t vuib_codec_enc_create(const VuibCodecEncConfig* cfg, VuibCodecEnc** out);
+int32_t vuib_codec_enc_destroy(VuibCodecEnc* c);
+int32_t vuib_codec_enc_last_error(VuibCodecEnc* c, char* buf, size_t n);
+int32_t vuib_codec_enc_workspace_bytes(VuibCodecEnc* c, size_t* bytes);
+int32_t vuib_codec_enc_bind_workspace(VuibCodecEnc* c, void* dev, size_t bytes);
+int32_t vuib_codec_enc_bind_weights(VuibCodecEnc* c, const VuibCodecEncWeights* w);
+/* audio_dev float[n_samples] (n_samples a multiple of 1920, <= max_samples) -> codes_out_dev
+ * int64[n_q][n_samples / 1920] (n_q <= 16).  Stateless: every call encodes from zero left padding. */
+int32_t vuib_codec_enc_encode(VuibCodecEnc* c, const float* audio_dev, int32_t n_samples, int32_t n_q,
+                              int64_t* codes_out_dev, void* stream);
+/* Latents before quantisation of the last call, (512, n_samples / 1920) floats, for parity tests.  Synchronous. */
+int32_t vuib_codec_enc_read_latent(VuibCodecEnc* c, float* out_host, int32_t n, void* stream);
+int64_t vuib_codec_enc_launch_count(VuibCodecEnc* c);
+
 #ifdef __cplusplus
 }
 #endif

@@ -124,3 +124,88 @@ def test_product_codec_ctx_follows_the_same_policy(fx):
     assert a.shape[-1] == 6 * 1920 and all(s[2] <= 5 for s in dec2.calls)
     ctx2.reset()
     assert ctx2.n_frames == 0 and ctx2._stack is None
+
+
+# ---------------------------------------------------------------------------------------------- encoder
+ENC_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "codec_enc_fp32.pt")
+
+
+@pytest.fixture(scope="module")
+def efx():
+    return torch.load(ENC_GOLDEN)
+
+
+def codes_agree_up_to_near_ties(mine, ref, margin, tie=1e-3):
+    """Per frame the codes must be identical from codebook 0 up to the first codebook whose two nearest codes are
+    closer than `tie` in the reference (after such a flip the residual, hence every later codebook, differs).
+    Returns the number of frames that end at a near tie."""
+    cut = 0
+    for t in range(ref.shape[1]):
+        for q in range(ref.shape[0]):
+            if int(mine[q, t]) != int(ref[q, t]):
+                assert float(margin[q, t]) < tie, (q, t, int(mine[q, t]), int(ref[q, t]), float(margin[q, t]))
+                cut += 1
+                break
+    return cut
+
+
+def test_encoder_oracle_matches_reference(efx):
+    from oracle.codec_enc_oracle import EncoderOracle, test_audio
+    from vui_b200.codec_encoder import encoder_param_shapes, random_encoder_state
+
+    shapes = encoder_param_shapes()
+    assert len(shapes) == 161 and sum(torch.Size(s).numel() for s in shapes.values()) == 56168736
+    orc = EncoderOracle(random_encoder_state(0))
+    audio = test_audio(240000, seed=0)
+    codes = orc.encode(audio)[0]
+    assert codes.shape == (16, 125)
+    ref = efx["codes"].long()
+    assert (orc.latent - efx["latent"]).abs().max() <= 1e-4 * efx["latent"].abs().max()
+    assert codes_agree_up_to_near_ties(codes, ref, efx["margin"]) <= 2
+    assert (codes == ref).float().mean() > 0.98
+    # causality: a shorter buffer gives the same first frames
+    n = efx["short"].shape[1]
+    assert codes_agree_up_to_near_ties(orc.encode(audio[..., : n * 1920])[0], efx["short"].long(), efx["margin"][:, :n]) <= 1
+
+
+class _StubEncoder:
+    """Counts frames: code value = frame index, so a trace shows which frames each feed returned."""
+
+    n_q = 16
+
+    def __init__(self):
+        self.calls = 0
+
+    def parameters(self):
+        return iter([torch.zeros(1)])
+
+    def __call__(self, buf):
+        self.calls += 1
+        T = buf.shape[-1] // 1920
+        return torch.arange(T).view(1, 1, T).expand(1, self.n_q, T).clone()
+
+
+def test_product_streaming_encoder_follows_the_reference_protocol(efx):
+    """vui_b200.codec_encoder.StreamingCodecEncoder (host logic, no GPU): same chunks in, the same feeds return the
+    same number of frames at the same frame indices as the reference's trace, across the 10 s boundary."""
+    from vui_b200.codec_encoder import StreamingCodecEncoder
+
+    st = efx["stream"]
+    se = StreamingCodecEncoder(_StubEncoder())
+    assert se.max_samples == 240000 and se.max_frames == 125 and se.min_chunk_samples == 12 * 1920
+    first_frame = 0
+    for n, ref in zip(st["sizes"], st["feeds"]):
+        if se._pos + n > se.max_samples:
+            first_frame = 0                       # the buffer restarts at the boundary
+        got = se.feed(torch.zeros(n))
+        assert (got is None) == (ref is None)
+        if got is not None:
+            assert got.shape == ref.shape and got.dtype == torch.long
+            assert got[:, 0].tolist() == list(range(first_frame, first_frame + got.shape[0]))
+            first_frame += got.shape[0]
+    tail = se.flush()
+    assert (tail is None) == (st["flush"] is None)
+    if tail is not None:
+        assert tail.shape == st["flush"].shape
+    se.reset()
+    assert se._pos == 0 and se._emitted == 0 and se.feed(torch.zeros(0)) is None

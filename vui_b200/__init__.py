@@ -2,8 +2,9 @@
 reference's Engine / Row / GenConfig API."""
 
 from .codec import CodecCtx, QwenCodecDecoder
+from .codec_encoder import QwenCodecEncoder, StreamingCodecEncoder
 from .engine import Engine, GenConfig, RenderRequest, Row, Segment
 from .model import VuiB200, VuiShape
 
-__all__ = ["CodecCtx", "Engine", "GenConfig", "QwenCodecDecoder", "RenderRequest", "Row", "Segment", "VuiB200",
-           "VuiShape"]
+__all__ = ["CodecCtx", "Engine", "GenConfig", "QwenCodecDecoder", "QwenCodecEncoder", "RenderRequest", "Row", "Segment",
+           "StreamingCodecEncoder", "VuiB200", "VuiShape"]

@@ -21,6 +21,7 @@ _API_H = os.path.join(_ROOT, "include", "vuib200.h")
 UNITS = {
     "vuib200.cu": ["decode_kernels.cuh", "tc_gemm.cuh", "fused_blocks.cuh", "depth_group.cuh", "prefill_attn.cuh"],
     "codec.cu": ["codec_kernels.cuh"],
+    "codec_enc.cu": ["codec_enc_kernels.cuh"],
 }
 SOURCES = [os.path.join(_CSRC, u) for u in UNITS]
 HEADERS = sorted({os.path.join(_CSRC, h) for hs in UNITS.values() for h in hs}) + [_API_H]
@@ -117,6 +118,28 @@ class VuibCodecWeights(C.Structure):
     ]
 
 
+class VuibCodecEncConfig(C.Structure):
+    _fields_ = [("base_dim", C.c_int32), ("ratios", C.c_int32 * 4), ("d_model", C.c_int32), ("n_layers", C.c_int32),
+                ("n_heads", C.c_int32), ("mlp_dim", C.c_int32), ("max_samples", C.c_int32)]
+
+
+class VuibEncResBlockW(C.Structure):
+    _fields_ = [("c3", VuibConvW), ("c1", VuibConvW)]
+
+
+class VuibEncLayerW(C.Structure):
+    _fields_ = [(n, _F) for n in ("ln1_w", "ln1_b", "wq", "wk", "wv", "wo", "attn_scale", "ln2_w", "ln2_b", "fc1", "fc2",
+                                  "mlp_scale")]
+
+
+class VuibCodecEncWeights(C.Structure):
+    _fields_ = [
+        ("conv_in", VuibConvW), ("res", VuibEncResBlockW * 4), ("down", VuibConvW * 4), ("conv_out", VuibConvW),
+        ("layer", VuibEncLayerW * VUIB_CODEC_LAYERS), ("rope_cos", _F), ("rope_sin", _F), ("downsample", _F),
+        ("sem_in", _F), ("acq_in", _F), ("codebook", _F * 16), ("codebook_norm2", _F * 16),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/vuib200.h declares
 _P = C.c_void_p
 SYMBOLS = {
@@ -166,6 +189,15 @@ SYMBOLS = {
     "vuib_codec_check_flag": (C.c_int32, [_P, _P]),
     "vuib_codec_read_tap": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_float), C.c_int32, _P]),
     "vuib_codec_launch_count": (C.c_int64, [_P]),
+    "vuib_codec_enc_create": (C.c_int32, [C.POINTER(VuibCodecEncConfig), C.POINTER(_P)]),
+    "vuib_codec_enc_destroy": (C.c_int32, [_P]),
+    "vuib_codec_enc_last_error": (C.c_int32, [_P, C.c_char_p, C.c_size_t]),
+    "vuib_codec_enc_workspace_bytes": (C.c_int32, [_P, C.POINTER(C.c_size_t)]),
+    "vuib_codec_enc_bind_workspace": (C.c_int32, [_P, _P, C.c_size_t]),
+    "vuib_codec_enc_bind_weights": (C.c_int32, [_P, C.POINTER(VuibCodecEncWeights)]),
+    "vuib_codec_enc_encode": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P, _P]),
+    "vuib_codec_enc_read_latent": (C.c_int32, [_P, C.POINTER(C.c_float), C.c_int32, _P]),
+    "vuib_codec_enc_launch_count": (C.c_int64, [_P]),
 }
 
 
