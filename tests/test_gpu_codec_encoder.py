@@ -116,3 +116,71 @@ def test_streaming_encoder_reproduces_the_reference_trace(enc, efx):
     want = orc.encode(second)[0]
     have = enc(second.cuda())[0].cpu()
     assert (have == want).float().mean().item() > 0.97
+
+
+def test_serving_adapter_user_audio_commands(enc, nano_sd):
+    """encode_full / stream_start / stream_feed / stream_flush / stream_stop and decode_prompt through the command
+    queue, with this package's codec encoder and decoder attached (tts_worker.py:1404-1490, 1804-1878)."""
+    import queue
+    import threading
+    import zlib
+
+    from oracle.codec_enc_oracle import test_audio
+    from vui_b200 import VuiB200, VuiShape
+    from vui_b200.codec import QwenCodecDecoder
+    from vui_b200.serving import TTSEngine, tts_process
+
+    class StubTok:
+        vocab_size = 151936
+
+        def __init__(self):
+            self.special_to_id = {"[SC]": 151900}
+
+        def encode(self, text):
+            return torch.tensor([zlib.crc32(w.encode()) % 151000 for w in text.split()] or [1], dtype=torch.long)
+
+    model = VuiB200(VuiShape(), nano_sd, device="cuda", tokenizer=StubTok())
+    dec = QwenCodecDecoder.random_init(0, device="cuda")
+    cmd, out = queue.Queue(), queue.Queue()
+    th = threading.Thread(target=tts_process, daemon=True,
+                          args=(cmd, out, lambda: TTSEngine(model, codec_dec=dec, codec_enc=enc, max_seq=768).setup(),
+                                threading.Event()))
+    th.start()
+
+    def get(kind, timeout=180):
+        while True:
+            m = out.get(timeout=timeout)
+            assert m["type"] != "error", m
+            if m["type"] == kind:
+                return m
+
+    get("ready")
+    audio = test_audio(24000 * 4, seed=5)[0, 0]
+    cmd.put({"cmd": "encode_full", "audio": audio.numpy()})
+    full = get("encoded")["codes"]
+    assert full.shape == (50, 16) and full.dtype == torch.long and 0 <= full.min() and full.max() < 2048
+    cmd.put({"cmd": "stream_start"})
+    pos, parts = 0, []
+    for n in (9000, 30000, 20000, 37000):
+        cmd.put({"cmd": "stream_feed", "audio": audio[pos:pos + n].numpy()})
+        pos += n
+    cmd.put({"cmd": "stream_flush"})
+    cmd.put({"cmd": "stream_stop"})
+    while True:
+        m = out.get(timeout=180)
+        assert m["type"] != "error", m
+        if m["type"] == "codes":
+            parts.append(m["codes"])
+        if m["type"] == "codes_final":
+            assert m["n_frames"] == 50
+            break
+    streamed = torch.cat(parts, dim=0)
+    assert streamed.shape == (50, 16)
+    assert (streamed == full).float().mean().item() > 0.97     # causal: streamed partials equal the full encode
+    cmd.put({"cmd": "allocate_and_prefill", "codes": full[:30], "text": "the user said this", "settings": {}})
+    get("prompt_loaded")
+    cmd.put({"cmd": "decode_prompt"})
+    m = get("prompt_audio")
+    assert m["audio"].shape == (30 * 1920,) and m["sample_rate"] == 24000 and m["audio"].abs().max() <= 1
+    cmd.put({"cmd": "shutdown"})
+    th.join(timeout=60)

@@ -12,10 +12,12 @@ KV on-disk formats.
 * ``tts_process`` serves the command dicts of the reference's protocol from a queue and answers on
   another; it runs in a thread or a process.
 
-Audio codecs, the streaming encoder, VAD and ASR alignment are outside this package: commands that
-need raw audio answer with an error unless the caller attached an encoder object.  Without a codec
-with a streaming context, ``generate`` emits ``{"type": "codes"}`` events in place of
-``{"type": "audio"}``.
+The codec decoder and encoder are ``vui_b200.codec.QwenCodecDecoder`` and
+``vui_b200.codec_encoder.QwenCodecEncoder`` (or any objects with the same methods); with an encoder attached the
+user-audio commands ``encode_full`` / ``stream_start`` / ``stream_feed`` / ``stream_flush`` / ``stream_stop``
+work as in the reference (tts_worker.py:1404-1490, 1804-1878).  VAD and ASR alignment are outside this
+package.  Without a codec with a streaming context, ``generate`` emits ``{"type": "codes"}`` events in place
+of ``{"type": "audio"}``.
 """
 
 from __future__ import annotations
@@ -60,6 +62,11 @@ class TTSEngine:
         self.checkpoint_path: str | None = None
         self.engine: Engine | None = None
         self.row = None
+        self.stream_enc = None
+        self._prompt_rms = 0.0
+        self._reset_user_prefill()
+        self._stream_samples_fed = 0
+        self._stream_frames_emitted = 0
 
     @property
     def T(self) -> int:
@@ -73,7 +80,74 @@ class TTSEngine:
     def setup(self) -> "TTSEngine":
         self.engine = Engine(model=self.model, codec=self.codec_dec, max_rows=1, max_seq=self.max_seqlen)
         self.row = self.engine.new_row()
+        if self.codec_enc is not None:   # tts_worker.py:231-238
+            from .codec_encoder import StreamingCodecEncoder
+
+            self.stream_enc = StreamingCodecEncoder(self.codec_enc, n_quantizers=self.n_q, max_secs=10, min_chunk_frames=12)
+            self.stream_enc.setup_graph()
         return self
+
+    # ----------------------------------------------------------- user audio -> codes (tts_worker.py:1404-1490)
+    def _reset_user_prefill(self) -> None:
+        self._user_codes_parts: list[Tensor] = []
+        self._user_codes_consumed = 0
+        self._user_text_prefilled: list[str] = []
+        self._segment_start_idx = 0
+
+    def _normalize_audio(self, audio: Tensor) -> Tensor:
+        """Bring the user's level to the prompt's (gain within [0.25, 4]), tts_worker.py:369-376."""
+        if self._prompt_rms < 1e-6:
+            return audio
+        rms = audio.float().pow(2).mean().sqrt().item()
+        if rms < 1e-6:
+            return audio
+        return audio * max(0.25, min(4.0, self._prompt_rms / rms))
+
+    def _need_enc(self):
+        if self.codec_enc is None or self.stream_enc is None:
+            raise RuntimeError("no codec encoder is attached")
+
+    def encode_full(self, audio) -> Tensor:
+        self._need_enc()
+        a = torch.as_tensor(audio).float().reshape(1, 1, -1)
+        a = a[..., : a.shape[-1] // 1920 * 1920].to(self.device)
+        return self.codec_enc.encode(a)[0, : self.n_q].T.long().cpu()
+
+    def stream_start(self, *, continuation: bool = False) -> None:
+        self._need_enc()
+        self.stream_enc.reset()
+        if not continuation:
+            self._reset_user_prefill()
+        self._segment_start_idx = len(self._user_codes_parts)
+        self._stream_samples_fed = 0
+        self._stream_frames_emitted = 0
+
+    def _took(self, codes):
+        if codes is None:
+            return None
+        codes = codes.cpu()
+        self._user_codes_parts.append(codes)
+        self._stream_frames_emitted += codes.shape[0]
+        return codes
+
+    def stream_feed(self, audio):
+        self._need_enc()
+        a = self._normalize_audio(torch.as_tensor(audio).float())
+        self._stream_samples_fed += a.numel()
+        return self._took(self.stream_enc.feed(a))
+
+    def stream_flush(self):
+        self._need_enc()
+        return self._took(self.stream_enc.flush())
+
+    def stream_stop(self):
+        """Re-encode the whole buffered segment once more: more accurate than the streamed partials."""
+        self._need_enc()
+        self.stream_enc.flush()
+        total = self.stream_enc._emitted
+        if total == 0:
+            return None
+        return self.stream_enc._encode()[0, :, :total].T.long().cpu()
 
     # ----------------------------------------------------------- KV position, conditioning
     def reset(self) -> None:
@@ -392,6 +466,35 @@ def tts_process(cmd_queue, audio_queue, engine_or_factory, cancel_event=None) ->
                     if rewind_to is not None and rewind_to < engine.T:
                         engine.T = rewind_to
                     cancel_event.clear()
+                elif cmd == "encode_full":
+                    try:
+                        audio_queue.put({"type": "encoded", "codes": engine.encode_full(msg["audio"])})
+                    except Exception:  # noqa: BLE001 - the reference answers None and keeps serving
+                        traceback.print_exc()
+                        audio_queue.put({"type": "encoded", "codes": None})
+                elif cmd == "stream_start":
+                    engine.stream_start(continuation=bool(msg.get("continuation", False)))
+                elif cmd in ("stream_feed", "stream_flush"):
+                    codes = engine.stream_feed(msg["audio"]) if cmd == "stream_feed" else engine.stream_flush()
+                    if codes is not None:
+                        audio_queue.put({"type": "codes", "codes": codes})
+                elif cmd == "stream_stop":
+                    try:
+                        codes = engine.stream_stop()
+                        if codes is not None:   # the re-encoded segment replaces its streamed partials
+                            engine._user_codes_parts = engine._user_codes_parts[: engine._segment_start_idx] + [codes]
+                        audio_queue.put({"type": "codes_final", "n_frames": 0 if codes is None else codes.shape[0]})
+                    except Exception:  # noqa: BLE001
+                        traceback.print_exc()
+                        audio_queue.put({"type": "codes_final", "n_frames": 0})
+                elif cmd == "decode_prompt":
+                    if engine.prompt_codes is not None and engine.codec_dec is not None:
+                        codes = engine.prompt_codes.long().to(engine.device).T.unsqueeze(0)
+                        wav = engine.codec_dec.decode_chunked(codes, chunk_size=200)[0, 0].cpu().float()
+                        audio_queue.put({"type": "prompt_audio", "audio": wav, "sample_rate": 24000,
+                                         "codes_shape": list(engine.prompt_codes.shape)})
+                    else:
+                        audio_queue.put({"type": "prompt_audio", "audio": None})
                 elif cmd == "get_state":
                     audio_queue.put({"type": "state", "T": engine.T, "max_T": engine.max_seqlen,
                                      "has_prompt": engine.prompt_codes is not None, "prompt_text": engine.prompt_text or ""})
