@@ -16,7 +16,8 @@ Beside the headline the same line carries
               tokens/s, time to first frame, 375 greedy frames;
   streams256  configuration 5's per-GPU shape: 256 streams, 512-id prompts, 2048-position KV;
   codec       the step after the path: streaming codec decode of one stream's frames (16 codes ->
-              1920 samples, fp32), ms per frame, x realtime, HBM roofline on its 423 MB of weights.
+              1920 samples, fp32), ms per frame, x realtime, HBM roofline on its 423 MB of weights; and the
+              codec encoder's whole-buffer encode (10 s of audio -> codes) used for user turns.
 
 Under torchrun (N > 1) every rank is an independent replica with its own streams
 on its own GPU; there is no data-path collective, the process group only aligns
@@ -531,6 +532,48 @@ def codec_block(dev, cpu_baseline: bool, frames: int = 100, reps: int = 5, model
     return res
 
 
+def codec_encoder_block(dev, cpu_baseline: bool, reps: int = 5):
+    """Codec encoder: one call of StreamingCodecEncoder's whole-buffer encode (10 s of audio -> 16 x 125 codes)."""
+    import torch
+
+    from oracle.codec_enc_oracle import test_audio
+    from vui_b200.codec_encoder import QwenCodecEncoder, StreamingCodecEncoder
+
+    enc = QwenCodecEncoder.random_init(0, device=dev)
+    se = StreamingCodecEncoder(enc)
+    se.setup_graph()
+    se._audio_buf.copy_(test_audio(240000, seed=0).to(dev))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(reps):
+        torch.cuda.synchronize(dev)
+        e0.record()
+        se._graph.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    res = {"workload": "codec encoder, 10 s buffer (240000 samples -> 16 x 125 codes), fp32, seeded random weights; "
+                       f"median of {reps} graph replays",
+           "ms_per_buffer": ms, "x_realtime": 10e3 / ms, "launches": 91, "gflop": 40.0, "tflops": 40.0 / ms}
+    if cpu_baseline:
+        from oracle.codec_enc_oracle import EncoderOracle
+        from vui_b200.codec_encoder import random_encoder_state
+
+        torch.set_num_threads(os.cpu_count() or 1)
+        orc = EncoderOracle(random_encoder_state(0))
+        a = test_audio(240000, seed=0)
+        orc.encode(a)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            orc.encode(a)
+        res["cpu_baseline"] = {"value": 1e3 * (time.perf_counter() - t0) / 3, "unit": "ms per buffer", "cores": os.cpu_count() or 1,
+                               "kind": "port", "sample": "3 encodes of the same buffer, oracle/codec_enc_oracle.py fp32 on torch CPU"}
+    del se, enc
+    torch.cuda.empty_cache()
+    return res
+
+
 def profile_codec(dev, n):
     """`n` streamed codec frames kernel by kernel (no graph) after 3 warm-up frames: for ncu."""
     import torch
@@ -616,6 +659,7 @@ def run_b200(args):
     if B == 1 and not args.no_batched and rank == 0:
         try:
             codec = codec_block(dev, world == 1 and not args.no_cpu_baseline, model=model)
+            codec["encoder"] = codec_encoder_block(dev, world == 1 and not args.no_cpu_baseline)
         except Exception as exc:  # noqa: BLE001 - an extra block must never take the bench line down
             print(f"codec block failed: {exc}", file=sys.stderr)
     if B == 1 and not args.no_batched:
