@@ -26,7 +26,8 @@ the timed window and takes the max time over ranks.
 `--impl reference` times the CPU restatement of the reference's PyTorch path
 (oracle/, fp32, all host threads) on the same metric.  `--profile-frames N` runs N
 frames kernel by kernel (no graph) and exits: the command the ncu summaries under
-profiles/ are taken with; `--profile-codec N` does the same for N streamed codec frames.
+profiles/ are taken with; `--profile-codec N` does the same for N streamed codec frames, `--profile-encoder N`
+for N codec-encoder calls.
 """
 
 from __future__ import annotations
@@ -595,6 +596,25 @@ def profile_codec(dev, n):
                       "launches_per_frame": (dec.launch_count() - before) // max(n, 1)}), flush=True)
 
 
+def profile_encoder(dev, n):
+    """`n` whole-buffer encodes of the codec encoder kernel by kernel after one warm-up call: for ncu."""
+    import torch
+
+    from oracle.codec_enc_oracle import test_audio
+    from vui_b200.codec_encoder import QwenCodecEncoder
+
+    enc = QwenCodecEncoder.random_init(0, device=dev)
+    a = test_audio(240000, seed=0).to(dev)
+    enc(a)
+    torch.cuda.synchronize(dev)
+    before = enc.launch_count()
+    for _ in range(n):
+        enc(a)
+    torch.cuda.synchronize(dev)
+    print(json.dumps({"profile_encoder": n, "launches_before": before,
+                      "launches_per_encode": (enc.launch_count() - before) // max(n, 1)}), flush=True)
+
+
 def profile_frames(model, dev, n, B, prompt_len):
     """Prefill B streams of `prompt_len` ids, then `n` frames kernel by kernel (no graph): the command the
     `ncu` launch lists and captures under profiles/ are taken with."""
@@ -637,6 +657,9 @@ def run_b200(args):
 
     if args.profile_codec:
         profile_codec(dev, args.profile_codec)
+        return
+    if args.profile_encoder:
+        profile_encoder(dev, args.profile_encoder)
         return
     model = VuiB200.random_init(VuiShape(), seed=0, device=dev)
     if args.profile_frames:
@@ -771,6 +794,7 @@ def main():
     ap.add_argument("--no-batched", action="store_true", help="skip the 64-stream, cfg4 and 256-stream blocks")
     ap.add_argument("--profile-frames", type=int, default=0, help="run N frames without a graph and exit (for ncu)")
     ap.add_argument("--profile-codec", type=int, default=0, help="run N streamed codec frames without a graph and exit")
+    ap.add_argument("--profile-encoder", type=int, default=0, help="run N codec-encoder calls on a 10 s buffer and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

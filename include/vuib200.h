@@ -425,7 +425,9 @@ typedef struct VuibCodecEncConfig {
 
 typedef struct VuibEncResBlockW { VuibConvW c3; VuibConvW c1; } VuibEncResBlockW;   /* ResBlock, 278-290 */
 typedef struct VuibEncLayerW {       /* EncTransformerBlock, 314-344 */
-    const float *ln1_w, *ln1_b, *wq, *wk, *wv, *wo, *attn_scale, *ln2_w, *ln2_b, *fc1, *fc2, *mlp_scale;
+    const float *ln1_w, *ln1_b;
+    const float* wqkv;     /* q_proj | k_proj | v_proj weights stacked by rows: (1536, 512) */
+    const float *wo, *attn_scale, *ln2_w, *ln2_b, *fc1, *fc2, *mlp_scale;
 } VuibEncLayerW;
 typedef struct VuibCodecEncWeights {
     VuibConvW conv_in;               /* conv_encoder.layers.0: (64, 1, 7) */

@@ -128,8 +128,7 @@ class VuibEncResBlockW(C.Structure):
 
 
 class VuibEncLayerW(C.Structure):
-    _fields_ = [(n, _F) for n in ("ln1_w", "ln1_b", "wq", "wk", "wv", "wo", "attn_scale", "ln2_w", "ln2_b", "fc1", "fc2",
-                                  "mlp_scale")]
+    _fields_ = [(n, _F) for n in ("ln1_w", "ln1_b", "wqkv", "wo", "attn_scale", "ln2_w", "ln2_b", "fc1", "fc2", "mlp_scale")]
 
 
 class VuibCodecEncWeights(C.Structure):

@@ -138,7 +138,8 @@ class QwenCodecEncoder:
         for l in range(N_LAYERS):
             q, lw = f"transformer.layers.{l}.", w.layer[l]
             lw.ln1_w, lw.ln1_b = P(sd[q + "input_layernorm.weight"]), P(sd[q + "input_layernorm.bias"])
-            lw.wq, lw.wk, lw.wv, lw.wo = (P(sd[q + n + ".weight"]) for n in ("q_proj", "k_proj", "v_proj", "o_proj"))
+            lw.wqkv = P(torch.cat([sd[q + n + ".weight"] for n in ("q_proj", "k_proj", "v_proj")], dim=0))
+            lw.wo = P(sd[q + "o_proj.weight"])
             lw.attn_scale, lw.mlp_scale = P(sd[q + "attn_scale"]), P(sd[q + "mlp_scale"])
             lw.ln2_w, lw.ln2_b = P(sd[q + "post_attention_layernorm.weight"]), P(sd[q + "post_attention_layernorm.bias"])
             lw.fc1, lw.fc2 = P(sd[q + "fc1.weight"]), P(sd[q + "fc2.weight"])

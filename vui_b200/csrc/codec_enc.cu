@@ -18,7 +18,7 @@ struct VuibCodecEnc {
     unsigned char* ws;
     bool have_ws, have_w;
     int64_t launches;
-    size_t off_a, off_b, off_x, off_n, off_q, off_k, off_v, off_o, off_g, off_d, off_hs, off_ha, total;
+    size_t off_a, off_b, off_x, off_n, off_q, off_o, off_g, off_d, off_hs, off_ha, total;
     int last_frames;
     char err[256];
 };
@@ -50,8 +50,9 @@ cudaError_t conv(VuibCodecEnc* c, const float* w, const float* bias, const float
     a.w = w; a.bias = bias; a.x = x; a.res = res; a.scale = scale; a.y = y;
     a.Cin = Cin; a.Cout = Cout; a.K = K; a.stride = stride; a.Tin = Tin; a.Tout = Tin / stride;
     a.elu_in = elu_in ? 1 : 0; a.epi = epi;
+    a.cc = K == 1 ? 32 : 8;
     const int XW = EC_T * stride + (K - stride);
-    const size_t smem = (size_t)(EC_CC * XW + EC_CO * (EC_CC * K + 1)) * 4;
+    const size_t smem = (size_t)(a.cc * XW + EC_CO * (a.cc * K + 1)) * 4;
     dim3 grid((a.Tout + EC_T - 1) / EC_T, (Cout + EC_CO - 1) / EC_CO);
     c->launches++;
     k_econv<<<grid, EC_THREADS, smem, s>>>(a);
@@ -80,9 +81,7 @@ extern "C" int32_t vuib_codec_enc_create(const VuibCodecEncConfig* cfg, VuibCode
     c->off_b = take(64 * T0);
     c->off_x = take(512 * T25);
     c->off_n = take(512 * T25);
-    c->off_q = take(512 * T25);
-    c->off_k = take(512 * T25);
-    c->off_v = take(512 * T25);
+    c->off_q = take(3 * 512 * T25);
     c->off_o = take(512 * T25);
     c->off_g = take((size_t)g.mlp_dim * T25);
     c->off_d = take(512 * T12);
@@ -176,19 +175,16 @@ extern "C" int32_t vuib_codec_enc_encode(VuibCodecEnc* c, const float* audio_dev
     // ---- EncTransformer (314-365) on [512][T], T = 25 Hz frames
     const int D = g.d_model, H = g.n_heads;
     float* nrm = wsf(c, c->off_n);
-    float* q = wsf(c, c->off_q);
-    float* k = wsf(c, c->off_k);
-    float* v = wsf(c, c->off_v);
+    float* q = wsf(c, c->off_q);   // [3 * 512][T]: q, k, v
     float* o = wsf(c, c->off_o);
     float* gact = wsf(c, c->off_g);
     for (int l = 0; l < g.n_layers; ++l) {
         const VuibEncLayerW& lw = w.layer[l];
         k_elayernorm<<<(T + 31) / 32, 256, 0, s>>>(x, lw.ln1_w, lw.ln1_b, nrm, D, T);
         c->launches++;
-        CK(conv(c, lw.wq, nullptr, nrm, q, D, D, 1, 1, T, false, EE_BIAS, nullptr, nullptr, s));
-        CK(conv(c, lw.wk, nullptr, nrm, k, D, D, 1, 1, T, false, EE_BIAS, nullptr, nullptr, s));
-        CK(conv(c, lw.wv, nullptr, nrm, v, D, D, 1, 1, T, false, EE_BIAS, nullptr, nullptr, s));
-        k_eattn<<<(H * T + 3) / 4, 128, 0, s>>>(q, k, v, w.rope_cos, w.rope_sin, o, H, T);
+        // q | k | v rows stacked in one matrix: one launch with three times the CTAs
+        CK(conv(c, lw.wqkv, nullptr, nrm, q, D, 3 * D, 1, 1, T, false, EE_BIAS, nullptr, nullptr, s));
+        k_eattn<<<(H * T + 3) / 4, 128, 0, s>>>(q, q + (size_t)D * T, q + (size_t)2 * D * T, w.rope_cos, w.rope_sin, o, H, T);
         c->launches++;
         CK(conv(c, lw.wo, nullptr, o, x, D, D, 1, 1, T, false, EE_SCALE_RES, x, lw.attn_scale, s));
         k_elayernorm<<<(T + 31) / 32, 256, 0, s>>>(x, lw.ln2_w, lw.ln2_b, nrm, D, T);

@@ -30,11 +30,12 @@ struct EConvArgs {
     const float* scale;  // [Cout] (EE_SCALE_RES)
     float* y;            // [Cout][Tout]
     int Cin, Cout, K, stride, Tin, Tout;
+    int cc;              // input channels per staging step (8, or 32 for k = 1: fewer, fatter steps)
     int elu_in;          // ELU on the input (the nn.ELU() that precedes the convolution)
     int epi;
 };
 
-constexpr int EC_CO = 32, EC_T = 64, EC_CC = 8, EC_THREADS = 128;
+constexpr int EC_CO = 32, EC_T = 64, EC_THREADS = 128;
 
 // y[co][t] = bias[co] + sum_{ci, j} w[co][ci][j] * act(x)[ci][t * stride + j - (K - stride)]   (zero left padding:
 // CausalConv1d outside a streaming context, qwen_codec.py:92-98), then the epilogue.
@@ -43,9 +44,10 @@ __global__ void __launch_bounds__(EC_THREADS) k_econv(EConvArgs a) {
     extern __shared__ float sm[];
     const int K = a.K, s = a.stride, pad = K - s;
     const int XW = EC_T * s + pad;                 // input columns one tile needs
+    const int CC = a.cc;
     float* xs = sm;                                // [CC][XW]
-    float* ws = sm + EC_CC * XW;                   // [32][CC * K + 1]
-    const int WS = EC_CC * K + 1;
+    float* ws = sm + CC * XW;                      // [32][CC * K + 1]
+    const int WS = CC * K + 1;
     const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;   // ty: 16 groups of 2 channels
     const int t0 = blockIdx.x * EC_T, co0 = blockIdx.y * EC_CO;
     const int x0 = t0 * s - pad;                   // input column of window position 0
@@ -54,9 +56,11 @@ __global__ void __launch_bounds__(EC_THREADS) k_econv(EConvArgs a) {
     for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
-    for (int c0 = 0; c0 < a.Cin; c0 += EC_CC) {
-        const int nc = min(EC_CC, a.Cin - c0);
-        for (int i = tid; i < EC_CC * XW; i += EC_THREADS) {
+    for (int c0 = 0; c0 < a.Cin; c0 += CC) {
+        const int nc = min(CC, a.Cin - c0);
+        // staging loads are unrolled so that several are in flight (they are what bounds a step at small grids)
+#pragma unroll 8
+        for (int i = tid; i < CC * XW; i += EC_THREADS) {
             const int c = i / XW, p = i - c * XW, col = x0 + p;
             float v = 0.f;
             if (c < nc && col >= 0 && col < a.Tin) {
@@ -65,13 +69,15 @@ __global__ void __launch_bounds__(EC_THREADS) k_econv(EConvArgs a) {
             }
             xs[i] = v;
         }
-        for (int i = tid; i < EC_CO * EC_CC * K; i += EC_THREADS) {
-            const int r = i / (EC_CC * K), e = i - r * (EC_CC * K), co = co0 + r;
+#pragma unroll 8
+        for (int i = tid; i < EC_CO * CC * K; i += EC_THREADS) {
+            const int r = i / (CC * K), e = i - r * (CC * K), co = co0 + r;
             float v = 0.f;
             if (co < a.Cout && e < nc * K) v = __ldg(a.w + ((size_t)co * a.Cin + c0) * K + e);
             ws[r * WS + e] = v;
         }
         __syncthreads();
+#pragma unroll 2
         for (int c = 0; c < nc; ++c)
             for (int j = 0; j < K; ++j) {
                 const float w0 = ws[(ty * 2) * WS + c * K + j], w1 = ws[(ty * 2 + 1) * WS + c * K + j];
