@@ -41,6 +41,7 @@ constexpr int DG_THREADS = DG_CONSUMERS + 32;
 constexpr int DG_RING = 16;          // boxes in the ring
 constexpr int DG_STAGE = 4;          // boxes per stage: one full / empty mbarrier pair, one producer wake-up
 constexpr int DG_STAGES = DG_RING / DG_STAGE;
+static_assert(DG_STAGE == 4 && DG_RING == 16, "dg_rowgroup shifts by these");
 constexpr int DG_BOX_BYTES = 64 * 64 * 2;
 constexpr int DG_LAYERS = 4;
 constexpr int DG_D = 512;
@@ -223,12 +224,17 @@ __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, 
                                             int kshift, int kmul, float (&acc)[R / 8][4], int owner = -1) {
     constexpr int NT = R / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int set = warp >> 2, mt = warp & 3, g = lane >> 2, t = lane & 3;
+    const int set = warp >> 2, mt = warp & 3;
     const int base = st.bi;
     st.bi += nbox;
-    // A warp's chain per box (wait, ldmatrix, fragment loads, MMAs, release) bounds the kernel: the four k-steps of
-    // a box go to four independent accumulators (added at the end) instead of one dependent chain, and the
-    // fragments of the warp's next box are fetched while the MMAs of the current one are in flight.
+    // A warp runs this loop alone on its scheduler, so every dependent instruction of the per-box bookkeeping costs
+    // its full latency: a box is ~60 instructions here (it was ~300 with per-element activation loads and 64-bit
+    // address arithmetic, 490 cycles per box against the 128 the shared-memory port allows).  Everything that does
+    // not change from box to box is computed once: the lane's four ldmatrix offsets into a swizzled box, and the
+    // lane's row address for the activation fragments, which are ldmatrix loads too (an activation row is k-major,
+    // so a non-transposed 8x8 matrix is the B fragment of eight streams).
+    // The four k-steps of a box go to four independent accumulators (added at the end), and the fragments of the
+    // warp's next box are fetched while the MMAs of the current one are in flight.
     float c4[4][NT][4];
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks)
@@ -238,26 +244,37 @@ __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, 
     Frag f0, f1;   // two named buffers (a run-time buffer index would put them in local memory)
     const int first = owner < 0 ? set : 0, step = owner < 0 ? 2 : 1;   // this set's boxes: first, first + step, ...
     const bool mine = owner < 0 || owner == set;
-    auto fetch = [&](int j, Frag& f) {
-        const int bi = base + j, slot = bi % DG_RING, stage = slot / DG_STAGE;
-        if (bi / DG_STAGE != st.waited) {   // an mbarrier wait costs ~250 cycles even when the copy has landed
-            dg_wait_local_or_die(st, &sm.full[stage], (bi / DG_RING) & 1);
-            st.waited = bi / DG_STAGE;
-        }
-        const uint32_t bx = smem_u32(sm.ring[slot]);
-        const int k0 = (j >> kshift) * kmul;
+    uint32_t a_off[4];
+    {
+        const int row = mt * 16 + (lane & 15);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const int row = mt * 16 + (lane & 15), chunk = ks * 2 + (lane >> 4);
+        for (int ks = 0; ks < 4; ++ks) a_off[ks] = (uint32_t)(row * 128 + (((ks * 2 + (lane >> 4)) ^ (row & 7)) << 4));
+    }
+    const uint32_t ring_s = smem_u32(sm.ring[0]), empty_s = smem_u32(&sm.empty[0]);
+    // matrix (lane >> 3) of an x4 load is k-offset 8 * (lane >> 3); its row (lane & 7) is stream nt * 8 + (lane & 7)
+    const uint32_t b_row = smem_u32(act) + (uint32_t)(((lane & 7) * astride + (lane >> 3) * 8) * 2);
+    auto fetch = [&](int j, Frag& f) {
+        const int bi = base + j;
+        if ((bi >> 2) != st.waited) {   // an mbarrier wait costs ~250 cycles even when the copy has landed
+            dg_wait_local_or_die(st, &sm.full[(bi & (DG_RING - 1)) >> 2], (bi / DG_RING) & 1);
+            st.waited = bi >> 2;
+        }
+        const uint32_t bx = ring_s + (uint32_t)((bi & (DG_RING - 1)) * DG_BOX_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(f.a[ks][0]), "=r"(f.a[ks][1]), "=r"(f.a[ks][2]), "=r"(f.a[ks][3])
-                         : "r"(bx + row * 128 + ((chunk ^ (row & 7)) << 4)));
+                         : "r"(bx + a_off[ks]));
+        const uint32_t kb = b_row + (uint32_t)(((j >> kshift) * kmul) * 2);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const bf16* ap = act + (size_t)(nt * 8 + g) * astride + k0 + ks * 16 + 2 * t;
-                f.b[ks][nt][0] = *reinterpret_cast<const uint32_t*>(ap);
-                f.b[ks][nt][1] = *reinterpret_cast<const uint32_t*>(ap + 8);
-            }
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t ba = kb + (uint32_t)(nt * 8 * astride * 2);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(f.b[0][nt][0]), "=r"(f.b[0][nt][1]), "=r"(f.b[1][nt][0]), "=r"(f.b[1][nt][1])
+                         : "r"(ba));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(f.b[2][nt][0]), "=r"(f.b[2][nt][1]), "=r"(f.b[3][nt][0]), "=r"(f.b[3][nt][1])
+                         : "r"(ba + 64));
         }
     };
     // MMAs of box j, then its release: issuing the MMAs has taken the box's fragments out of shared memory
@@ -271,10 +288,9 @@ __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, 
                              : "r"(f.a[ks][0]), "r"(f.a[ks][1]), "r"(f.a[ks][2]), "r"(f.a[ks][3]),
                                "r"(f.b[ks][nt][0]), "r"(f.b[ks][nt][1]));
         __syncwarp();
-        if (lane == 0) {
-            const int stage = ((base + j) % DG_RING) / DG_STAGE;
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.empty[stage])) : "memory");
-        }
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                         ::"r"(empty_s + (uint32_t)((((base + j) & (DG_RING - 1)) >> 2) * 8)) : "memory");
     };
     if (mine) {
         if (first < nbox) fetch(first, f0);
