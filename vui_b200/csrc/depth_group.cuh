@@ -294,6 +294,7 @@ __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, 
     };
     if (mine) {
         if (first < nbox) fetch(first, f0);
+#pragma unroll
         for (int j = first; j < nbox; j += 2 * step) {
             consume(j, f0);
             if (j + step < nbox) {
