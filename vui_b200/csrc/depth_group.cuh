@@ -73,8 +73,8 @@ struct DgStreamBuild {
 };
 
 // One CTA per box of the stream; the box sequence of a layer is q|k|v rows of head c (8 K-chunks each), the
-// head's K-slice of out_proj (8 row blocks), w1/w3 of the CTA's hidden units (per 64 units: 8 K-chunks, w1 and w3
-// alternating), the CTA's K-slice of w2 (8 row blocks x n_ub column blocks).
+// head's K-slice of out_proj (8 row blocks), w1/w3 of the CTA's hidden units (per 64 units: the 8 K-chunks of w1, then
+// the 8 of w3), the CTA's K-slice of w2 (8 row blocks x n_ub column blocks).
 __global__ void __launch_bounds__(256) k_build_dg_stream(DgStreamBuild b) {
     const int bpl = dg_boxes_per_layer(b.n_ub);
     const int n_layer_boxes = b.n_layers * DG_CL * bpl;
@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(256) k_build_dg_stream(DgStreamBuild b) {
         if (j < 24) { W = b.wqkv[l]; N = 3 * DG_D; K = DG_D; x = (j % 8) * 64; y = (j / 8) * DG_D + c * HD; }
         else if ((j -= 24) < 8) { W = b.out[l]; N = DG_D; K = DG_D; x = c * HD; y = j * 64; }
         else if ((j -= 8) < 16 * b.n_ub) {
-            const int ub = j / 16, kb = (j % 16) / 2;
-            W = (j & 1) ? b.w3[l] : b.w1[l]; N = b.ffn; K = DG_D; x = kb * 64; y = c * b.upc + ub * 64;
+            const int ub = j / 16, kb = j % 8;
+            W = (j % 16) >= 8 ? b.w3[l] : b.w1[l]; N = b.ffn; K = DG_D; x = kb * 64; y = c * b.upc + ub * 64;
         } else {
             j -= 16 * b.n_ub;
             W = b.w2[l]; N = DG_D; K = b.ffn; x = c * b.upc + (j % b.n_ub) * 64; y = (j / b.n_ub) * 64;
@@ -645,9 +645,12 @@ k_depth_group(const DepthGroupStream strm, DepthGroupArgs a) {
             dg_bar();
             fb_stamp(dbg, 6);
             for (int ub = 0; ub < n_ub; ++ub) {
-                float acc[NT][4], oth[NT][4];
-                dg_rowgroup<R>(sm, st, 16, &sm.h[0][0], DG_XS, 1, 64, acc);  // even boxes w1, odd boxes w3
-                if (dg_combine<R>(sm, st, acc, oth)) {
+                // w1's row group is the first warp set's, w3's the second's (both fit the ring at once, and a warp
+                // waits for its own two stage fills only); the second set hands its sums over for the gate product
+                float acc[NT][4], a3[NT][4], oth[NT][4];
+                dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, acc, 0);
+                dg_rowgroup<R>(sm, st, 8, &sm.h[0][0], DG_XS, 0, 64, a3, 1);
+                if (dg_combine<R>(sm, st, a3, oth)) {
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
