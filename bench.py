@@ -255,6 +255,8 @@ class Bench:
         # end to end: host-driven loop, codes H2D + replay + codes/EOS D2H every frame
         lat, e2e_ms = [], None
         if e2e:
+            # the library captures its host-to-host frame graph on first use: outside the timed region
+            eng._frame_host(B, eng._g_codes_in[:B].cpu().pin_memory())
             e2e_blocks = []
             for _ in range(max(1, min(reps, 5))):
                 eng.seq_lens.copy_(seq0)
@@ -262,11 +264,9 @@ class Bench:
                 h_in = eng._g_codes_in[:B].cpu().pin_memory()
                 self.barrier()
                 t0 = time.perf_counter()
-                for _ in range(K):
+                for _ in range(K):  # one library call per frame: H2D codes, the frame, D2H codes + EOS, one graph launch
                     t1 = time.perf_counter()
-                    eng._g_codes_in[:B].copy_(h_in, non_blocking=True)
-                    graph.replay()
-                    h_codes, h_eos = eng._read_frame(B)
+                    h_codes, h_eos = eng._frame_host(B, h_in)
                     h_in.copy_(h_codes)
                     lat.append(time.perf_counter() - t1)
                 torch.cuda.synchronize(dev)

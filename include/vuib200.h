@@ -188,6 +188,24 @@ int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* slots_dev,
                           void* hidden_out_dev, void* cb0_out_dev, void* eos_out_dev,
                           float* eos_prob_out_dev, void* stream);
 
+/* One whole frame from and to HOST memory, as one CUDA-graph launch: what the per-frame body of `_stream_row`
+ * (engine.py:1450-1546: replay the frame, read the codes and the EOS probability back) costs a serving loop.
+ *
+ * vuib_frame_host_capture records, for this B and these device buffers, the graph
+ *   [pinned staging -> codes_io (only when with_h2d != 0)] -> vuib_decode_frame -> [codes_io, eos_prob -> pinned staging]
+ * on `stream` (a stream of the caller's, not the default stream).  The kernels must have run once before (module
+ * loading cannot happen inside a capture): call vuib_decode_frame, or replay a captured one, first.  Capturing again
+ * for the same (B, with_h2d) replaces the earlier graph.  The staging buffers and graphs are freed by vuib_destroy.
+ *
+ * vuib_frame_host copies codes_in_host (B, Q) int64 into the staging buffer (with_h2d != 0), launches the graph,
+ * waits for it on `stream` and copies the frame's codes (B, Q) and EOS probabilities (B, may be NULL) out.  The
+ * device buffers named at capture must still be alive.  Returns VUIB_ERR_UNBOUND without a captured graph. */
+int32_t vuib_frame_host_capture(VuibEngine* e, int32_t B, int32_t with_h2d, const int32_t* slots_dev,
+                                const int32_t* seq_inc_dev, int64_t* codes_io_dev, void* hidden_out_dev,
+                                void* cb0_out_dev, void* eos_out_dev, float* eos_prob_out_dev, void* stream);
+int32_t vuib_frame_host(VuibEngine* e, int32_t B, int32_t with_h2d, const int64_t* codes_in_host,
+                        int64_t* codes_out_host, float* eos_prob_out_host, void* stream);
+
 /* Decode attention alone over layer `layer` of the bound KV cache: the device work of the
  * flash_attn_with_kvcache call (MHA.forward_flash, model.py:247-257) minus the append, which
  * the QKV kernel has already done.  Row r attends keys [0, row_pos[r]] of slot row_slot[r];

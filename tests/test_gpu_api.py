@@ -181,3 +181,46 @@ def test_cb0_statistics_and_streaming_entropy_gate(model_tok):
     assert [t for t in temps if t is not None] == [0.5, 0.3]
     assert gated.shape == plain.shape and gated.min() >= 0 and gated.max() < 2048
     eng.check_device()
+
+
+def test_frame_through_host_memory_equals_replay_and_read(model_tok):
+    """vuib_frame_host (host -> device codes, the frame, device -> host codes and EOS, one graph launch inside the
+    library) produces the frames that a graph replay followed by the engine's read-back produces, with and
+    without the input copy, for one stream and for three (padded to a bucket of four)."""
+    from vui_b200 import Engine
+
+    ids = torch.randint(0, 1000, (40,), generator=torch.Generator().manual_seed(3))
+
+    def start(n_rows):
+        eng = Engine(model=model_tok, max_rows=4, max_seq=256, seed=11)
+        rows = [eng.new_row() for _ in range(n_rows)]
+        hid = torch.stack([eng.prefill_ids(r, ids[: 30 + 3 * i]) for i, r in enumerate(rows)])
+        eng._apply_cfg(None, greedy=True)
+        eng._g_slot_idx[:n_rows] = torch.tensor([r.idx for r in rows], device=eng.device, dtype=torch.int32)
+        eng._g_seq_inc[:n_rows].fill_(1)
+        eng._g_codes_in[:n_rows] = eng._first_frames(rows, hid)
+        return eng
+
+    for n_rows in (1, 3):
+        ref = start(n_rows)
+        want = []
+        for _ in range(5):
+            ref._frame_step(n_rows)
+            c, e = ref._read_frame(n_rows)
+            want.append((c.clone(), e.clone()))
+        ref.check_device()
+
+        a = start(n_rows)  # results only
+        for c, e in want:
+            hc, he = a._frame_host(n_rows)
+            assert torch.equal(hc, c) and torch.equal(he, e)
+        a.check_device()
+
+        b = start(n_rows)  # the previous frame's codes travel through host memory as well
+        h_in = b._g_codes_in[:n_rows].cpu().pin_memory()
+        for c, e in want:
+            hc, he = b._frame_host(n_rows, h_in)
+            assert torch.equal(hc, c) and torch.equal(he, e)
+            h_in.copy_(hc)
+        b.check_device()
+        assert torch.equal(a.seq_lens, ref.seq_lens) and torch.equal(b.seq_lens, ref.seq_lens)

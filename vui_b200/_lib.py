@@ -159,6 +159,8 @@ SYMBOLS = {
     "vuib_heads": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P]),
     "vuib_depth_step": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, C.c_int32, _P, _P, _P]),
     "vuib_decode_frame": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "vuib_frame_host_capture": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "vuib_frame_host": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P]),
     "vuib_attention": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "vuib_attention_noalloc": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P,
                                            C.c_char_p, C.c_size_t]),

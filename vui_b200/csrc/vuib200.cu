@@ -73,8 +73,40 @@ struct VuibEngine {
     bool dg_stream_ready; // the depth weights' box stream has been built in the workspace
     float* cb0_stats;   // optional (max_rows, 2) fp32: entropy and top probability of each cb0 draw
     TcMaps* tc;         // NULL until the weights are bound and the maps could be encoded
+    struct HostFrame* host_frames;   // captured frames with host-side staging (vuib_frame_host_capture), a short list
     char err[256];
 };
+
+// One captured frame that starts and ends in pinned host memory: [staging -> codes_io] -> the frame's kernels ->
+// [codes_io -> staging, eos_prob -> staging], as ONE graph launch.
+struct HostFrame {
+    int B;
+    bool with_h2d;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    int64_t* stage_in;     // pinned (B, Q)
+    int64_t* stage_out;    // pinned (B, Q)
+    float* stage_eos;      // pinned (B)
+    HostFrame* next;
+};
+
+static void free_host_frame(HostFrame* f) {
+    if (f->exec) cudaGraphExecDestroy(f->exec);
+    if (f->graph) cudaGraphDestroy(f->graph);
+    if (f->stage_in) cudaFreeHost(f->stage_in);
+    if (f->stage_out) cudaFreeHost(f->stage_out);
+    if (f->stage_eos) cudaFreeHost(f->stage_eos);
+    delete f;
+}
+
+static void free_host_frames(VuibEngine* e) {
+    for (HostFrame* f = e->host_frames; f;) {
+        HostFrame* n = f->next;
+        free_host_frame(f);
+        f = n;
+    }
+    e->host_frames = nullptr;
+}
 
 static int32_t fail(VuibEngine* e, int32_t code, const char* fmt, ...) {
     if (e) {
@@ -271,7 +303,10 @@ extern "C" int32_t vuib_create(const VuibConfig* cfg, VuibEngine** out) {
 }
 
 extern "C" int32_t vuib_destroy(VuibEngine* e) {
-    if (e) delete e->tc;
+    if (e) {
+        free_host_frames(e);
+        delete e->tc;
+    }
     delete e;
     return VUIB_OK;
 }
@@ -1309,6 +1344,78 @@ extern "C" int32_t vuib_decode_frame(VuibEngine* e, int32_t B, const int32_t* sl
     return run_depth(e, B, slots_dev, static_cast<const bf16*>(hidden_out_dev),
                      static_cast<const bf16*>(cb0_out_dev), static_cast<const bf16*>(eos_out_dev), 0,
                      codes_io_dev, eos_prob_out_dev, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// A frame from and to host memory: what a serving loop does per codec frame, as one graph launch.
+// ---------------------------------------------------------------------------
+extern "C" int32_t vuib_frame_host_capture(VuibEngine* e, int32_t B, int32_t with_h2d, const int32_t* slots_dev,
+                                           const int32_t* seq_inc_dev, int64_t* codes_io_dev, void* hidden_out_dev,
+                                           void* cb0_out_dev, void* eos_out_dev, float* eos_prob_out_dev,
+                                           void* stream) {
+    int32_t rc = ready(e);
+    if (rc) return rc;
+    if (!slots_dev || !codes_io_dev || !hidden_out_dev || !cb0_out_dev || !eos_out_dev || !eos_prob_out_dev)
+        return VUIB_ERR_NULL;
+    if (B < 1 || B > e->cfg.max_rows) return fail(e, VUIB_ERR_RANGE, "B %d outside [1, %d]", B, e->cfg.max_rows);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!s) return fail(e, VUIB_ERR_RANGE, "capture needs a stream of its own, not the default stream");
+    // a frame captured earlier for the same (B, with_h2d) is replaced
+    for (HostFrame** pf = &e->host_frames; *pf; pf = &(*pf)->next)
+        if ((*pf)->B == B && (*pf)->with_h2d == (with_h2d != 0)) {
+            HostFrame* old = *pf;
+            *pf = old->next;
+            free_host_frame(old);
+            break;
+        }
+    HostFrame* f = new (std::nothrow) HostFrame();
+    if (!f) return fail(e, VUIB_ERR_CUDA, "out of host memory");
+    memset(f, 0, sizeof(*f));
+    f->B = B;
+    f->with_h2d = with_h2d != 0;
+    f->next = e->host_frames;
+    e->host_frames = f;   // owned from here on: freed with the engine whatever happens below
+    const size_t code_bytes = (size_t)B * e->cfg.n_quantizers * sizeof(int64_t);
+    CK(cudaHostAlloc(reinterpret_cast<void**>(&f->stage_in), code_bytes, cudaHostAllocDefault));
+    CK(cudaHostAlloc(reinterpret_cast<void**>(&f->stage_out), code_bytes, cudaHostAllocDefault));
+    CK(cudaHostAlloc(reinterpret_cast<void**>(&f->stage_eos), (size_t)B * sizeof(float), cudaHostAllocDefault));
+    memset(f->stage_in, 0, code_bytes);
+    CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    cudaError_t ce = cudaSuccess;
+    if (f->with_h2d) ce = cudaMemcpyAsync(codes_io_dev, f->stage_in, code_bytes, cudaMemcpyHostToDevice, s);
+    rc = ce == cudaSuccess ? vuib_decode_frame(e, B, slots_dev, seq_inc_dev, codes_io_dev, hidden_out_dev, cb0_out_dev,
+                                               eos_out_dev, eos_prob_out_dev, stream)
+                           : VUIB_ERR_CUDA;
+    if (rc == VUIB_OK) {
+        ce = cudaMemcpyAsync(f->stage_out, codes_io_dev, code_bytes, cudaMemcpyDeviceToHost, s);
+        if (ce == cudaSuccess)
+            ce = cudaMemcpyAsync(f->stage_eos, eos_prob_out_dev, (size_t)B * sizeof(float), cudaMemcpyDeviceToHost, s);
+    }
+    cudaGraph_t g = nullptr;
+    const cudaError_t end = cudaStreamEndCapture(s, &g);   // always ends the capture, also after a failure above
+    f->graph = g;
+    if (rc != VUIB_OK) return rc;
+    if (ce != cudaSuccess) return fail(e, VUIB_ERR_CUDA, "capture: %s", cudaGetErrorString(ce));
+    if (end != cudaSuccess || !g) return fail(e, VUIB_ERR_CUDA, "capture: %s", cudaGetErrorString(end));
+    CK(cudaGraphInstantiate(&f->exec, f->graph, 0));
+    return VUIB_OK;
+}
+
+extern "C" int32_t vuib_frame_host(VuibEngine* e, int32_t B, int32_t with_h2d, const int64_t* codes_in_host,
+                                   int64_t* codes_out_host, float* eos_prob_out_host, void* stream) {
+    if (!e || !codes_out_host) return VUIB_ERR_NULL;
+    HostFrame* f = e->host_frames;
+    while (f && !(f->B == B && f->with_h2d == (with_h2d != 0) && f->exec)) f = f->next;
+    if (!f) return fail(e, VUIB_ERR_UNBOUND, "no captured frame for B = %d: call vuib_frame_host_capture first", B);
+    if (f->with_h2d && !codes_in_host) return VUIB_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t code_bytes = (size_t)B * e->cfg.n_quantizers * sizeof(int64_t);
+    if (f->with_h2d) memcpy(f->stage_in, codes_in_host, code_bytes);
+    CK(cudaGraphLaunch(f->exec, s));
+    CK(cudaStreamSynchronize(s));
+    memcpy(codes_out_host, f->stage_out, code_bytes);
+    if (eos_prob_out_host) memcpy(eos_prob_out_host, f->stage_eos, (size_t)B * sizeof(float));
+    return VUIB_OK;
 }
 
 extern "C" int32_t vuib_attention(VuibEngine* e, int32_t layer, int32_t n_rows, const void* q_dev,

@@ -216,6 +216,8 @@ class Engine:
         self._lib = _lib.load()
         self._handle = C.c_void_p()
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._host_frames: set[tuple[int, bool]] = set()   # (rows, with input copy) captured inside the library
+        self._capture_stream = None
         self._sampling_key = None
         self._setup_native()
         self._free: set[int] = set(range(max_rows))
@@ -296,6 +298,7 @@ class Engine:
         # pinned landing zone for the one read-back per frame
         self._h_codes = torch.zeros(N, self.Q, dtype=torch.long).pin_memory()
         self._h_eos = torch.zeros(N, dtype=torch.float32).pin_memory()
+        self._h_codes_in = torch.zeros(N, self.Q, dtype=torch.long).pin_memory()
         self._done = torch.cuda.Event()
         self._set_sampling(1.0, 1, 1, 1.0, 0, 0)
 
@@ -332,6 +335,7 @@ class Engine:
         self._sampling_key = key
         if old_ncb is not None and old_ncb != key[5]:
             self._graphs = {}  # the codebook count is baked into captured graphs
+            self._host_frames = set()
 
     def _apply_cfg(self, cfg: GenConfig | None, temperature: float | None = None, greedy: bool = False) -> None:
         cfg = cfg or GenConfig()
@@ -410,6 +414,39 @@ class Engine:
             self._g_slot_idx[B_active:B].fill_(self._pad_slot)
             self._g_seq_inc[B_active:B].zero_()
         g.replay()
+
+    def _frame_host(self, B_active: int, h_codes_in: Tensor | None = None):
+        """One whole frame through host memory in ONE library call (vuib_frame_host): optional host -> device
+        copy of the previous frame's codes, the frame's kernels, device -> host copy of the new codes and EOS
+        probabilities, all one CUDA-graph launch.  Returns views of the engine's pinned result buffers.
+        The per-frame body of `_stream_row` (engine.py:1450-1546)."""
+        B = _get_bucket(B_active, self._buckets)
+        with_in = h_codes_in is not None
+        if (B, with_in) not in self._host_frames:
+            self._frame_graph(B)  # runs the frame once outside any capture (kernel loading) and restores the state
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream(self.device)
+            torch.cuda.synchronize(self.device)
+            P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+            self._ck(self._lib.vuib_frame_host_capture(
+                self._handle, B, int(with_in), P(self._g_slot_idx), P(self._g_seq_inc), P(self._g_codes_in),
+                P(self._g_hidden_out), P(self._g_cb0_out), P(self._g_eos_out), P(self._g_eos_prob),
+                C.c_void_p(self._capture_stream.cuda_stream)))
+            self._host_frames.add((B, with_in))
+        if B_active < B:
+            self._g_slot_idx[B_active:B].fill_(self._pad_slot)
+            self._g_seq_inc[B_active:B].zero_()
+        src = None
+        if with_in:
+            if h_codes_in.dtype != torch.long or not h_codes_in.is_contiguous() or h_codes_in.is_cuda:
+                raise ValueError("h_codes_in must be a contiguous int64 host tensor")
+            if h_codes_in.shape[0] < B:  # the library reads B rows: pad rows come from the engine's own buffer
+                self._h_codes_in[: h_codes_in.shape[0]].copy_(h_codes_in)
+                h_codes_in = self._h_codes_in
+            src = C.c_void_p(h_codes_in.data_ptr())
+        self._ck(self._lib.vuib_frame_host(self._handle, B, int(with_in), src, C.c_void_p(self._h_codes.data_ptr()),
+                                           C.c_void_p(self._h_eos.data_ptr()), self._stream))
+        return self._h_codes[:B_active], self._h_eos[:B_active]
 
     def _read_frame(self, B: int):
         """The frame's one device->host read: codes (B, Q) and EOS probabilities."""
@@ -578,6 +615,7 @@ class Engine:
     # ------------------------------------------------- test / debug helpers
     def _set_taps(self, layer_hidden: Tensor | None, rq_logits: Tensor | None) -> None:
         self._graphs = {}
+        self._host_frames = set()
         self._tap_refs = (layer_hidden, rq_logits)
         P = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
         self._ck(self._lib.vuib_set_taps(self._handle, P(layer_hidden), P(rq_logits)))
@@ -1022,9 +1060,8 @@ class Engine:
                                 total += 1
                         self._apply_cfg(cfg)
                         return
-                    self._frame_step(1)
+                    h_codes, h_eos = self._frame_host(1)
                     offset += 1
-                    h_codes, h_eos = self._read_frame(1)
                     gathering = use_gate and len(held) < cfg.gate_frames
                     if gathering:
                         entropies.append(float(self._g_cb0_stats[0, 0]))
