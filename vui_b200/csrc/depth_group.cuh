@@ -37,7 +37,7 @@ namespace vuib {
 
 constexpr int DG_CL = 8;
 constexpr int DG_CONSUMERS = 256;
-constexpr int DG_THREADS = DG_CONSUMERS + 32;
+constexpr int DG_THREADS = DG_CONSUMERS + 128;   // two consumer warpgroups + one whose first warp is the producer
 constexpr int DG_RING = 16;          // boxes in the ring
 constexpr int DG_STAGE = 4;          // boxes per stage: one full / empty mbarrier pair, one producer wake-up
 constexpr int DG_STAGES = DG_RING / DG_STAGE;
@@ -296,11 +296,11 @@ __device__ __forceinline__ void dg_rowgroup(DepthGroupSmem<R>& sm, DgState& st, 
         if (first < nbox) fetch(first, f0);
 #pragma unroll
         for (int j = first; j < nbox; j += 2 * step) {
+            if (j + step < nbox) fetch(j + step, f1);      // requested before the MMAs of box j are issued
             consume(j, f0);
             if (j + step < nbox) {
-                fetch(j + step, f1);
-                consume(j + step, f1);
                 if (j + 2 * step < nbox) fetch(j + 2 * step, f0);
+                consume(j + step, f1);
             }
         }
     }
@@ -446,8 +446,17 @@ k_depth_group(const DepthGroupStream strm, DepthGroupArgs a) {
     const int n_pos = a.Qn;  // depth positions 0 .. Qn-1; position p >= 1 yields codebook p
     const int n_ub = (a.upc + 63) / 64;
 
-    // ------------------------------------------------------------------ producer warp
-    if (warp == DG_CONSUMERS / 32) {
+    // Registers: a CTA of 384 threads starts with 168 per thread.  The producer's warpgroup gives most of its
+    // share back and the two consumer warpgroups take it (setmaxnreg is a warpgroup-wide instruction: all four
+    // warps of each group execute it), so the consumers can hold a second set of fragments in flight.
+    // (The two paths never meet again: the compiler allocates registers for each under its own limit.)
+    // ------------------------------------------------------------------ producer warpgroup
+    if (warp >= DG_CONSUMERS / 32) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+        if (warp > DG_CONSUMERS / 32) {   // the producer's three idle companions
+            cluster_wait();
+            return;
+        }
         if (lane == 0) {
             int i = 0;   // stages issued so far (a stage = DG_STAGE consecutive boxes = one contiguous 32 KB copy)
             bool dead = false;
@@ -499,6 +508,7 @@ k_depth_group(const DepthGroupStream strm, DepthGroupArgs a) {
     }
 
     // ------------------------------------------------------------------ consumers (256 threads)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
     pdl_wait();
     cluster_wait();
     const int set = warp >> 2, mt = warp & 3;   // warp set (even / odd boxes of a row group), 16-row tile of the box
