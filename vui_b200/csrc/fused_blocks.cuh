@@ -847,19 +847,15 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
     pdl_wait();
     fb_stamp(a.dbg, 1);
 
+    // the next layer's K/V rows are asked into L2 further down, by threads with nothing else to do: here the
+    // dependent load of the position and the address arithmetic sat on the chain to the norm (0.6 us per layer)
+    int pf_slot = 0, pf_pos = 0;
+    if (a.next_k) {
+        pf_slot = __ldcg(a.row_slot);
+        pf_pos = __ldcg(a.row_pos);
+    }
     float x[EPT];
     load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
-    if (a.next_k) {  // one 128-byte line per thread and step, the grid shares the rows
-        const int slot = __ldcg(a.row_slot), pos = __ldcg(a.row_pos);
-        const size_t row_bytes = (size_t)a.kvcols * sizeof(bf16);
-        const size_t lines = (size_t)pos * row_bytes / 128;
-        const char* kbase = reinterpret_cast<const char*>(a.next_k) + (size_t)slot * a.max_seq * row_bytes;
-        const char* vbase = reinterpret_cast<const char*>(a.next_v) + (size_t)slot * a.max_seq * row_bytes;
-        for (size_t i = (size_t)blockIdx.x * TH + tid; i < 2 * lines; i += (size_t)gridDim.x * TH) {
-            const char* p = i < lines ? kbase + i * 128 : vbase + (i - lines) * 128;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-        }
-    }
     if (blockIdx.x == 0) store_bf16<EPT>(a.x_out + k0, x);
     norm_to_smem<K, EPT, NWARP>(x, nw, a.eps, sm.xs, k0, sm.red);
     __syncthreads();
@@ -879,6 +875,21 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         const float a3 = rbf(mma_row_total<2 * U, NWARP>(sm.dots, U + u));
         const float sl = rbf(a1 / (1.0f + expf(-a1)));
         push_f32(peer_addr(sm.g + rank * U + u, tid & 7), peer_addr(&sm.bar_g, tid & 7), rbf(sl * a3));
+    }
+    if (a.next_k) {  // one 128-byte line per thread and step, the grid shares the rows
+        constexpr int IDLE = TH - U * FB_CL;   // threads without a hidden unit to finish (all of them if none are idle)
+        constexpr int PF = IDLE > 0 ? IDLE : TH;
+        const int pt = IDLE > 0 ? tid - U * FB_CL : tid;
+        if (pt >= 0) {
+            const size_t row_bytes = (size_t)a.kvcols * sizeof(bf16);
+            const size_t lines = (size_t)pf_pos * row_bytes / 128;
+            const char* kbase = reinterpret_cast<const char*>(a.next_k) + (size_t)pf_slot * a.max_seq * row_bytes;
+            const char* vbase = reinterpret_cast<const char*>(a.next_v) + (size_t)pf_slot * a.max_seq * row_bytes;
+            for (size_t i = (size_t)blockIdx.x * PF + pt; i < 2 * lines; i += (size_t)gridDim.x * PF) {
+                const char* p = i < lines ? kbase + i * 128 : vbase + (i - lines) * 128;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+            }
+        }
     }
     fb_stamp(a.dbg, 9);
     if (!wait_pushed(&sm.bar_g, a.spin_limit) && tid == 0) atomicOr(a.flag, FLAG_COPY_TIMEOUT);
