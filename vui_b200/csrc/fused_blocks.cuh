@@ -778,7 +778,7 @@ struct MlpBlockArgs {
     const bf16* next_v;
     const int32_t* row_slot;
     const int32_t* row_pos;
-    int max_seq, kvcols;
+    int max_seq, kvcols, n_slots;
     int32_t* flag;
     unsigned spin_limit;
     PrefetchList next;
@@ -844,16 +844,27 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
 #pragma unroll
         for (int j = 0; j < EPT; ++j) nw[j] = bf2f(t[j]);
     }
+    if (a.next_k) {
+        // The next layer's K/V rows are asked into L2 BEFORE the dependency wait (after it, the dependent load of the
+        // position and the address arithmetic sat on the chain to the norm: 0.6 us per layer).  The rows before the
+        // stream's position do not change during a frame.  The position itself may still be last frame's here (the
+        // kernel that writes it need not have finished): then one row is not asked for, nothing more - these are
+        // hints, and slot and position are clamped so that every address lies inside the cache.
+        int slot = __ldcg(a.row_slot), pos = __ldcg(a.row_pos);
+        slot = slot < 0 ? 0 : (slot >= a.n_slots ? a.n_slots - 1 : slot);
+        pos = pos < 0 ? 0 : (pos > a.max_seq ? a.max_seq : pos);
+        const size_t row_bytes = (size_t)a.kvcols * sizeof(bf16);
+        const size_t lines = (size_t)pos * row_bytes / 128;
+        const char* kbase = reinterpret_cast<const char*>(a.next_k) + (size_t)slot * a.max_seq * row_bytes;
+        const char* vbase = reinterpret_cast<const char*>(a.next_v) + (size_t)slot * a.max_seq * row_bytes;
+        for (size_t i = (size_t)blockIdx.x * TH + tid; i < 2 * lines; i += (size_t)gridDim.x * TH) {
+            const char* p = i < lines ? kbase + i * 128 : vbase + (i - lines) * 128;   // one 128-byte line each
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+    }
     pdl_wait();
     fb_stamp(a.dbg, 1);
 
-    // the next layer's K/V rows are asked into L2 further down, by threads with nothing else to do: here the
-    // dependent load of the position and the address arithmetic sat on the chain to the norm (0.6 us per layer)
-    int pf_slot = 0, pf_pos = 0;
-    if (a.next_k) {
-        pf_slot = __ldcg(a.row_slot);
-        pf_pos = __ldcg(a.row_pos);
-    }
     float x[EPT];
     load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
     if (blockIdx.x == 0) store_bf16<EPT>(a.x_out + k0, x);
@@ -875,21 +886,6 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         const float a3 = rbf(mma_row_total<2 * U, NWARP>(sm.dots, U + u));
         const float sl = rbf(a1 / (1.0f + expf(-a1)));
         push_f32(peer_addr(sm.g + rank * U + u, tid & 7), peer_addr(&sm.bar_g, tid & 7), rbf(sl * a3));
-    }
-    if (a.next_k) {  // one 128-byte line per thread and step, the grid shares the rows
-        constexpr int IDLE = TH - U * FB_CL;   // threads without a hidden unit to finish (all of them if none are idle)
-        constexpr int PF = IDLE > 0 ? IDLE : TH;
-        const int pt = IDLE > 0 ? tid - U * FB_CL : tid;
-        if (pt >= 0) {
-            const size_t row_bytes = (size_t)a.kvcols * sizeof(bf16);
-            const size_t lines = (size_t)pf_pos * row_bytes / 128;
-            const char* kbase = reinterpret_cast<const char*>(a.next_k) + (size_t)pf_slot * a.max_seq * row_bytes;
-            const char* vbase = reinterpret_cast<const char*>(a.next_v) + (size_t)pf_slot * a.max_seq * row_bytes;
-            for (size_t i = (size_t)blockIdx.x * PF + pt; i < 2 * lines; i += (size_t)gridDim.x * PF) {
-                const char* p = i < lines ? kbase + i * 128 : vbase + (i - lines) * 128;
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-            }
-        }
     }
     fb_stamp(a.dbg, 9);
     if (!wait_pushed(&sm.bar_g, a.spin_limit) && tid == 0) atomicOr(a.flag, FLAG_COPY_TIMEOUT);

@@ -872,6 +872,7 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
         ma.row_pos = wsp<int32_t>(e, L.row_pos);
         ma.max_seq = c.max_seq;
         ma.kvcols = kvc;
+        ma.n_slots = c.n_slots;
         ma.flag = wsp<int32_t>(e, L.flag);
         ma.spin_limit = e->spin_limit;
         ma.next = li + 1 < c.n_layers ? prefetch_of(e->w.wqkv[li + 1], qkv_bytes, e->w.out_proj[li + 1], wo_bytes)
