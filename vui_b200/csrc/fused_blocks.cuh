@@ -391,7 +391,7 @@ struct AttnBlockArgs {
     const int32_t* row_slot;  // checked (slot, position) of the row; NULL -> fixed_slot / fixed_pos
     const int32_t* row_pos;
     int fixed_slot, fixed_pos;
-    int max_seq;
+    int max_seq, n_slots;
     const bf16* rope;       // (max_seq, 64, 2) or NULL
     int Hq, Hkv;
     int32_t* flag;
@@ -474,55 +474,76 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
 #pragma unroll
         for (int j = 0; j < EPT; ++j) nw[j] = bf2f(t[j]);
     }
-    pdl_wait();
-    fb_stamp(a.dbg, 1);
-
-    // ---- row position first (the K/V requests depend on it), then the residual stream
-    int slot = a.fixed_slot, pos = a.fixed_pos;
-    if (a.row_slot) {
-        slot = __ldcg(a.row_slot);
-        pos = __ldcg(a.row_pos);
-    }
-    float x[EPT];
-    load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
-
-    // old keys [0, pos) split over the cluster's CTAs; this CTA's first FB_ATT_PRE blocks requested now
-    const int n_old = SHORT ? min(pos, 16) : pos;
-    const int chunk = SHORT ? n_old : (n_old + FB_CL - 1) / FB_CL;
-    const int t_begin = SHORT ? 0 : rank * chunk, t_end = min(n_old, t_begin + chunk);
-    const int s8 = lane & 7, g4 = lane >> 3;
-    const size_t pos_stride = (size_t)kvcols;
-    const bf16* kb = a.k_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
-    const bf16* vb = a.v_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
-    uint4 kr[FB_ATT_PRE], vr[FB_ATT_PRE];
-#pragma unroll
-    for (int it = 0; it < FB_ATT_PRE; ++it) {
-        // SHORT: warp 0 alone takes all (<= 16) keys, four per pass
-        const int t = SHORT ? (warp == 0 ? it * 4 + g4 : t_end) : t_begin + it * 32 + warp * 4 + g4;
-        if (t < t_end) {
-            kr[it] = ldg_stream(kb + (size_t)t * pos_stride);
-            vr[it] = ldg_stream(vb + (size_t)t * pos_stride);
-        } else {
-            kr[it] = make_uint4(0, 0, 0, 0);
-            vr[it] = make_uint4(0, 0, 0, 0);
-        }
-    }
-    // After the tensor-core dot products eight threads finish each interleaved row pair, one per peer CTA.
-    // RoPE factors of the thread's pair:
+    // ---- the row's old keys and its RoPE factors
+    // After the tensor-core dot products eight threads finish each interleaved row pair, one per peer CTA:
     const int my_pair = tid >> 3;
     const bool pair_live = my_pair < NP;
     const int prow = 2 * (pair_live ? my_pair : 0);  // first local row of the pair
     const bool is_q = prow < QR, is_k = !is_q && prow < QR + KR;
     const int sub = is_q ? prow : (is_k ? prow - QR : prow - QR - KR);
+    const int s8 = lane & 7, g4 = lane >> 3;
+    const size_t pos_stride = (size_t)kvcols;
+    int slot = a.fixed_slot, pos = a.fixed_pos;
+    int n_old = 0, chunk = 0, t_begin = 0, t_end = 0;
+    const bf16* kb = nullptr;
+    const bf16* vb = nullptr;
+    uint4 kr[FB_ATT_PRE], vr[FB_ATT_PRE];
     float c0 = 1.f, s0 = 0.f, c1 = 1.f, s1 = 0.f;
-    if (a.rope && (is_q || is_k)) {
-        const int dd = (is_q ? rank * QR + sub : rank * KR + sub) & (HD - 1);
-        const uint2 f = __ldg(reinterpret_cast<const uint2*>(a.rope + ((size_t)pos * HD + dd) * 2));
-        c0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x & 0xffffu)));
-        s0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x >> 16)));
-        c1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y & 0xffffu)));
-        s1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y >> 16)));
+    // old keys [0, pos) split over the cluster's CTAs; this CTA's first FB_ATT_PRE blocks are requested
+    auto request = [&](int sl, int ps) {
+        slot = sl;
+        pos = ps;
+        n_old = SHORT ? min(pos, 16) : pos;
+        chunk = SHORT ? n_old : (n_old + FB_CL - 1) / FB_CL;
+        t_begin = SHORT ? 0 : rank * chunk;
+        t_end = min(n_old, t_begin + chunk);
+        kb = a.k_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
+        vb = a.v_cache + (size_t)slot * a.max_seq * pos_stride + kvh * HD + s8 * 8;
+#pragma unroll
+        for (int it = 0; it < FB_ATT_PRE; ++it) {
+            // SHORT: warp 0 alone takes all (<= 16) keys, four per pass
+            const int t = SHORT ? (warp == 0 ? it * 4 + g4 : t_end) : t_begin + it * 32 + warp * 4 + g4;
+            if (t < t_end) {
+                kr[it] = ldg_stream(kb + (size_t)t * pos_stride);
+                vr[it] = ldg_stream(vb + (size_t)t * pos_stride);
+            } else {
+                kr[it] = make_uint4(0, 0, 0, 0);
+                vr[it] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (a.rope && (is_q || is_k)) {
+            const int dd = (is_q ? rank * QR + sub : rank * KR + sub) & (HD - 1);
+            const uint2 f = __ldg(reinterpret_cast<const uint2*>(a.rope + ((size_t)pos * HD + dd) * 2));
+            c0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x & 0xffffu)));
+            s0 = bf2f(__ushort_as_bfloat16((unsigned short)(f.x >> 16)));
+            c1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y & 0xffffu)));
+            s1 = bf2f(__ushort_as_bfloat16((unsigned short)(f.y >> 16)));
+        }
+    };
+    // A stream's rows before its position were written by earlier frames, so for the backbone they can be requested
+    // BEFORE the dependency wait, with the position as it stands in memory now.  It is read again after the wait: if
+    // the kernel that sets it had not finished (first layer of a frame), the requests are simply made again.
+    bool early = false;
+    if constexpr (!SHORT) {
+        if (a.row_slot) {
+            int sg = __ldcg(a.row_slot), pg = __ldcg(a.row_pos);
+            sg = sg < 0 ? 0 : (sg >= a.n_slots ? a.n_slots - 1 : sg);
+            pg = pg < 0 ? 0 : (pg >= a.max_seq ? a.max_seq - 1 : pg);
+            request(sg, pg);
+            early = true;
+        }
     }
+    pdl_wait();
+    fb_stamp(a.dbg, 1);
+
+    int sl = a.fixed_slot, ps = a.fixed_pos;
+    if (a.row_slot) {
+        sl = __ldcg(a.row_slot);
+        ps = __ldcg(a.row_pos);
+    }
+    float x[EPT];
+    load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
+    if (!early || sl != slot || ps != pos) request(sl, ps);
     fb_stamp(a.dbg, 8);
     if (blockIdx.x == 0) {
         store_bf16<EPT>(a.x_out + k0, x);

@@ -842,6 +842,7 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
         aa.row_slot = wsp<int32_t>(e, L.row_slot);
         aa.row_pos = wsp<int32_t>(e, L.row_pos);
         aa.max_seq = c.max_seq;
+        aa.n_slots = c.n_slots;
         aa.rope = e->rope;
         aa.Hq = c.n_heads;
         aa.Hkv = c.n_kv_heads;
@@ -918,6 +919,7 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
         aa.fixed_slot = 0;
         aa.fixed_pos = pos;
         aa.max_seq = Q;
+        aa.n_slots = c.max_rows;
         aa.Hq = c.rq_n_heads;
         aa.Hkv = c.rq_n_heads;
         aa.flag = wsp<int32_t>(e, L.flag);
