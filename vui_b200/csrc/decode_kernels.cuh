@@ -1142,6 +1142,8 @@ struct SampleSmem {
 __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, SampleSmem& S_, int bar_id) {
     constexpr int CS = SAMPLE_THREADS * SAMPLE_EL;
     const int warp = tid >> 5, lane = tid & 31;
+    // the row's logits are requested before anything waits for the slot (one dependent round trip less)
+    const uint4 raw_logits = __ldcg(reinterpret_cast<const uint4*>(a.logits + (size_t)r * a.stride + tid * SAMPLE_EL));
     int slot = __ldcg(a.slots + r);
     if (slot < 0 || slot >= a.n_slots) {
         if (a.flag && tid == 0) atomicOr(a.flag, FLAG_BAD_SLOT);
@@ -1157,8 +1159,9 @@ __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, S
     int& s_pick = S_.s_pick;
     int& s_lastkept = S_.s_lastkept;
 
+    const uint32_t frame_no = (uint32_t)a.frame_ctr[slot];   // for the draw's Philox key, asked for early
     float v[SAMPLE_EL];
-    unpack8(__ldcg(reinterpret_cast<const uint4*>(a.logits + (size_t)r * a.stride + tid * SAMPLE_EL)), v);
+    unpack8(raw_logits, v);
     if (is_cb0 && ctl.rep_penalty > 1.0f) {
         const float* cnt = a.rep_counts + (size_t)slot * CS + tid * SAMPLE_EL;
 #pragma unroll
@@ -1296,7 +1299,7 @@ __device__ __forceinline__ int sample_row(const SampleArgs& a, int r, int tid, S
             if (w < warp) wbase += s_f[w];
             total += s_f[w];
         }
-        uint32_t c[4] = {(uint32_t)slot, (uint32_t)a.frame_ctr[slot], (uint32_t)a.codebook, 0u};
+        uint32_t c[4] = {(uint32_t)slot, frame_no, (uint32_t)a.codebook, 0u};
         philox4x32_10(c, ctl.seed_lo, ctl.seed_hi);
         const float u = (float)(c[0] >> 8) * (1.0f / 16777216.0f);
         const float target = u * total;
