@@ -818,7 +818,7 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
     const int d = c.d_model, qc = c.n_heads * HD, kvc = c.n_kv_heads * HD;
-    const size_t qkv_bytes = (size_t)(qc + 2 * kvc) * d * 2, wo_bytes = (size_t)d * qc * 2, ffn_bytes = (size_t)c.ffn * d * 2;
+    const size_t qkv_bytes = (size_t)(qc + 2 * kvc) * d * 2, wo_bytes = (size_t)d * qc * 2;
     constexpr int NCL = 3072 / (FB_MLP_U_BACKBONE * FB_CL);
     bf16* xa = wsp<bf16>(e, L.fx_a);
     bf16* xb = wsp<bf16>(e, L.fx_b);
@@ -848,7 +848,9 @@ static int32_t run_layers_fused(VuibEngine* e, cudaStream_t s, Residual* out, co
         aa.Hkv = c.n_kv_heads;
         aa.flag = wsp<int32_t>(e, L.flag);
         aa.spin_limit = e->spin_limit;
-        aa.next = prefetch_of(e->w.w1[li], ffn_bytes, e->w.w3[li], ffn_bytes, e->w.w2[li], ffn_bytes);
+        // no L2 hint for the MLP block's matrices: that kernel is resident two launches ahead and copies them itself,
+        // and 19 MB of hints during this block delayed its own loads (0.799 -> 0.788 ms per frame without them)
+        aa.next = prefetch_of(nullptr, 0);
         if (env_off("VUIB_TRACE") && (li == 5 || li == 6)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 5) * 32;
         CK(launch_cluster(k_attn_block<1024, 2, false>, c.n_kv_heads, FB_THREADS, sizeof(AttnBlockSmem<1024, 2>), s, e->tc->f_out[li], aa));
         e->launches++;
@@ -895,7 +897,7 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
     const VuibConfig& c = e->cfg;
     const WsLayout& L = e->lay;
     const int rd = c.rq_d_model, Q = c.n_quantizers;
-    const size_t qkv_bytes = (size_t)3 * rd * rd * 2, wo_bytes = (size_t)rd * rd * 2, ffn_bytes = (size_t)c.rq_ffn * rd * 2;
+    const size_t qkv_bytes = (size_t)3 * rd * rd * 2, wo_bytes = (size_t)rd * rd * 2;
     const int ncl = c.rq_ffn / (FB_MLP_U_DEPTH * FB_CL);
     bf16* xa = wsp<bf16>(e, L.rq_fx_a);
     bf16* xb = wsp<bf16>(e, L.rq_fx_b);
@@ -924,7 +926,7 @@ static int32_t rq_layers_fused(VuibEngine* e, const bf16* x, int pos, cudaStream
         aa.Hkv = c.rq_n_heads;
         aa.flag = wsp<int32_t>(e, L.flag);
         aa.spin_limit = e->spin_limit;
-        aa.next = prefetch_of(e->w.rq_w1[li], ffn_bytes, e->w.rq_w3[li], ffn_bytes, e->w.rq_w2[li], ffn_bytes);
+        aa.next = prefetch_of(nullptr, 0);   // as in the backbone: the MLP block copies its own matrices early enough
         if (env_off("VUIB_TRACE_DEPTH") && pos == 8 && (li == 1 || li == 2)) aa.dbg = wsp<unsigned long long>(e, L.trace) + (li - 1) * 32;
         CK(launch_cluster(k_attn_block<512, 1, true>, c.rq_n_heads, FB_THREADS, sizeof(AttnBlockSmem<512, 1>), s, e->tc->f_rq_out[li], aa));
         e->launches++;
