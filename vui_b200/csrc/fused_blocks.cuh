@@ -825,6 +825,7 @@ struct MlpBlockSmem {
     float dots[(TH / 32) * ((2 * U + 15) / 16) * 16];  // per-warp partial sums of the w1 / w3 rows
     alignas(8) uint64_t bar;     // weight copies
     alignas(8) uint64_t bar_g;   // the cluster's activations complete (all peers' units)
+    alignas(8) uint64_t bar_w2;  // the w2 slice, when it is copied after the dependency wait
 };
 
 template <int K, int F, int U, int TH>
@@ -833,6 +834,10 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
     constexpr int EPT = K / TH;
     constexpr int NWARP = TH / 32;
     constexpr int CU = S::CU, OR = S::OR;
+    // The backbone's w2 slice (6 MB over the grid, needed last) is copied only once this kernel's residual is in: before
+    // that it would travel together with the attention block's own loads, which are on the chain (0.794 -> 0.786 ms).
+    // The depth block's slice is small and its chain tighter: there the late copy cost 0.005 ms.
+    constexpr bool LATE_W2 = K >= 1024;
     extern __shared__ __align__(128) unsigned char fb_smem[];
     S& sm = *reinterpret_cast<S*>(fb_smem);
     cg::cluster_group cluster = cg::this_cluster();
@@ -846,15 +851,16 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         if (lane == 0) {
             mbar_init(&sm.bar, 1);
             mbar_init(&sm.bar_g, 1);
+            mbar_init(&sm.bar_w2, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(&sm.bar_g, (uint32_t)(CU * 4));
-            mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + OR * CU * 2));
+            mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + (LATE_W2 ? 0 : OR * CU * 2)));
             const size_t u0 = (size_t)cid * CU + rank * U;
             bulk_g2s(sm.w13, a.w1 + u0 * K, U * K * 2, &sm.bar);
             bulk_g2s(sm.w13 + U * K, a.w3 + u0 * K, U * K * 2, &sm.bar);
             // the w2 slice (OR rows x CU columns) as ONE tiled copy
-            tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
+            if constexpr (!LATE_W2) tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
         }
     }
     __syncthreads();
@@ -896,6 +902,10 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
     norm_to_smem<K, EPT, NWARP>(x, nw, a.eps, sm.xs, k0, sm.red);
     __syncthreads();
     fb_stamp(a.dbg, 2);
+    if (LATE_W2 && tid == 0) {   // needed last: requested once the residual is in
+        mbar_expect_tx(&sm.bar_w2, (uint32_t)(OR * CU * 2));
+        tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar_w2);
+    }
     wait_weights(&sm.bar, a.spin_limit, a.flag);
     cluster_wait();
     fb_stamp(a.dbg, 3);
@@ -918,6 +928,7 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
 
     // ---- the cluster's K-slice of w2 for this CTA's rows
     static_assert(OR % NWARP == 0, "rows split evenly over the warps");
+    if constexpr (LATE_W2) wait_weights(&sm.bar_w2, a.spin_limit, a.flag);
     small_matvec<CU, OR / NWARP>(sm.w2, sm.g, warp * (OR / NWARP), a.parts_out + (size_t)cid * K + rank * OR, lane);
     fb_stamp(a.dbg, 6);
 }
