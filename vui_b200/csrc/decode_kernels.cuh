@@ -121,21 +121,36 @@ static __global__ void __launch_bounds__(128) k_embed_codes(
             row_pos[r] = pos;
         }
     }
+    // All codes are requested at once, then all table rows, then the rows are added in codebook order (the order the
+    // sum is defined in): one dependent round trip instead of one per codebook.
+    constexpr int QB = 16;
     for (int k = threadIdx.x * 8; k < d; k += blockDim.x * 8) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int q = 0; q < Q; ++q) {
-            long long c = codes[(size_t)r * Q + q];
-            if (c < 0 || c >= CS) {
-                atomicOr(flag, FLAG_BAD_CODE);
-                c = 0;
-            }
-            uint4 u = __ldg(reinterpret_cast<const uint4*>(table + ((size_t)q * CS + c) * d + k));
-            float f[8];
-            unpack8(u, f);
+        for (int q0 = 0; q0 < Q; q0 += QB) {
+            long long c[QB];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            for (int u = 0; u < QB; ++u) c[u] = q0 + u < Q ? codes[(size_t)r * Q + q0 + u] : 0;
+            uint4 row[QB];
+#pragma unroll
+            for (int u = 0; u < QB; ++u) {
+                if (c[u] < 0 || c[u] >= CS) {
+                    atomicOr(flag, FLAG_BAD_CODE);
+                    c[u] = 0;
+                }
+                row[u] = q0 + u < Q ? __ldg(reinterpret_cast<const uint4*>(table + ((size_t)(q0 + u) * CS + c[u]) * d + k))
+                                    : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < QB; ++u) {
+                if (q0 + u < Q) {
+                    float f[8];
+                    unpack8(row[u], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += f[j];
+                }
+            }
         }
         *reinterpret_cast<uint4*>(x + (size_t)r * d + k) = pack8(acc);
     }
@@ -1010,6 +1025,12 @@ static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restric
                                                     const float* __restrict__ parts, int n_parts,
                                                     bf16* __restrict__ xsum_out) {
     pdl_trigger();
+    // the norm weights do not depend on the previous kernel (single pass over d <= 1024: one piece per thread)
+    float wf0[8];
+    {
+        const int k = threadIdx.x * 8;
+        unpack8(k < d ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0, 0, 0, 0), wf0);
+    }
     pdl_wait();
     const int r = blockIdx.x;
     __shared__ float red[4];
@@ -1020,17 +1041,17 @@ static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restric
         for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
             float f[8], sp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             unpack8(__ldcg(reinterpret_cast<const uint4*>(xr + k)), f);
-            for (int p0 = 0; p0 < n_parts; p0 += 8) {  // eight rows in flight at a time, added in row order
-                float4 pa[8], pb[8];
+            for (int p0 = 0; p0 < n_parts; p0 += 16) {  // sixteen rows in flight at a time, added in row order
+                float4 pa[16], pb[16];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 16; ++u) {
                     const bool ok = p0 + u < n_parts;
                     const float* q = parts + (size_t)(ok ? p0 + u : p0) * d + k;
                     pa[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0.f, 0.f, 0.f, 0.f);
                     pb[u] = ok ? __ldcg(reinterpret_cast<const float4*>(q + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 16; ++u) {
                     sp[0] += pa[u].x; sp[1] += pa[u].y; sp[2] += pa[u].z; sp[3] += pa[u].w;
                     sp[4] += pb[u].x; sp[5] += pb[u].y; sp[6] += pb[u].z; sp[7] += pb[u].w;
                 }
@@ -1059,7 +1080,12 @@ static __global__ void __launch_bounds__(128) k_final_norm(const bf16* __restric
     for (int k = threadIdx.x * 8; k < d; k += 128 * 8) {
         float f[8], wf[8], o[8];
         unpack8(*reinterpret_cast<const uint4*>(xr + k), f);
-        unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+        if (k == (int)threadIdx.x * 8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wf[j] = wf0[j];
+        } else {
+            unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rbf(f[j] * rinv) * wf[j];
         *reinterpret_cast<uint4*>(out + (size_t)r * d + k) = pack8(o);
