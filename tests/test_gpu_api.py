@@ -224,3 +224,48 @@ def test_frame_through_host_memory_equals_replay_and_read(model_tok):
             h_in.copy_(hc)
         b.check_device()
         assert torch.equal(a.seq_lens, ref.seq_lens) and torch.equal(b.seq_lens, ref.seq_lens)
+
+
+def test_single_row_frames_alternating_between_two_rows(model_tok):
+    """The one-stream attention block asks for a row's old keys before it has waited for its predecessor, with the
+    (slot, position) it finds in memory, and asks again if they turn out to be another row's.  Two rows of different
+    lengths decoded in turn, one frame each, must give exactly the frames each of them gives when decoded alone."""
+    from vui_b200 import Engine
+
+    gen = torch.Generator().manual_seed(5)
+    ids = [torch.randint(0, 1000, (n,), generator=gen) for n in (31, 57)]
+
+    def first(eng, row, tokens):
+        hid = eng.prefill_ids(row, tokens)
+        return eng._first_frames([row], hid[None])[0]
+
+    def step(eng, row, codes_in):
+        eng._g_slot_idx[0] = row.idx
+        eng._g_seq_inc[0] = 1
+        eng._g_codes_in[0] = codes_in
+        eng._frame_step(1)
+        c, _ = eng._read_frame(1)
+        return c[0].clone()
+
+    alone = []
+    for tokens in ids:
+        eng = Engine(model=model_tok, max_rows=2, max_seq=256, seed=3)
+        eng._apply_cfg(None, greedy=True)
+        row = eng.new_row()
+        cur = first(eng, row, tokens)
+        out = []
+        for _ in range(4):
+            cur = step(eng, row, cur.to(eng.device))
+            out.append(cur)
+        eng.check_device()
+        alone.append(out)
+
+    eng = Engine(model=model_tok, max_rows=2, max_seq=256, seed=3)
+    eng._apply_cfg(None, greedy=True)
+    rows = [eng.new_row(), eng.new_row()]
+    cur = [first(eng, rows[i], ids[i]) for i in range(2)]
+    for f in range(4):
+        for i in range(2):
+            cur[i] = step(eng, rows[i], cur[i].to(eng.device))
+            assert torch.equal(cur[i], alone[i][f]), (f, i)
+    eng.check_device()
