@@ -38,6 +38,7 @@ namespace cg = cooperative_groups;
 constexpr int FB_THREADS = 256;  // attention block
 constexpr int FB_WARPS = 8;
 constexpr int FB_CL = 8;         // CTAs per cluster
+constexpr int FB_HINT_CLUSTERS = 6;   // clusters of an MLP block that issue the K/V hints (those resident early)
 constexpr int FB_ATT_PRE = 4;    // key blocks (of 32 per CTA) whose loads are in flight before use
 constexpr int FB_MAX_PF = 3;     // matrices of the successor a kernel asks the L2 for
 
@@ -867,15 +868,13 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
     cluster_arrive();  // after the mbarriers exist: a peer that has passed cluster_wait() may push to them
     prefetch_l2(a.next, TH);
     const int k0 = tid * EPT;
-    float nw[EPT];
-    {
-        bf16 t[EPT];
-        if constexpr (EPT == 4) *reinterpret_cast<uint2*>(t) = __ldg(reinterpret_cast<const uint2*>(a.norm_w + k0));
-        else *reinterpret_cast<unsigned*>(t) = __ldg(reinterpret_cast<const unsigned*>(a.norm_w + k0));
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) nw[j] = bf2f(t[j]);
-    }
-    if (a.next_k) {
+    // Requested here, converted after the wait: the clusters of this kernel that only become resident when the
+    // attention block's CTAs leave (at most 15 clusters of 8 fit the part at once) run this prologue ON the chain,
+    // so nothing in it may wait for a load.
+    alignas(8) bf16 nw_raw[EPT];
+    if constexpr (EPT == 4) *reinterpret_cast<uint2*>(nw_raw) = __ldg(reinterpret_cast<const uint2*>(a.norm_w + k0));
+    else *reinterpret_cast<unsigned*>(nw_raw) = __ldg(reinterpret_cast<const unsigned*>(a.norm_w + k0));
+    if (a.next_k && cid < FB_HINT_CLUSTERS) {   // the hints are the early clusters' job, for the same reason
         // The next layer's K/V rows are asked into L2 BEFORE the dependency wait (after it, the dependent load of the
         // position and the address arithmetic sat on the chain to the norm: 0.6 us per layer).  The rows before the
         // stream's position do not change during a frame.  The position itself may still be last frame's here (the
@@ -888,7 +887,8 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         const size_t lines = (size_t)pos * row_bytes / 128;
         const char* kbase = reinterpret_cast<const char*>(a.next_k) + (size_t)slot * a.max_seq * row_bytes;
         const char* vbase = reinterpret_cast<const char*>(a.next_v) + (size_t)slot * a.max_seq * row_bytes;
-        for (size_t i = (size_t)blockIdx.x * TH + tid; i < 2 * lines; i += (size_t)gridDim.x * TH) {
+        const size_t n_hint = (size_t)(gridDim.x < FB_HINT_CLUSTERS * FB_CL ? gridDim.x : FB_HINT_CLUSTERS * FB_CL) * TH;
+        for (size_t i = (size_t)blockIdx.x * TH + tid; i < 2 * lines; i += n_hint) {
             const char* p = i < lines ? kbase + i * 128 : vbase + (i - lines) * 128;   // one 128-byte line each
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
         }
@@ -898,6 +898,9 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
 
     float x[EPT];
     load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
+    float nw[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) nw[j] = bf2f(nw_raw[j]);
     if (blockIdx.x == 0) store_bf16<EPT>(a.x_out + k0, x);
     norm_to_smem<K, EPT, NWARP>(x, nw, a.eps, sm.xs, k0, sm.red);
     __syncthreads();
