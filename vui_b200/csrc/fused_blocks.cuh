@@ -454,17 +454,21 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(&sm.bar_qkv, (uint32_t)((G * HD + 2 * HD) * 4));
             mbar_expect_tx(&sm.bar_part, (uint32_t)(FB_CL * G * (HD + 2) * 4));
-            mbar_expect_tx(&sm.bar, (uint32_t)(S::NR * K * 2 + OR * OC * 2));
-            bulk_g2s(sm.w, a.wqkv + (size_t)(kvh * G * HD + rank * QR) * K, QR * K * 2, &sm.bar);
-            bulk_g2s(sm.w + QR * K, a.wqkv + (size_t)(qcols + kvh * HD + rank * KR) * K, KR * K * 2, &sm.bar);
-            bulk_g2s(sm.w + (QR + KR) * K, a.wqkv + (size_t)(qcols + kvcols + kvh * HD + rank * KR) * K, KR * K * 2,
-                     &sm.bar);
-            // the out_proj slice (OR rows x OC columns of a row-major matrix) as ONE tiled copy
-            tma_load_2d(sm.wo, &map_wo, kvh * OC, rank * OR, &sm.bar);
         }
     }
     __syncthreads();
-    cluster_arrive();  // after the mbarriers exist: a peer that has passed cluster_wait() may push to them
+    // After the mbarriers exist (a peer that has passed cluster_wait() may push to them) and BEFORE the weight copies
+    // are issued: with copies of this thread in flight the releasing arrival took as long as the copies (1.3 us), which
+    // a cluster that only becomes resident when the previous kernel's CTAs leave pays on the chain.
+    cluster_arrive();
+    if (tid == 0) {
+        mbar_expect_tx(&sm.bar, (uint32_t)(S::NR * K * 2 + OR * OC * 2));
+        bulk_g2s(sm.w, a.wqkv + (size_t)(kvh * G * HD + rank * QR) * K, QR * K * 2, &sm.bar);
+        bulk_g2s(sm.w + QR * K, a.wqkv + (size_t)(qcols + kvh * HD + rank * KR) * K, KR * K * 2, &sm.bar);
+        bulk_g2s(sm.w + (QR + KR) * K, a.wqkv + (size_t)(qcols + kvcols + kvh * HD + rank * KR) * K, KR * K * 2, &sm.bar);
+        // the out_proj slice (OR rows x OC columns of a row-major matrix) as ONE tiled copy
+        tma_load_2d(sm.wo, &map_wo, kvh * OC, rank * OR, &sm.bar);
+    }
     prefetch_l2(a.next, FB_THREADS);
     const int k0 = tid * EPT;
     float nw[EPT];
@@ -856,16 +860,18 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(&sm.bar_g, (uint32_t)(CU * 4));
-            mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + (LATE_W2 ? 0 : OR * CU * 2)));
-            const size_t u0 = (size_t)cid * CU + rank * U;
-            bulk_g2s(sm.w13, a.w1 + u0 * K, U * K * 2, &sm.bar);
-            bulk_g2s(sm.w13 + U * K, a.w3 + u0 * K, U * K * 2, &sm.bar);
-            // the w2 slice (OR rows x CU columns) as ONE tiled copy
-            if constexpr (!LATE_W2) tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
         }
     }
     __syncthreads();
-    cluster_arrive();  // after the mbarriers exist: a peer that has passed cluster_wait() may push to them
+    cluster_arrive();  // after the mbarriers exist, before the weight copies are issued (see the attention block)
+    if (tid == 0) {
+        mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + (LATE_W2 ? 0 : OR * CU * 2)));
+        const size_t u0 = (size_t)cid * CU + rank * U;
+        bulk_g2s(sm.w13, a.w1 + u0 * K, U * K * 2, &sm.bar);
+        bulk_g2s(sm.w13 + U * K, a.w3 + u0 * K, U * K * 2, &sm.bar);
+        // the w2 slice (OR rows x CU columns) as ONE tiled copy
+        if constexpr (!LATE_W2) tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
+    }
     prefetch_l2(a.next, TH);
     const int k0 = tid * EPT;
     // Requested here, converted after the wait: the clusters of this kernel that only become resident when the
