@@ -61,6 +61,8 @@ __device__ __forceinline__ void prefetch_l2(const PrefetchList& pf, int n_thread
 // Split cluster barrier: arrive when the CTA starts, wait right before the first access to a peer's
 // shared memory, which is only legal once every CTA of the cluster has started.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// After fence.mbarrier_init.release.cluster has published the CTA's mbarriers, the arrival itself needs no release.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void fb_stamp(unsigned long long* dbg, int i) {
@@ -460,7 +462,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     // After the mbarriers exist (a peer that has passed cluster_wait() may push to them) and BEFORE the weight copies
     // are issued: with copies of this thread in flight the releasing arrival took as long as the copies (1.3 us), which
     // a cluster that only becomes resident when the previous kernel's CTAs leave pays on the chain.
-    cluster_arrive();
+    cluster_arrive_relaxed();
     if (tid == 0) {
         mbar_expect_tx(&sm.bar, (uint32_t)(S::NR * K * 2 + OR * OC * 2));
         bulk_g2s(sm.w, a.wqkv + (size_t)(kvh * G * HD + rank * QR) * K, QR * K * 2, &sm.bar);
@@ -863,7 +865,7 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         }
     }
     __syncthreads();
-    cluster_arrive();  // after the mbarriers exist, before the weight copies are issued (see the attention block)
+    cluster_arrive_relaxed();  // after the mbarriers exist, before the weight copies are issued (see the attention block)
     if (tid == 0) {
         mbar_expect_tx(&sm.bar, (uint32_t)(2 * U * K * 2 + (LATE_W2 ? 0 : OR * CU * 2)));
         const size_t u0 = (size_t)cid * CU + rank * U;
@@ -872,7 +874,7 @@ __global__ void __launch_bounds__(TH, 1) k_mlp_block(const __grid_constant__ CUt
         // the w2 slice (OR rows x CU columns) as ONE tiled copy
         if constexpr (!LATE_W2) tma_load_2d(sm.w2, &map_w2, cid * CU, rank * OR, &sm.bar);
     }
-    prefetch_l2(a.next, TH);
+    if (cid < FB_HINT_CLUSTERS) prefetch_l2(a.next, TH);   // a hint: partial coverage is fine
     const int k0 = tid * EPT;
     // Requested here, converted after the wait: the clusters of this kernel that only become resident when the
     // attention block's CTAs leave (at most 15 clusters of 8 fit the part at once) run this prologue ON the chain,
