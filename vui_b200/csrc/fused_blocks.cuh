@@ -473,14 +473,10 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     }
     prefetch_l2(a.next, FB_THREADS);
     const int k0 = tid * EPT;
-    float nw[EPT];
-    {
-        bf16 t[EPT];
-        if constexpr (EPT == 4) *reinterpret_cast<uint2*>(t) = __ldg(reinterpret_cast<const uint2*>(a.norm_w + k0));
-        else *reinterpret_cast<unsigned*>(t) = __ldg(reinterpret_cast<const unsigned*>(a.norm_w + k0));
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) nw[j] = bf2f(t[j]);
-    }
+    // requested here, converted after the wait (nothing in the prologue waits for a load, see the MLP block)
+    alignas(8) bf16 nw_raw[EPT];
+    if constexpr (EPT == 4) *reinterpret_cast<uint2*>(nw_raw) = __ldg(reinterpret_cast<const uint2*>(a.norm_w + k0));
+    else *reinterpret_cast<unsigned*>(nw_raw) = __ldg(reinterpret_cast<const unsigned*>(a.norm_w + k0));
     // ---- the row's old keys and its RoPE factors
     // After the tensor-core dot products eight threads finish each interleaved row pair, one per peer CTA:
     const int my_pair = tid >> 3;
@@ -550,6 +546,9 @@ __global__ void __launch_bounds__(FB_THREADS, 1) k_attn_block(const __grid_const
     }
     float x[EPT];
     load_residual<K, EPT>(a.x_in, a.parts_in, a.n_parts_in, k0, x);
+    float nw[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) nw[j] = bf2f(nw_raw[j]);
     if (!early || sl != slot || ps != pos) request(sl, ps);
     fb_stamp(a.dbg, 8);
     if (blockIdx.x == 0) {
